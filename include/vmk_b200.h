@@ -1,0 +1,126 @@
+/* libvmk_b200: C ABI of the B200 (sm_100a) kernels for the three attention-decode ops `prefix`, `spec`
+ * and `dsa`.
+ *
+ * The reference project has no native boundary: each op is reached through a Python module exposing
+ * `def kernel(...)`, called by its verifier as fn(**inputs) (reference verify.py:35-37, 44-45, 139).
+ * The entry points below are what such a kernel module binds instead of its Metal launches; each one
+ * cites the reference launch path it replaces.
+ *
+ * Conventions for every entry point
+ *   - All tensor pointers are DEVICE pointers to C-contiguous arrays; `fp16` means IEEE binary16.
+ *     Inputs are borrowed and never written.  Pointers must be 16-byte aligned.
+ *   - `ws` is caller-provided device scratch of at least vmk_<op>_workspace_bytes(...) bytes,
+ *     256-byte aligned.  The library never allocates device memory and never synchronises; all work is
+ *     enqueued on `stream` (a cudaStream_t passed as void*).  Calls on different streams are
+ *     independent when their workspaces differ.
+ *   - `status` (nullable) is a device int32 the kernels OR bits into when a bounded device-side wait
+ *     ran out (bit 0) or an out-of-range index was clamped (bit 1).  The caller zeroes it and reads it
+ *     back after synchronising.
+ *   - Return value: VMK_OK or a negative VMK_E_* code; vmk_error_string() names it.  No C++
+ *     exception crosses the boundary.
+ */
+#ifndef VMK_B200_H_
+#define VMK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define VMK_API __attribute__((visibility("default")))
+#else
+#define VMK_API
+#endif
+
+#define VMK_OK 0
+#define VMK_E_BADARG (-1)       /* null / misaligned pointer, non-positive dimension */
+#define VMK_E_UNSUPPORTED (-2)  /* shape outside what the kernels implement (see each entry point) */
+#define VMK_E_WORKSPACE (-3)    /* ws_bytes smaller than vmk_<op>_workspace_bytes(...) */
+#define VMK_E_LAUNCH (-4)       /* the CUDA runtime rejected a launch */
+#define VMK_E_DRIVER (-5)       /* tensor-map encoding failed / driver entry point missing */
+
+#define VMK_DSA_TOPK 2048
+#define VMK_SPEC_MAX_DRAFTS 128
+
+VMK_API int vmk_version(void);
+VMK_API const char* vmk_error_string(int code);
+
+/* ---- prefix: shared-prefix decode -------------------------------------------------------------
+ * Replaces the two Metal launches of the reference kernel module (kernels/prefix_opus55_v8.py:282-355:
+ * fused prefix-tile / suffix-stream pass, then the log-sum-exp combine).
+ *   q (N,Hq,D)  kp,vp (Hkv,P,D)  ks,vs (N,Hkv,S,D)  out (N,Hq,D), all fp16.  D must be 128, Hq a
+ *   multiple of Hkv with Hq/Hkv <= 16.
+ *   slens (N) int32, nullable: true suffix length of each request (0..S); NULL means S for all.
+ */
+VMK_API size_t vmk_prefix_workspace_bytes(int N, int Hq, int Hkv, int D, int P, int S);
+VMK_API int vmk_prefix_decode(const void* q, const void* kp, const void* vp, const void* ks, const void* vs,
+                      const int32_t* slens, void* out, int N, int Hq, int Hkv, int D, int P, int S,
+                      void* ws, size_t ws_bytes, int32_t* status, void* stream);
+
+/* ---- spec: speculative chain / tree verification ----------------------------------------------
+ * Replaces the reference's permute / partial / combine launches (kernels/spec_opus55_v7.py:467-521).
+ *   q (B,kd,Hq,D)  k,v (B,Hkv,L,D)  out (B,kd,Hq,D) fp16.  The drafts are the last kd cache positions.
+ *   bits (B,kd,bits_words) uint32, little-endian words: bit j of row (b,i) set = draft i attends draft
+ *   j.  bits_words = 1 is the reference's (B,kd) int32 layout (ops/spec.py:56); kd <= 32*bits_words,
+ *   kd <= VMK_SPEC_MAX_DRAFTS, kd <= L.
+ */
+VMK_API size_t vmk_spec_workspace_bytes(int B, int kd, int Hq, int Hkv, int D, int L);
+VMK_API int vmk_spec_verify(const void* q, const void* k, const void* v, const uint32_t* bits, int bits_words,
+                    void* out, int B, int kd, int Hq, int Hkv, int D, int L, void* ws, size_t ws_bytes,
+                    int32_t* status, void* stream);
+
+/* ---- dsa: DeepSeek sparse attention decode ----------------------------------------------------
+ * Replaces the reference's indexer / select / gather+QK / softmax / PV / reduce launches
+ * (kernels/dsa_opus55_v7.py:946-977).  Fixed head geometry (ops/dsa.py:15): 128 heads, rows of
+ * 576 = 512 latent + 64 rope, 64 indexer heads of width 128, top-2048.
+ *   q (B,128,576)  kv (B,L,576)  iq (B,64,128)  ik (B,L,128) fp16;  w (B,64) fp32;
+ *   lens (B) int32, nullable: valid cache length per request (1..L);  out (B,128,512) fp16.
+ *   idx_out (B,2048) int32 and cnt_out (B) int32, nullable: the selected positions (ascending) and how
+ *   many are valid, exposed so the integer stage can be checked bit for bit.
+ * vmk_dsa_decode runs the three stages below back to back; they are also exported one by one.
+ */
+VMK_API size_t vmk_dsa_workspace_bytes(int B, int L);
+VMK_API int vmk_dsa_decode(const void* q, const void* kv, const void* iq, const void* ik, const float* w,
+                   const int32_t* lens, void* out, int32_t* idx_out, int32_t* cnt_out, int B, int L,
+                   void* ws, size_t ws_bytes, int32_t* status, void* stream);
+
+/* Stage 1 (kernels/dsa_opus55_v7.py:629-661): scores (B,L) fp32 = sum_h w[h]*relu(iq[h].ik[l]), fp32
+ * accumulation.  Positions at or beyond lens[b] are left unwritten. */
+VMK_API int vmk_dsa_indexer(const void* iq, const void* ik, const float* w, const int32_t* lens, float* scores,
+                    int B, int L, int32_t* status, void* stream);
+/* Stage 2 (kernels/dsa_opus55_v7.py:100-307): exact top-2048 of scores[b,:n], n = lens[b] or L; all n
+ * positions when n <= 2048.  Ties at the boundary go to the lowest positions; NaN scores rank last.
+ * idx (B,2048) ascending, entries beyond cnt[b] are 0. */
+VMK_API int vmk_dsa_select(const float* scores, const int32_t* lens, int32_t* idx, int32_t* cnt, int B, int L,
+                   void* stream);
+/* Stage 3 (kernels/dsa_opus55_v7.py:839-871): absorbed-MLA attention over the selected rows. */
+VMK_API size_t vmk_dsa_attend_workspace_bytes(int B);
+VMK_API int vmk_dsa_attend(const void* q, const void* kv, const int32_t* idx, const int32_t* cnt, void* out,
+                   int B, int L, void* ws, size_t ws_bytes, int32_t* status, void* stream);
+
+/* ---- merge of split partials -------------------------------------------------------------------
+ * Log-sum-exp merge used after a KV split across GPUs (the reference merges its in-GPU splits the
+ * same way, kernels/prefix_opus55_v8.py:211-261).  m, l (parts,rows) and o (parts,rows,D) fp32 with m
+ * in the base-2 scaled-score domain the partial kernels emit; out (rows,D) fp16. */
+VMK_API int vmk_lse_merge(const float* m, const float* l, const float* o, int parts, int rows, int D, void* out,
+                  void* stream);
+
+/* Split partials of one rank, for the multi-GPU KV split: the same computations as vmk_prefix_decode /
+ * vmk_spec_verify restricted to keys [key_lo, key_hi) of the shared prefix / the cache, returning the
+ * un-normalised partial (m, l, o) per output row instead of the final output.
+ *   part_m, part_l (rows) fp32, part_o (rows, D) fp32 with rows = N*Hq (prefix) or B*kd*Hq (spec). */
+VMK_API int vmk_prefix_partial(const void* q, const void* kp, const void* vp, const void* ks, const void* vs,
+                       const int32_t* slens, int N, int Hq, int Hkv, int D, int P, int S, int key_lo,
+                       int key_hi, int with_suffix, float* part_m, float* part_l, float* part_o, void* ws,
+                       size_t ws_bytes, int32_t* status, void* stream);
+VMK_API int vmk_spec_partial(const void* q, const void* k, const void* v, const uint32_t* bits, int bits_words,
+                     int B, int kd, int Hq, int Hkv, int D, int L, int key_lo, int key_hi, float* part_m,
+                     float* part_l, float* part_o, void* ws, size_t ws_bytes, int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VMK_B200_H_ */

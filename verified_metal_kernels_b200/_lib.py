@@ -1,0 +1,113 @@
+"""ctypes binding of libvmk_b200.so (the C ABI declared in include/vmk_b200.h).
+
+The library is built in-tree by build.py.  There is no fallback: if it is missing or a call fails, the
+kernel modules raise."""
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libvmk_b200.so")
+
+_c = ctypes
+_vp, _i, _sz = _c.c_void_p, _c.c_int, _c.c_size_t
+
+# name -> (restype, argtypes): one entry per symbol declared in include/vmk_b200.h
+SIGNATURES = {
+    "vmk_version": (_i, []),
+    "vmk_error_string": (_c.c_char_p, [_i]),
+    "vmk_prefix_workspace_bytes": (_sz, [_i] * 6),
+    "vmk_prefix_decode": (_i, [_vp] * 7 + [_i] * 6 + [_vp, _sz, _vp, _vp]),
+    "vmk_spec_workspace_bytes": (_sz, [_i] * 6),
+    "vmk_spec_verify": (_i, [_vp] * 4 + [_i] + [_vp] + [_i] * 6 + [_vp, _sz, _vp, _vp]),
+    "vmk_dsa_workspace_bytes": (_sz, [_i] * 2),
+    "vmk_dsa_decode": (_i, [_vp] * 9 + [_i] * 2 + [_vp, _sz, _vp, _vp]),
+    "vmk_dsa_indexer": (_i, [_vp] * 5 + [_i] * 2 + [_vp, _vp]),
+    "vmk_dsa_select": (_i, [_vp] * 4 + [_i] * 2 + [_vp]),
+    "vmk_dsa_attend_workspace_bytes": (_sz, [_i]),
+    "vmk_dsa_attend": (_i, [_vp] * 5 + [_i] * 2 + [_vp, _sz, _vp, _vp]),
+    "vmk_lse_merge": (_i, [_vp] * 3 + [_i] * 3 + [_vp, _vp]),
+    "vmk_prefix_partial": (_i, [_vp] * 6 + [_i] * 9 + [_vp] * 3 + [_vp, _sz, _vp, _vp]),
+    "vmk_spec_partial": (_i, [_vp] * 4 + [_i] + [_i] * 8 + [_vp] * 3 + [_vp, _sz, _vp, _vp]),
+}
+# exported for experiments, not part of the documented ABI
+_EXTRA = {"vmk_dsa_set_indexer_variant": (_i, [_i])}
+
+_lib = None
+
+
+class VmkError(RuntimeError):
+    def __init__(self, code, what):
+        self.code = code
+        super().__init__(f"{what}: libvmk_b200 error {code} ({error_string(code)})")
+
+
+def lib():
+    """The loaded library (loads it on first use; raises if it has not been built)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m verified_metal_kernels_b200.build` "
+                               "(nvcc, sm_100a); there is no fallback path")
+        L = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in {**SIGNATURES, **_EXTRA}.items():
+            fn = getattr(L, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = L
+    return _lib
+
+
+def error_string(code):
+    return lib().vmk_error_string(int(code)).decode()
+
+
+def check(code, what):
+    if code != 0:
+        raise VmkError(code, what)
+
+
+def ptr(t):
+    """Device (or host) address of a torch tensor, or None."""
+    return None if t is None else t.data_ptr()
+
+
+class Workspace:
+    """Grow-only device scratch buffer per (device, stream), plus the device status word."""
+
+    def __init__(self):
+        self._bufs = {}
+
+    def get(self, nbytes, device, stream_id):
+        import torch
+        key = (device.index, stream_id)
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < nbytes:
+            buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+            self._bufs[key] = buf
+        return buf
+
+
+_workspace = Workspace()
+_status = {}
+
+
+def workspace(nbytes, device, stream_id):
+    return _workspace.get(nbytes, device, stream_id)
+
+
+def status_word(device):
+    import torch
+    s = _status.get(device.index)
+    if s is None:
+        s = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[device.index] = s
+    return s
+
+
+def read_status(device):
+    """Synchronises and returns the device status word (0 = clean; bit 0 = a bounded wait ran out,
+    bit 1 = an index was clamped), then clears it."""
+    s = status_word(device)
+    v = int(s.item())
+    if v:
+        s.zero_()
+    return v

@@ -1,0 +1,403 @@
+// `prefix` and `spec` entry points: launch planning, the split-KV kernel instantiations and the
+// log-sum-exp combine pass.
+#include "attn_core.cuh"
+
+namespace vmk {
+
+// ------------------------------------------------------------------------------------------------
+// kernels
+// ------------------------------------------------------------------------------------------------
+template <int RT, int KS, int STAGES, bool HAS_B, int MIN_CTAS>
+__global__ void __launch_bounds__(256, MIN_CTAS) attn_kernel(const __grid_constant__ AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int cta = blockIdx.x;
+  if (!HAS_B || cta < p.a.n_cta) {
+    attn_core<RT, KS, STAGES>(p.a, p.sc, p.status, cta, smem);
+  } else {
+    attn_core<1, 4, STAGES>(p.b, p.sc, p.status, cta - p.a.n_cta, smem);
+  }
+}
+
+struct CombineSide {
+  const float* part_o;
+  const float* part_ml;
+  int nsplit, MP, rows_outer;
+};
+
+struct CombineParams {
+  CombineSide a, b;
+  int has_b;
+  int Hkv, G, Hq;
+  __half* out;       // (outers, Hq, 128) fp16, or null
+  float* pm;         // when out is null: un-normalised merged partial per row
+  float* pl;
+  float* po;
+};
+
+// One CTA of 128 threads per output row (outer, head); thread d merges column d over every split.
+__global__ void __launch_bounds__(128) combine_kernel(const CombineParams p) {
+  const int row = blockIdx.x;
+  const int d = threadIdx.x;
+  const int outer = row / p.Hq, hq = row % p.Hq;
+  const int h = hq / p.G, g = hq % p.G;
+  float M = -INFINITY;
+  size_t baseA, baseB = 0;
+  {
+    const int z = (outer / p.a.rows_outer) * p.Hkv + h;
+    const int r = (outer % p.a.rows_outer) * p.G + g;
+    baseA = ((size_t)z * p.a.nsplit) * p.a.MP + r;
+    for (int s = 0; s < p.a.nsplit; ++s) M = fmaxf(M, p.a.part_ml[(baseA + (size_t)s * p.a.MP) * 2]);
+  }
+  if (p.has_b) {
+    const int z = (outer / p.b.rows_outer) * p.Hkv + h;
+    const int r = (outer % p.b.rows_outer) * p.G + g;
+    baseB = ((size_t)z * p.b.nsplit) * p.b.MP + r;
+    for (int s = 0; s < p.b.nsplit; ++s) M = fmaxf(M, p.b.part_ml[(baseB + (size_t)s * p.b.MP) * 2]);
+  }
+  float acc = 0.f, lsum = 0.f;
+  for (int s = 0; s < p.a.nsplit; ++s) {
+    const size_t i = baseA + (size_t)s * p.a.MP;
+    const float m = p.a.part_ml[i * 2];
+    const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
+    acc += w * p.a.part_o[i * kHD + d];
+    lsum += w * p.a.part_ml[i * 2 + 1];
+  }
+  if (p.has_b) {
+    for (int s = 0; s < p.b.nsplit; ++s) {
+      const size_t i = baseB + (size_t)s * p.b.MP;
+      const float m = p.b.part_ml[i * 2];
+      const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
+      acc += w * p.b.part_o[i * kHD + d];
+      lsum += w * p.b.part_ml[i * 2 + 1];
+    }
+  }
+  if (p.out != nullptr) {
+    p.out[(size_t)row * kHD + d] = __float2half(acc / lsum);
+  } else {
+    p.po[(size_t)row * kHD + d] = acc;
+    if (d == 0) {
+      p.pm[row] = M;
+      p.pl[row] = lsum;
+    }
+  }
+}
+
+// Merge of `parts` partials per row (used after an exchange between GPUs).
+__global__ void __launch_bounds__(128) lse_merge_kernel(const float* __restrict__ m, const float* __restrict__ l,
+                                                         const float* __restrict__ o, int parts, int rows, int D,
+                                                         __half* __restrict__ out) {
+  const int row = blockIdx.x;
+  float M = -INFINITY;
+  for (int s = 0; s < parts; ++s) M = fmaxf(M, m[(size_t)s * rows + row]);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.f, lsum = 0.f;
+    for (int s = 0; s < parts; ++s) {
+      const float ms = m[(size_t)s * rows + row];
+      const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+      acc += w * o[((size_t)s * rows + row) * D + d];
+      lsum += w * l[(size_t)s * rows + row];
+    }
+    out[(size_t)row * D + d] = __float2half(acc / lsum);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// planning
+// ------------------------------------------------------------------------------------------------
+struct RolePlan {
+  int rt, ks;              // warp layout of the role's CTAs
+  int row_tiles, MP;
+  int nsplit, split_len;
+  int n_cta;
+  size_t off_o, off_ml;    // offsets into the workspace
+};
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+static void pick_layout(int rows, int* rt, int* ks) {
+  if (rows <= 16) { *rt = 1; *ks = 4; }
+  else if (rows <= 32) { *rt = 2; *ks = 4; }
+  else if (rows <= 64) { *rt = 4; *ks = 2; }
+  else { *rt = 8; *ks = 1; }
+}
+
+// Splits the keys of each (group, row tile) so that about `target` CTAs exist, in multiples of 64 keys.
+static void plan_role(RolePlan* r, int groups, int rows, int keys, int target, bool fixed_small) {
+  if (fixed_small) { r->rt = 1; r->ks = 4; } else pick_layout(rows, &r->rt, &r->ks);
+  const int mt = r->rt * 16;
+  r->row_tiles = cdiv(rows, mt);
+  r->MP = r->row_tiles * mt;
+  const int units = groups * r->row_tiles;
+  const int blocks = cdiv(keys > 0 ? keys : 1, kBK);
+  int want = cdiv(target > 0 ? target : 1, units > 0 ? units : 1);
+  if (want > blocks) want = blocks;
+  if (want < 1) want = 1;
+  r->split_len = cdiv(blocks, want) * kBK;
+  r->nsplit = cdiv(blocks * kBK, r->split_len);
+  r->n_cta = units * r->nsplit;
+}
+
+// Reserves the role's partial arrays.  They are sized for `cap` splits, an upper bound of nsplit that
+// does not depend on the key range, so one workspace size serves full and partial (key_lo/key_hi) calls.
+static size_t place(RolePlan* r, int groups, size_t off, int cap) {
+  if (cap < r->nsplit) cap = r->nsplit;
+  r->off_o = align_up(off, 256);
+  r->off_ml = align_up(r->off_o + (size_t)groups * cap * r->MP * kHD * sizeof(float), 256);
+  return r->off_ml + (size_t)groups * cap * r->MP * 2 * sizeof(float);
+}
+
+struct PrefixPlan {
+  RolePlan a, b;
+  bool has_b;
+  size_t ws_bytes;
+};
+
+static PrefixPlan plan_prefix(int N, int Hq, int Hkv, int P, int S, int key_lo, int key_hi, bool with_suffix) {
+  PrefixPlan pl;
+  const int G = Hq / Hkv;
+  const int sms = sm_count();
+  pl.has_b = with_suffix && S > 0;
+  // Suffix role: one group per (request, kv head), G rows; aim for chunks of at least 128 keys.
+  int target_b = 0;
+  if (pl.has_b) {
+    const int groups_b = N * Hkv;
+    int per = cdiv(2 * sms, groups_b);
+    const int maxper = cdiv(S, 128);
+    if (per > maxper) per = maxper;
+    if (per < 1) per = 1;
+    plan_role(&pl.b, groups_b, G, S, groups_b * per, true);
+    target_b = pl.b.n_cta;
+  } else {
+    pl.b = RolePlan{};
+  }
+  int target_a = 2 * sms - target_b;
+  if (target_a < sms) target_a = sms;
+  plan_role(&pl.a, Hkv, N * G, key_hi - key_lo, target_a, false);
+  size_t off = place(&pl.a, Hkv, 0, cdiv(2 * sms, Hkv * pl.a.row_tiles));
+  if (pl.has_b) off = place(&pl.b, N * Hkv, off, pl.b.nsplit);
+  pl.ws_bytes = align_up(off, 256);
+  return pl;
+}
+
+struct SpecPlan {
+  RolePlan a;
+  size_t ws_bytes;
+};
+
+static SpecPlan plan_spec(int B, int kd, int Hq, int Hkv, int key_lo, int key_hi) {
+  SpecPlan pl;
+  const int G = Hq / Hkv;
+  plan_role(&pl.a, B * Hkv, kd * G, key_hi - key_lo, 2 * sm_count(), false);
+  pl.ws_bytes = align_up(place(&pl.a, B * Hkv, 0, cdiv(2 * sm_count(), B * Hkv * pl.a.row_tiles)), 256);
+  return pl;
+}
+
+// ------------------------------------------------------------------------------------------------
+// launch
+// ------------------------------------------------------------------------------------------------
+template <int RT, int KS, int STAGES, bool HAS_B, int MIN_CTAS>
+static int launch_attn_inst(const AttnParams& p, int n_cta, cudaStream_t stream) {
+  constexpr int smem = attn_smem_bytes<(RT > 1 ? RT : 1), STAGES>();
+  auto kern = attn_kernel<RT, KS, STAGES, HAS_B, MIN_CTAS>;
+  static bool configured = false;   // per instantiation; the attribute is per device function
+  static int configured_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured || configured_dev != dev) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return check_launch(e);
+    configured = true;
+    configured_dev = dev;
+  }
+  kern<<<n_cta, 256, smem, stream>>>(p);
+  return check_launch(cudaGetLastError());
+}
+
+template <bool HAS_B>
+static int launch_attn(const AttnParams& p, int rt, int n_cta, cudaStream_t stream) {
+  switch (rt) {
+    case 1: return launch_attn_inst<1, 4, 3, HAS_B, 2>(p, n_cta, stream);
+    case 2: return launch_attn_inst<2, 4, 3, HAS_B, 2>(p, n_cta, stream);
+    case 4: return launch_attn_inst<4, 2, 4, HAS_B, 1>(p, n_cta, stream);
+    default: return launch_attn_inst<8, 1, 4, HAS_B, 1>(p, n_cta, stream);
+  }
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+static void fill_role(AttnRole* r, const RolePlan& pl, uint8_t* ws) {
+  r->row_tiles = pl.row_tiles;
+  r->MP = pl.MP;
+  r->nsplit = pl.nsplit;
+  r->split_len = pl.split_len;
+  r->n_cta = pl.n_cta;
+  r->part_o = reinterpret_cast<float*>(ws + pl.off_o);
+  r->part_ml = reinterpret_cast<float*>(ws + pl.off_ml);
+}
+
+static int prefix_impl(const void* q, const void* kp, const void* vp, const void* ks, const void* vs,
+                       const int32_t* slens, void* out, int N, int Hq, int Hkv, int D, int P, int S, int key_lo,
+                       int key_hi, int with_suffix, float* pm, float* plv, float* po, void* ws, size_t ws_bytes,
+                       int32_t* status, cudaStream_t stream) {
+  if (N <= 0 || Hq <= 0 || Hkv <= 0 || P <= 0 || S < 0) return VMK_E_BADARG;
+  if (D != kHD || Hq % Hkv != 0 || Hq / Hkv > 16) return VMK_E_UNSUPPORTED;
+  if ((long long)N * (Hq / Hkv) > (1 << 24)) return VMK_E_UNSUPPORTED;
+  if (!q || !kp || !vp || (S > 0 && with_suffix && (!ks || !vs)) || (!out && !(pm && plv && po)) || !ws)
+    return VMK_E_BADARG;
+  if (!aligned16(q) || !aligned16(kp) || !aligned16(vp) || !aligned16(ks) || !aligned16(vs) || !aligned16(out) ||
+      (reinterpret_cast<uintptr_t>(ws) & 255))
+    return VMK_E_BADARG;
+  if (key_lo < 0 || key_hi > P || key_lo > key_hi) return VMK_E_BADARG;
+  const int G = Hq / Hkv;
+  const PrefixPlan pl = plan_prefix(N, Hq, Hkv, P, S, key_lo, key_hi, with_suffix != 0);
+  if (ws_bytes < pl.ws_bytes) return VMK_E_WORKSPACE;
+
+  AttnParams p;
+  memset(&p, 0, sizeof(p));
+  p.sc = kLog2e / sqrtf((float)D);
+  p.status = status;
+  int rc = make_tmap_3d(&p.a.tmK, kp, D, P, Hkv, 64, kBK);
+  if (rc) return rc;
+  rc = make_tmap_3d(&p.a.tmV, vp, D, P, Hkv, 64, kBK);
+  if (rc) return rc;
+  p.a.q = static_cast<const __half*>(q);
+  p.a.n_groups = Hkv; p.a.Hkv = Hkv; p.a.G = G; p.a.Hq = Hq;
+  p.a.rows_outer = N;
+  p.a.klen = P; p.a.key_lo = key_lo; p.a.key_hi = key_hi;
+  p.a.mask_start = INT_MAX;
+  fill_role(&p.a, pl.a, static_cast<uint8_t*>(ws));
+  if (pl.has_b) {
+    rc = make_tmap_3d(&p.b.tmK, ks, D, S, (uint64_t)N * Hkv, 64, kBK);
+    if (rc) return rc;
+    rc = make_tmap_3d(&p.b.tmV, vs, D, S, (uint64_t)N * Hkv, 64, kBK);
+    if (rc) return rc;
+    p.b.q = static_cast<const __half*>(q);
+    p.b.klens = slens;
+    p.b.n_groups = N * Hkv; p.b.Hkv = Hkv; p.b.G = G; p.b.Hq = Hq;
+    p.b.rows_outer = 1;
+    p.b.klen = S; p.b.key_lo = 0; p.b.key_hi = S;
+    p.b.mask_start = INT_MAX;
+    fill_role(&p.b, pl.b, static_cast<uint8_t*>(ws));
+    rc = launch_attn<true>(p, pl.a.rt, pl.a.n_cta + pl.b.n_cta, stream);
+  } else {
+    rc = launch_attn<false>(p, pl.a.rt, pl.a.n_cta, stream);
+  }
+  if (rc) return rc;
+
+  CombineParams c;
+  memset(&c, 0, sizeof(c));
+  c.a = CombineSide{p.a.part_o, p.a.part_ml, pl.a.nsplit, pl.a.MP, N};
+  c.has_b = pl.has_b ? 1 : 0;
+  if (pl.has_b) c.b = CombineSide{p.b.part_o, p.b.part_ml, pl.b.nsplit, pl.b.MP, 1};
+  c.Hkv = Hkv; c.G = G; c.Hq = Hq;
+  c.out = static_cast<__half*>(out);
+  c.pm = pm; c.pl = plv; c.po = po;
+  combine_kernel<<<N * Hq, 128, 0, stream>>>(c);
+  return check_launch(cudaGetLastError());
+}
+
+static int spec_impl(const void* q, const void* k, const void* v, const uint32_t* bits, int bits_words, void* out,
+                     int B, int kd, int Hq, int Hkv, int D, int L, int key_lo, int key_hi, float* pm, float* plv,
+                     float* po, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream) {
+  if (B <= 0 || kd <= 0 || Hq <= 0 || Hkv <= 0 || L <= 0 || bits_words <= 0) return VMK_E_BADARG;
+  if (D != kHD || Hq % Hkv != 0 || Hq / Hkv > 16) return VMK_E_UNSUPPORTED;
+  if (kd > L || kd > VMK_SPEC_MAX_DRAFTS || kd > 32 * bits_words || bits_words > kMaxMaskWords) return VMK_E_UNSUPPORTED;
+  if (!q || !k || !v || !bits || (!out && !(pm && plv && po)) || !ws) return VMK_E_BADARG;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || (reinterpret_cast<uintptr_t>(bits) & 3) ||
+      (reinterpret_cast<uintptr_t>(ws) & 255))
+    return VMK_E_BADARG;
+  if (key_lo < 0 || key_hi > L || key_lo > key_hi) return VMK_E_BADARG;
+  const int G = Hq / Hkv;
+  const SpecPlan pl = plan_spec(B, kd, Hq, Hkv, key_lo, key_hi);
+  if (ws_bytes < pl.ws_bytes) return VMK_E_WORKSPACE;
+
+  AttnParams p;
+  memset(&p, 0, sizeof(p));
+  p.sc = kLog2e / sqrtf((float)D);
+  p.status = status;
+  int rc = make_tmap_3d(&p.a.tmK, k, D, L, (uint64_t)B * Hkv, 64, kBK);
+  if (rc) return rc;
+  rc = make_tmap_3d(&p.a.tmV, v, D, L, (uint64_t)B * Hkv, 64, kBK);
+  if (rc) return rc;
+  p.a.q = static_cast<const __half*>(q);
+  p.a.out = static_cast<__half*>(out);
+  p.a.bits = bits;
+  p.a.bits_words = bits_words;
+  p.a.n_groups = B * Hkv; p.a.Hkv = Hkv; p.a.G = G; p.a.Hq = Hq;
+  p.a.rows_outer = kd;
+  p.a.klen = L; p.a.key_lo = key_lo; p.a.key_hi = key_hi;
+  p.a.mask_start = L - kd;
+  fill_role(&p.a, pl.a, static_cast<uint8_t*>(ws));
+  p.a.direct = (out != nullptr && pl.a.nsplit == 1 && key_hi > key_lo) ? 1 : 0;
+  rc = launch_attn<false>(p, pl.a.rt, pl.a.n_cta, stream);
+  if (rc || p.a.direct) return rc;
+
+  CombineParams c;
+  memset(&c, 0, sizeof(c));
+  c.a = CombineSide{p.a.part_o, p.a.part_ml, pl.a.nsplit, pl.a.MP, kd};
+  c.Hkv = Hkv; c.G = G; c.Hq = Hq;
+  c.out = static_cast<__half*>(out);
+  c.pm = pm; c.pl = plv; c.po = po;
+  combine_kernel<<<B * kd * Hq, 128, 0, stream>>>(c);
+  return check_launch(cudaGetLastError());
+}
+
+}  // namespace vmk
+
+// ------------------------------------------------------------------------------------------------
+// C ABI
+// ------------------------------------------------------------------------------------------------
+using namespace vmk;
+
+extern "C" size_t vmk_prefix_workspace_bytes(int N, int Hq, int Hkv, int D, int P, int S) {
+  if (N <= 0 || Hq <= 0 || Hkv <= 0 || P <= 0 || S < 0 || D != kHD || Hq % Hkv != 0) return 0;
+  return plan_prefix(N, Hq, Hkv, P, S, 0, P, true).ws_bytes;
+}
+
+extern "C" int vmk_prefix_decode(const void* q, const void* kp, const void* vp, const void* ks, const void* vs,
+                                 const int32_t* slens, void* out, int N, int Hq, int Hkv, int D, int P, int S,
+                                 void* ws, size_t ws_bytes, int32_t* status, void* stream) {
+  if (!out) return VMK_E_BADARG;
+  return prefix_impl(q, kp, vp, ks, vs, slens, out, N, Hq, Hkv, D, P, S, 0, P, 1, nullptr, nullptr, nullptr, ws,
+                     ws_bytes, status, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int vmk_prefix_partial(const void* q, const void* kp, const void* vp, const void* ks, const void* vs,
+                                  const int32_t* slens, int N, int Hq, int Hkv, int D, int P, int S, int key_lo,
+                                  int key_hi, int with_suffix, float* part_m, float* part_l, float* part_o, void* ws,
+                                  size_t ws_bytes, int32_t* status, void* stream) {
+  if (!part_m || !part_l || !part_o) return VMK_E_BADARG;
+  return prefix_impl(q, kp, vp, ks, vs, slens, nullptr, N, Hq, Hkv, D, P, S, key_lo, key_hi, with_suffix, part_m,
+                     part_l, part_o, ws, ws_bytes, status, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" size_t vmk_spec_workspace_bytes(int B, int kd, int Hq, int Hkv, int D, int L) {
+  if (B <= 0 || kd <= 0 || Hq <= 0 || Hkv <= 0 || L <= 0 || D != kHD || Hq % Hkv != 0) return 0;
+  return plan_spec(B, kd, Hq, Hkv, 0, L).ws_bytes;
+}
+
+extern "C" int vmk_spec_verify(const void* q, const void* k, const void* v, const uint32_t* bits, int bits_words,
+                               void* out, int B, int kd, int Hq, int Hkv, int D, int L, void* ws, size_t ws_bytes,
+                               int32_t* status, void* stream) {
+  if (!out) return VMK_E_BADARG;
+  return spec_impl(q, k, v, bits, bits_words, out, B, kd, Hq, Hkv, D, L, 0, L, nullptr, nullptr, nullptr, ws,
+                   ws_bytes, status, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int vmk_spec_partial(const void* q, const void* k, const void* v, const uint32_t* bits, int bits_words,
+                                int B, int kd, int Hq, int Hkv, int D, int L, int key_lo, int key_hi, float* part_m,
+                                float* part_l, float* part_o, void* ws, size_t ws_bytes, int32_t* status,
+                                void* stream) {
+  if (!part_m || !part_l || !part_o) return VMK_E_BADARG;
+  return spec_impl(q, k, v, bits, bits_words, nullptr, B, kd, Hq, Hkv, D, L, key_lo, key_hi, part_m, part_l, part_o,
+                   ws, ws_bytes, status, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int vmk_lse_merge(const float* m, const float* l, const float* o, int parts, int rows, int D, void* out,
+                             void* stream) {
+  if (!m || !l || !o || !out || parts <= 0 || rows <= 0 || D <= 0) return VMK_E_BADARG;
+  lse_merge_kernel<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(m, l, o, parts, rows, D,
+                                                                          static_cast<__half*>(out));
+  return check_launch(cudaGetLastError());
+}

@@ -1,0 +1,336 @@
+// Split-KV decode attention core shared by `prefix` and `spec`.
+//
+// One CTA = one (key group z, row tile, key split).  The rows of a tile are the stacked query rows that
+// share the group's keys (requests x GQA heads for the shared prefix, draft rows x GQA heads for
+// speculative verification, the GQA heads alone for a private suffix).  Keys stream through a ring of
+// TMA-filled shared-memory stages (K and V tiles of 64 keys x 128, 128-byte swizzle, out-of-range keys
+// read as zero); scores, softmax statistics and the output accumulate in fp32; P is rounded to fp16 for
+// the P.V product, as fused fp16 SDPA implementations do.  Each CTA emits an un-normalised partial
+// (m, l, o) per row, m in the base-2 scaled-score domain; a combine pass merges the splits.
+//
+// Warp layout inside a CTA: RT row tiles of 16 rows x KS key slices; warp (rt, ks) owns rows
+// [16 rt, 16 rt + 16) and keys [ks*64/KS, (ks+1)*64/KS) of every 64-key block, with private softmax
+// statistics that are merged through shared memory at the end.  Small row counts therefore still use
+// every warp (decode shapes have 4..32 rows), large ones get up to 128 rows per CTA.
+#pragma once
+
+#include <limits.h>
+
+#include "common.cuh"
+
+namespace vmk {
+
+constexpr int kBK = 64;                       // keys per stage
+constexpr int kHD = 128;                      // head dimension
+constexpr int kHalfTile = kBK * 128;          // one swizzled [64 keys][128 B] box
+constexpr int kStageBytes = 4 * kHalfTile;    // K lo, K hi, V lo, V hi = 32 KiB
+constexpr int kQStride = kHD * 2 + 16;        // padded query row in shared memory (bank-conflict free)
+constexpr int kMergeStride = 132;             // floats per row in the end-of-CTA merge buffer
+constexpr int kMaxMaskWords = VMK_SPEC_MAX_DRAFTS / 32;
+
+struct AttnRole {
+  CUtensorMap tmK, tmV;     // fp16 (groups, keys, 128), box (64, 64, 1)
+  const __half* q;          // queries; row (outer, head) at ((outer * Hq) + head) * 128
+  __half* out;              // same layout as q; written only when `direct`
+  const uint32_t* bits;     // draft visibility words, row (outer) at outer * bits_words; null = no mask
+  const int32_t* klens;     // valid key count per outer group (ragged suffixes); null = klen
+  float* part_o;            // ((z * nsplit + split) * MP + row) * 128
+  float* part_ml;           // ((z * nsplit + split) * MP + row) * 2  -> (m, l)
+  int n_groups, Hkv, G, Hq;
+  int rows_outer;           // outer rows (requests / drafts) stacked per group; rows = rows_outer * G
+  int row_tiles;            // ceil(rows / (16 RT))
+  int nsplit, split_len;    // split_len is a multiple of 64
+  int klen;                 // key extent of the tensor
+  int key_lo, key_hi;       // keys processed: [key_lo, key_hi)
+  int mask_start;           // keys at or beyond it are subject to `bits` (INT_MAX = never)
+  int bits_words;
+  int MP;                   // padded rows per (group, split) in the partial arrays
+  int direct;               // single split and nothing to merge with: write the fp16 result
+  int n_cta;
+};
+
+struct AttnParams {
+  AttnRole a, b;            // b is used only by kernels instantiated with HAS_B
+  float sc;                 // softmax scale * log2(e)
+  int32_t* status;
+};
+
+template <int RT, int STAGES>
+constexpr int attn_smem_bytes() {
+  return STAGES * kStageBytes + RT * 16 * kQStride + STAGES * 8 + 1024 /* alignment slack */;
+}
+
+template <int RT, int KS, int STAGES>
+__device__ __forceinline__ void attn_core(const AttnRole& R, float sc, int32_t* status, int cta, uint8_t* smem) {
+  constexpr int NW = RT * KS;          // computing warps
+  constexpr int KPW = kBK / KS;        // keys per warp per block
+  constexpr int NT8 = KPW / 8;         // score n-tiles per warp
+  constexpr int MT = RT * 16;
+  static_assert(KPW >= 16 && NW <= 8, "warp layout");
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nthreads = blockDim.x;
+  const bool active = warp < NW;
+  const int rt = warp / KS, ks = warp % KS;
+
+  // ---- which piece of work --------------------------------------------------------------------
+  const int split = cta % R.nsplit;
+  const int t2 = cta / R.nsplit;
+  const int tile = t2 % R.row_tiles;
+  const int z = t2 / R.row_tiles;
+  const int zg = z / R.Hkv, h = z % R.Hkv;
+  const int rows = R.rows_outer * R.G;
+  const int row0 = tile * MT;
+  const int kbeg = R.key_lo + split * R.split_len;
+  int kend = min(kbeg + R.split_len, R.key_hi);
+  if (R.klens != nullptr) {
+    int kv = R.klens[zg];
+    if (kv < 0 || kv > R.klen) {
+      report(status, kStatusBadIndex);
+      kv = max(0, min(kv, R.klen));
+    }
+    kend = min(kend, kv);
+  }
+  const int nblk = kend > kbeg ? (kend - kbeg + kBK - 1) / kBK : 0;
+
+  uint8_t* stage0 = smem;
+  uint8_t* sQ = smem + STAGES * kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sQ + MT * kQStride);
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) mbar_init(&bars[s], 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  auto issue = [&](int j) {
+    const int s = j % STAGES;
+    uint8_t* st = stage0 + s * kStageBytes;
+    const int kb = kbeg + j * kBK;
+    mbar_expect_tx(&bars[s], kStageBytes);
+    tma_load_3d(st, &R.tmK, 0, kb, z, &bars[s]);
+    tma_load_3d(st + kHalfTile, &R.tmK, 64, kb, z, &bars[s]);
+    tma_load_3d(st + 2 * kHalfTile, &R.tmV, 0, kb, z, &bars[s]);
+    tma_load_3d(st + 3 * kHalfTile, &R.tmV, 64, kb, z, &bars[s]);
+  };
+  if (tid == 0) {
+    for (int j = 0; j < STAGES && j < nblk; ++j) issue(j);
+  }
+
+  // ---- query tile -> shared memory -> A fragments ------------------------------------------------
+  for (int i = tid; i < MT * 16; i += nthreads) {
+    const int r = i >> 4, c = i & 15;
+    const int row = row0 + r;
+    uint4 val = make_uint4(0u, 0u, 0u, 0u);
+    if (row < rows) {
+      const size_t outer = (size_t)zg * R.rows_outer + row / R.G;
+      const int head = h * R.G + row % R.G;
+      val = *reinterpret_cast<const uint4*>(R.q + (outer * R.Hq + head) * kHD + c * 8);
+    }
+    *reinterpret_cast<uint4*>(sQ + r * kQStride + c * 16) = val;
+  }
+  __syncthreads();
+
+  uint32_t qf[8][4];
+  if (active) {
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk)
+      ldsm_x4(qf[kk], smem_u32(sQ + (rt * 16 + (lane & 15)) * kQStride + (kk * 2 + (lane >> 4)) * 16));
+  }
+
+  // The two rows this thread owns in its warp's 16-row tile, and their draft-visibility words.
+  const int r_lo = row0 + rt * 16 + (lane >> 2), r_hi = r_lo + 8;
+  uint32_t mw_lo[kMaxMaskWords], mw_hi[kMaxMaskWords];
+#pragma unroll
+  for (int w = 0; w < kMaxMaskWords; ++w) mw_lo[w] = mw_hi[w] = 0xffffffffu;
+  if (R.bits != nullptr && active) {
+#pragma unroll
+    for (int w = 0; w < kMaxMaskWords; ++w) {
+      if (w < R.bits_words) {
+        if (r_lo < rows) mw_lo[w] = R.bits[((size_t)zg * R.rows_outer + r_lo / R.G) * R.bits_words + w];
+        if (r_hi < rows) mw_hi[w] = R.bits[((size_t)zg * R.rows_outer + r_hi / R.G) * R.bits_words + w];
+      }
+    }
+  }
+  auto visible = [&](const uint32_t (&mw)[kMaxMaskWords], int j) -> bool {
+    uint32_t word = mw[0];
+#pragma unroll
+    for (int w = 1; w < kMaxMaskWords; ++w) word = ((j >> 5) == w) ? mw[w] : word;
+    return (word >> (j & 31)) & 1u;
+  };
+
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+  float oacc[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
+
+  // ---- key blocks ---------------------------------------------------------------------------------
+  for (int j = 0; j < nblk; ++j) {
+    const int s = j % STAGES;
+    const bool arrived = mbar_wait(&bars[s], (uint32_t)((j / STAGES) & 1));
+    if (__syncthreads_or(!arrived)) {   // also: every warp is done with block j-1
+      if (tid == 0) report(status, kStatusTimeout);
+      return;
+    }
+    if (tid == 0 && j >= 1 && j - 1 + STAGES < nblk) issue(j - 1 + STAGES);
+
+    uint8_t* st = stage0 + s * kStageBytes;
+    const int kb = kbeg + j * kBK;
+    const bool tail = kb + kBK > kend;
+    if (tail && kend < R.klen) {
+      // Keys past kend exist in memory (ragged length / split of another rank): their V rows must not
+      // reach the MMA, where 0 * Inf would poison the row.  Uniform across the CTA.
+      const int r0 = kend - kb;
+      for (int i = tid; i < (kBK - r0) * 16; i += nthreads) {
+        const int r = r0 + (i >> 4), c = i & 15;
+        *reinterpret_cast<uint4*>(st + (2 + (c >> 3)) * kHalfTile + swz128(r, c & 7)) = make_uint4(0u, 0u, 0u, 0u);
+      }
+      __syncthreads();
+    }
+    if (!active) continue;
+
+    // S = Q K^T for this warp's 16 rows x KPW keys
+    float sacc[NT8][4];
+#pragma unroll
+    for (int n = 0; n < NT8; ++n) sacc[n][0] = sacc[n][1] = sacc[n][2] = sacc[n][3] = 0.f;
+    const int key0 = ks * KPW;
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+#pragma unroll
+      for (int np = 0; np < KPW / 16; ++np) {
+        // matrices: (keys 0-7, d 0-7) (keys 0-7, d 8-15) (keys 8-15, d 0-7) (keys 8-15, d 8-15)
+        const int mi = lane >> 3;
+        const uint32_t key = key0 + np * 16 + (mi >> 1) * 8 + (lane & 7);
+        const uint32_t ch = kk * 2 + (mi & 1);
+        uint32_t b[4];
+        ldsm_x4(b, smem_u32(st + (ch >> 3) * kHalfTile + swz128(key, ch & 7)));
+        mma_16816(sacc[2 * np], qf[kk], b[0], b[1]);
+        mma_16816(sacc[2 * np + 1], qf[kk], b[2], b[3]);
+      }
+    }
+
+    // scale, mask, online softmax
+    float bm_lo = -INFINITY, bm_hi = -INFINITY;
+    const bool edge = tail || (kb + kBK > R.mask_start);
+#pragma unroll
+    for (int n = 0; n < NT8; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float t = sacc[n][e] * sc;
+        if (edge) {
+          const int key = kb + key0 + n * 8 + 2 * (lane & 3) + (e & 1);
+          bool ok = key < kend;
+          if (ok && key >= R.mask_start) ok = visible((e < 2) ? mw_lo : mw_hi, key - R.mask_start);
+          t = ok ? t : -INFINITY;
+        }
+        sacc[n][e] = t;
+        if (e < 2) bm_lo = fmaxf(bm_lo, t); else bm_hi = fmaxf(bm_hi, t);
+      }
+    }
+    bm_lo = fmaxf(bm_lo, __shfl_xor_sync(0xffffffffu, bm_lo, 1));
+    bm_lo = fmaxf(bm_lo, __shfl_xor_sync(0xffffffffu, bm_lo, 2));
+    bm_hi = fmaxf(bm_hi, __shfl_xor_sync(0xffffffffu, bm_hi, 1));
+    bm_hi = fmaxf(bm_hi, __shfl_xor_sync(0xffffffffu, bm_hi, 2));
+    const float mn_lo = fmaxf(m_lo, bm_lo), mn_hi = fmaxf(m_hi, bm_hi);
+    const float mu_lo = (mn_lo == -INFINITY) ? 0.f : mn_lo, mu_hi = (mn_hi == -INFINITY) ? 0.f : mn_hi;
+    const float al_lo = exp2f(m_lo - mu_lo), al_hi = exp2f(m_hi - mu_hi);
+    m_lo = mn_lo;
+    m_hi = mn_hi;
+    float ps_lo = 0.f, ps_hi = 0.f;
+#pragma unroll
+    for (int n = 0; n < NT8; ++n) {
+      sacc[n][0] = exp2f(sacc[n][0] - mu_lo);
+      sacc[n][1] = exp2f(sacc[n][1] - mu_lo);
+      sacc[n][2] = exp2f(sacc[n][2] - mu_hi);
+      sacc[n][3] = exp2f(sacc[n][3] - mu_hi);
+      ps_lo += sacc[n][0] + sacc[n][1];
+      ps_hi += sacc[n][2] + sacc[n][3];
+    }
+    l_lo = l_lo * al_lo + ps_lo;
+    l_hi = l_hi * al_hi + ps_hi;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      oacc[i][0] *= al_lo;
+      oacc[i][1] *= al_lo;
+      oacc[i][2] *= al_hi;
+      oacc[i][3] *= al_hi;
+    }
+
+    // O += P V
+#pragma unroll
+    for (int k2 = 0; k2 < KPW / 16; ++k2) {
+      uint32_t pa[4];
+      pa[0] = pack_half2(sacc[2 * k2][0], sacc[2 * k2][1]);
+      pa[1] = pack_half2(sacc[2 * k2][2], sacc[2 * k2][3]);
+      pa[2] = pack_half2(sacc[2 * k2 + 1][0], sacc[2 * k2 + 1][1]);
+      pa[3] = pack_half2(sacc[2 * k2 + 1][2], sacc[2 * k2 + 1][3]);
+#pragma unroll
+      for (int dp = 0; dp < 8; ++dp) {
+        // transposed matrices: (keys 0-7, d 0-7) (keys 8-15, d 0-7) (keys 0-7, d 8-15) (keys 8-15, d 8-15)
+        const int mi = lane >> 3;
+        const uint32_t key = key0 + k2 * 16 + (mi & 1) * 8 + (lane & 7);
+        const uint32_t ch = dp * 2 + (mi >> 1);
+        uint32_t b[4];
+        ldsm_x4_t(b, smem_u32(st + (2 + (ch >> 3)) * kHalfTile + swz128(key, ch & 7)));
+        mma_16816(oacc[2 * dp], pa, b[0], b[1]);
+        mma_16816(oacc[2 * dp + 1], pa, b[2], b[3]);
+      }
+    }
+  }
+
+  // ---- merge the KS key slices of each row tile, emit ------------------------------------------
+  __syncthreads();   // every stage has been consumed; the ring is reused as the merge buffer
+  float* mo = reinterpret_cast<float*>(stage0);                      // [NW][16][kMergeStride]
+  float* ml = mo + NW * 16 * kMergeStride;                           // [NW][16][2]
+  if (active) {
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    float* wo = mo + warp * 16 * kMergeStride;
+    const int rl = lane >> 2, c0 = 2 * (lane & 3);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      *reinterpret_cast<float2*>(wo + rl * kMergeStride + i * 8 + c0) = make_float2(oacc[i][0], oacc[i][1]);
+      *reinterpret_cast<float2*>(wo + (rl + 8) * kMergeStride + i * 8 + c0) = make_float2(oacc[i][2], oacc[i][3]);
+    }
+    if ((lane & 3) == 0) {
+      ml[(warp * 16 + rl) * 2] = m_lo;
+      ml[(warp * 16 + rl) * 2 + 1] = l_lo;
+      ml[(warp * 16 + rl + 8) * 2] = m_hi;
+      ml[(warp * 16 + rl + 8) * 2 + 1] = l_hi;
+    }
+  }
+  __syncthreads();
+  const size_t slot = (size_t)z * R.nsplit + split;
+  for (int i = tid; i < MT * kHD; i += nthreads) {
+    const int row = i >> 7, d = i & 127;
+    const int grow = row0 + row;
+    if (grow >= rows) continue;
+    const int wr = (row >> 4) * KS, rr = row & 15;
+    float M = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < KS; ++k) M = fmaxf(M, ml[((wr + k) * 16 + rr) * 2]);
+    float acc = 0.f, lsum = 0.f;
+#pragma unroll
+    for (int k = 0; k < KS; ++k) {
+      const float mk = ml[((wr + k) * 16 + rr) * 2];
+      const float wgt = (mk == -INFINITY) ? 0.f : exp2f(mk - M);
+      acc += wgt * mo[((wr + k) * 16 + rr) * kMergeStride + d];
+      lsum += wgt * ml[((wr + k) * 16 + rr) * 2 + 1];
+    }
+    if (R.direct) {
+      const size_t outer = (size_t)zg * R.rows_outer + grow / R.G;
+      const int head = h * R.G + grow % R.G;
+      R.out[(outer * R.Hq + head) * kHD + d] = __float2half(acc / lsum);
+    } else {
+      R.part_o[(slot * R.MP + grow) * kHD + d] = acc;
+      if (d == 0) {
+        R.part_ml[(slot * R.MP + grow) * 2] = M;
+        R.part_ml[(slot * R.MP + grow) * 2 + 1] = lsum;
+      }
+    }
+  }
+}
+
+}  // namespace vmk

@@ -1,0 +1,100 @@
+"""Kernel module for op `dsa` (DeepSeek sparse attention decode) on B200.
+
+Drop-in for the reference's kernel module contract (reference kernels/dsa_opus55_v7.py:946, called as
+fn(**inputs) by verify.py:139 with lens=None when absent); indexer, top-2048 select and sparse MLA
+attention are sm_100a CUDA behind libvmk_b200's C ABI."""
+import torch
+
+from .. import _lib
+from ._common import need, stage_in
+
+H, DK, DC, HI, DI, TOPK = 128, 576, 512, 64, 128, 2048
+
+
+def _check(q, kv, iq, ik, w, lens):
+    need(q, "q", torch.float16, dims=3)
+    B = q.shape[0]
+    need(q, "q", torch.float16, shape=(B, H, DK))
+    need(kv, "kv", torch.float16, dims=3)
+    L = kv.shape[1]
+    need(kv, "kv", torch.float16, shape=(B, L, DK))
+    need(iq, "iq", torch.float16, shape=(B, HI, DI))
+    need(ik, "ik", torch.float16, shape=(B, L, DI))
+    need(w, "w", torch.float32, shape=(B, HI))
+    if lens is not None:
+        need(lens, "lens", torch.int32, shape=(B,))
+    return B, L
+
+
+def kernel(q, kv, iq, ik, w, lens=None, return_selection=False):
+    """q (B,128,576), kv (B,L,576), iq (B,64,128), ik (B,L,128) fp16, w (B,64) fp32, lens (B,) int32 or
+    None -> (B,128,512) fp16.  With return_selection=True also returns (idx (B,2048) int32 ascending,
+    cnt (B,) int32), the integer stage's result.  Inputs are not modified; host tensors are copied in
+    and the result is returned on the host."""
+    (q, kv, iq, ik, w, lens), host = stage_in([q, kv, iq, ik, w, lens])
+    B, L = _check(q, kv, iq, ik, w, lens)
+    lib = _lib.lib()
+    dev = q.device
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream()
+        out = torch.empty(B, H, DC, dtype=torch.float16, device=dev)
+        idx = torch.empty(B, TOPK, dtype=torch.int32, device=dev) if return_selection else None
+        cnt = torch.empty(B, dtype=torch.int32, device=dev) if return_selection else None
+        nbytes = lib.vmk_dsa_workspace_bytes(B, L)
+        ws = _lib.workspace(nbytes, dev, stream.cuda_stream)
+        rc = lib.vmk_dsa_decode(_lib.ptr(q), _lib.ptr(kv), _lib.ptr(iq), _lib.ptr(ik), _lib.ptr(w), _lib.ptr(lens),
+                                _lib.ptr(out), _lib.ptr(idx), _lib.ptr(cnt), B, L, _lib.ptr(ws), ws.numel(),
+                                _lib.ptr(_lib.status_word(dev)), stream.cuda_stream)
+    _lib.check(rc, "vmk_dsa_decode")
+    if host:
+        out = out.cpu()
+    return (out, idx, cnt) if return_selection else out
+
+
+def indexer(iq, ik, w, lens=None):
+    """Stage 1 alone: fp32 scores (B,L); positions at or beyond lens[b], and everything when L <= 2048,
+    are left as NaN-free zeros."""
+    B, L = ik.shape[0], ik.shape[1]
+    need(iq, "iq", torch.float16, shape=(B, HI, DI))
+    need(ik, "ik", torch.float16, shape=(B, L, DI))
+    need(w, "w", torch.float32, shape=(B, HI))
+    lib = _lib.lib()
+    with torch.cuda.device(ik.device):
+        scores = torch.zeros(B, L, dtype=torch.float32, device=ik.device)
+        rc = lib.vmk_dsa_indexer(_lib.ptr(iq), _lib.ptr(ik), _lib.ptr(w), _lib.ptr(lens), _lib.ptr(scores), B, L,
+                                 _lib.ptr(_lib.status_word(ik.device)), torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "vmk_dsa_indexer")
+    return scores
+
+
+def select(scores, lens=None):
+    """Stage 2 alone: (idx (B,2048) int32 ascending, cnt (B,) int32)."""
+    need(scores, "scores", torch.float32, dims=2)
+    B, L = scores.shape
+    lib = _lib.lib()
+    with torch.cuda.device(scores.device):
+        idx = torch.empty(B, TOPK, dtype=torch.int32, device=scores.device)
+        cnt = torch.empty(B, dtype=torch.int32, device=scores.device)
+        rc = lib.vmk_dsa_select(_lib.ptr(scores), _lib.ptr(lens), _lib.ptr(idx), _lib.ptr(cnt), B, L,
+                                torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "vmk_dsa_select")
+    return idx, cnt
+
+
+def attend(q, kv, idx, cnt):
+    """Stage 3 alone: absorbed-MLA attention over given selections."""
+    B, L = kv.shape[0], kv.shape[1]
+    need(q, "q", torch.float16, shape=(B, H, DK))
+    need(kv, "kv", torch.float16, shape=(B, L, DK))
+    need(idx, "idx", torch.int32, shape=(B, TOPK))
+    need(cnt, "cnt", torch.int32, shape=(B,))
+    lib = _lib.lib()
+    dev = q.device
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream()
+        out = torch.empty(B, H, DC, dtype=torch.float16, device=dev)
+        ws = _lib.workspace(lib.vmk_dsa_attend_workspace_bytes(B), dev, stream.cuda_stream)
+        rc = lib.vmk_dsa_attend(_lib.ptr(q), _lib.ptr(kv), _lib.ptr(idx), _lib.ptr(cnt), _lib.ptr(out), B, L,
+                                _lib.ptr(ws), ws.numel(), _lib.ptr(_lib.status_word(dev)), stream.cuda_stream)
+    _lib.check(rc, "vmk_dsa_attend")
+    return out
