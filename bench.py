@@ -1,0 +1,371 @@
+"""Benchmark of the B200 decode kernels on the multi-GPU sweep workload.
+
+    python bench.py                                   # 1 GPU, dsa B=128 L=131072 (+ prefix / spec side lines)
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus 8 --steps 20 --warmup 3       # the same total workload sharded by request
+    python bench.py --impl reference                  # the float64 NumPy truth timed on the host cores
+
+A step is one pass of the op over the whole batch.  The headline op is `dsa` on the sweep configuration
+(batch 128, cache 131072): rows/s where a row is one request's complete output.  The batch is sharded
+by request across ranks with no collective on the data path (strong scaling: the total batch is fixed).
+Inputs are synthetic (seeded N(0,1) rounded to fp16, head weights N(0,1)/sqrt(64*128), as the op's
+generator draws them) and far larger than the 126 MB L2, so no flush is needed between steps.
+
+Rank 0 prints one JSON line.  `value` is timed with inputs resident in HBM; `e2e` is timed through the
+kernel module's public call with pinned HOST tensors (host->device copies and the device->host read of
+the result inside the timed region); `roofline` is for the dominant kernel (the indexer) from CUDA
+events inside this run; `cpu_baseline` is the float64 oracle on a bounded sample on the host cores."""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "dsa decode rows/s (batch 128, cache 131072)"
+UNIT = "rows/s"
+DSA = dict(B=128, L=131072)
+PREFIX = dict(N=256, P=32768, S=2048)
+SPEC = dict(B=4, L=32768, k=64)
+FALLBACK_HBM_GBS = 6650.0
+E2E_MAX = 32
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def ncu_traffic():
+    """DRAM bytes per indexer launch from the committed ncu capture (profiles/traffic.json), or None."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(path):
+        try:
+            return json.load(open(path))
+        except Exception:
+            return None
+    return None
+
+
+# ------------------------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active")
+                                                          for r in self.rows)]
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=reasons, samples=len(sm))
+
+
+# ------------------------------------------------------------------------------------------------ inputs
+def dsa_inputs(B, L, device, seed):
+    """Synthetic dsa inputs on the device with the generator's distributions (chunked to bound memory)."""
+    import torch
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+
+    def randn16(*shape):
+        out = torch.empty(*shape, dtype=torch.float16, device=device)
+        flat = out.view(-1)
+        step = 1 << 28
+        for i in range(0, flat.numel(), step):
+            n = min(step, flat.numel() - i)
+            flat[i:i + n] = torch.randn(n, generator=g, device=device, dtype=torch.float32).half()
+        return out
+
+    return dict(q=randn16(B, 128, 576), kv=randn16(B, L, 576), iq=randn16(B, 64, 128), ik=randn16(B, L, 128),
+                w=torch.randn(B, 64, generator=g, device=device, dtype=torch.float32) * (64 ** -0.5 * 128 ** -0.5),
+                lens=None)
+
+
+def timed_steps(fn, steps, warmup, dist, torch, sampler=None):
+    """W warm-up calls, then K timed calls between barrier + synchronize; returns (max-over-ranks seconds
+    for the K steps, per-step milliseconds on this rank)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    if sampler:
+        sampler.start()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    ev[0].record()
+    for i in range(steps):
+        fn()
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler else None
+    total_ms = ev[0].elapsed_time(ev[-1])
+    per = [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
+    if dist is not None:
+        t = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    return total_ms / 1e3, per, clocks
+
+
+def stage_times(inp, steps, torch):
+    """Average device time of each dsa stage (CUDA events on the launching stream), same inputs."""
+    from verified_metal_kernels_b200.kernels import dsa_b200
+    out = {}
+    scores = dsa_b200.indexer(inp["iq"], inp["ik"], inp["w"])
+    idx, cnt = dsa_b200.select(scores)
+    torch.cuda.synchronize()
+
+    def avg(fn):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps
+
+    from verified_metal_kernels_b200 import _lib
+    L = _lib.lib()
+    B, Lk = inp["ik"].shape[0], inp["ik"].shape[1]
+    st = torch.cuda.current_stream().cuda_stream
+    status = _lib.status_word(inp["ik"].device)
+    out["indexer_ms"] = avg(lambda: L.vmk_dsa_indexer(inp["iq"].data_ptr(), inp["ik"].data_ptr(), inp["w"].data_ptr(),
+                                                      None, scores.data_ptr(), B, Lk, status.data_ptr(), st))
+    out["select_ms"] = avg(lambda: L.vmk_dsa_select(scores.data_ptr(), None, idx.data_ptr(), cnt.data_ptr(), B, Lk, st))
+    out["attend_ms"] = avg(lambda: dsa_b200.attend(inp["q"], inp["kv"], idx, cnt))
+    return out
+
+
+def side_line(opname, torch, steps):
+    """rows/s and HBM fraction of the other two ops on their sweep / tree configurations (1 GPU)."""
+    from verified_metal_kernels_b200 import load_kernel, ops
+    op = ops.load_op(opname)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(1)
+    r16 = lambda *s: torch.randn(*s, generator=g, device="cuda", dtype=torch.float32).half()
+    if opname == "prefix":
+        N, P, S = PREFIX["N"], PREFIX["P"], PREFIX["S"]
+        slens = torch.randint(0, S + 1, (N,), generator=g, device="cuda", dtype=torch.int32)
+        inp = dict(q=r16(N, 32, 128), kp=r16(8, P, 128), vp=r16(8, P, 128), ks=r16(N, 8, S, 128), vs=r16(N, 8, S, 128),
+                   slens=slens)
+        nbytes = op.algorithmic_bytes(PREFIX, slens.cpu().numpy())
+        rows, name = N, f"prefix N={N} P={P} S~U[0,{S}]"
+        flops = 4.0 * N * 32 * 128 * (P + float(slens.float().mean()))
+    else:
+        B, L, kd = SPEC["B"], SPEC["L"], SPEC["k"]
+        rng = np.random.default_rng(0)
+        bits = op.pack_bits([op.tree_bits(kd, rng, 8) for _ in range(B)], kd)
+        inp = dict(q=r16(B, kd, 32, 128), k=r16(B, 8, L, 128), v=r16(B, 8, L, 128), bits=torch.from_numpy(bits).cuda())
+        nbytes = op.algorithmic_bytes(SPEC)
+        rows, name = B * kd, f"spec tree B={B} k={kd} L={L} depth<=8"
+        flops = 4.0 * B * kd * 32 * 128 * L
+    fn = load_kernel(opname)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    times = []
+    for i in range(steps + 3):
+        flush.fill_(i & 0xff)                     # evict the inputs from L2 between iterations
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn(**inp)
+        b.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            times.append(a.elapsed_time(b))
+    ms = statistics.median(times)
+    peak, kind = peaks()
+    return dict(workload=name, rows_per_s=rows / (ms * 1e-3), ms=ms, algorithmic_gb=nbytes / 1e9,
+                hbm_gbs=nbytes / (ms * 1e-3) / 1e9, hbm_frac=nbytes / (ms * 1e-3) / 1e9 / peak, peak=kind,
+                tflops=flops / (ms * 1e-3) / 1e12, l2="flushed between iterations")
+
+
+# ------------------------------------------------------------------------------------------------ CPU arm
+def cpu_sample(n_requests, L):
+    """Float64 oracle on `n_requests` requests of the dsa workload; returns (seconds, cores used)."""
+    from oracle import ref64
+    from verified_metal_kernels_b200 import ops
+    op = ops.load_op("dsa")
+    inp = op.make_inputs(dict(B=n_requests, L=L), seed=0)
+    t0 = time.perf_counter()
+    ref64.dsa_ref64(inp["q"], inp["kv"], inp["iq"], inp["ik"], inp["w"], None)
+    return time.perf_counter() - t0
+
+
+def host_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def reference_arm(a):
+    """The reference's CPU implementation of the path: its float64 NumPy truth, restated in oracle/ (the
+    reference is a Python package that cannot travel to the GPU box).  One request per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    for _ in range(min(a.warmup, 1)):
+        cpu_sample(1, DSA["L"])
+    t = [cpu_sample(1, DSA["L"]) for _ in range(a.steps)]
+    sec = sum(t) / len(t)
+    v = 1.0 / sec
+    line = dict(metric=METRIC, value=v, unit=UNIT, impl="reference", n_gpus=a.gpus, steps=a.steps, warmup=min(a.warmup, 1),
+                ms_per_step=sec * 1e3, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f64",
+                data="synthetic", config=dict(workload="dsa B=128 L=131072 (sample: 1 request per step)"),
+                cpu_baseline=dict(value=v, unit=UNIT, cores=host_cores(), kind="port",
+                                  sample="1 of 128 requests (B=1, L=131072) per step, NumPy float64, BLAS threads"),
+                e2e=dict(value=v, unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
+    print(json.dumps(line))
+    return 0
+
+
+# ------------------------------------------------------------------------------------------------ main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=DSA["B"], help="total dsa batch (default: the sweep's 128)")
+    ap.add_argument("--cache", type=int, default=DSA["L"], help="dsa cache length (default: the sweep's 131072)")
+    ap.add_argument("--no-side", action="store_true", help="skip the prefix / spec side lines")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    a = ap.parse_args()
+    a.warmup = max(a.warmup, 3) if a.impl == "ours" else a.warmup
+    if a.impl == "reference":
+        return reference_arm(a)
+
+    import torch
+    from verified_metal_kernels_b200 import _lib, build, load_kernel, ops, shard
+    rank, local_rank, world = shard.world()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU path")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    build.build()
+    fn = load_kernel("dsa")
+    op = ops.load_op("dsa")
+    B, L = a.batch, a.cache
+    lo, hi = shard.unit_range(B, rank, world)
+    Bl = hi - lo
+    inp = dsa_inputs(max(Bl, 1), L, "cuda", seed=1000 + rank)
+    run = (lambda: fn(**inp)) if Bl > 0 else (lambda: None)
+
+    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+    sec, per, clocks = timed_steps(run, a.steps, a.warmup, dist, torch, sampler)
+    status = _lib.read_status(torch.device("cuda", torch.cuda.current_device()))
+    value = B * a.steps / sec
+
+    # end to end: pinned host tensors in, host tensor out, through the public kernel(...) call
+    e2e = None
+    if not a.no_e2e:
+        # Pinned host copies of (a bounded slice of) this rank's batch: at most E2E_MAX requests per call, so
+        # that host memory and the pinning time stay modest; rows/s is per-request work either way.
+        Be = min(max(Bl, 1), E2E_MAX)
+        host = {}
+        for k, v in inp.items():
+            if v is not None:
+                host[k] = torch.empty(v[:Be].shape, dtype=v.dtype, pin_memory=True)
+                host[k].copy_(v[:Be])
+            else:
+                host[k] = None
+        torch.cuda.synchronize()
+        h2d = sum(v.numel() * v.element_size() for v in host.values() if v is not None)
+        d2h = Be * 128 * 512 * 2
+        e_steps = min(a.steps, 5)
+        run_h = (lambda: fn(**host)) if Bl > 0 else (lambda: None)
+        esec, _, _ = timed_steps(run_h, e_steps, 1, dist, torch)
+        e_rows = Be * world if Bl > 0 else 0
+        e2e = dict(value=e_rows * e_steps / esec, unit=UNIT, h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
+                   steps=e_steps, sample=f"{Be} requests per call per rank (of {Bl}), pinned host tensors in, host tensor out")
+        del host
+
+    launches = 3 + (1 if _lib.lib().vmk_dsa_attend_workspace_bytes(max(Bl, 1)) > 256 else 0)
+    line = dict(metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=a.steps, warmup=a.warmup,
+                ms_per_step=sec * 1e3 / a.steps, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f16",
+                data="synthetic",
+                config=dict(workload=f"dsa B={B} L={L} (8-GPU sweep configuration)", parallelism=f"batch-sharded x{world}",
+                            per_rank_batch=Bl, l2="inputs (GBs per rank) far larger than the 126 MB L2; no flush"),
+                clocks=clocks, e2e=e2e, gpu_launches=launches * a.steps, device_status=status)
+
+    if rank == 0:
+        st = stage_times(inp, min(a.steps, 10), torch)
+        peak, kind = peaks()
+        alg = Bl * L * 128 * 2                       # the ik stream: every byte once
+        ach = alg / (st["indexer_ms"] * 1e-3) / 1e9
+        tr = ncu_traffic()
+        line["roofline"] = dict(kernel="dsa indexer", bound="hbm", achieved=ach, peak=peak, unit="GB/s", frac=ach / peak,
+                                peak_source=f"of {kind}", traffic=(tr or {}).get("indexer_bytes_per_launch"),
+                                algorithmic_bytes=alg, launch_ms=st["indexer_ms"])
+        total_alg = op.algorithmic_bytes(dict(B=Bl, L=L))
+        line["stages_ms"] = st
+        line["op_hbm"] = dict(algorithmic_bytes=total_alg, gbs=total_alg / (sec / a.steps) / 1e9,
+                              frac=total_alg / (sec / a.steps) / 1e9 / peak)
+        if not a.no_side and world == 1:
+            del inp
+            torch.cuda.empty_cache()
+            line["ops"] = dict(prefix=side_line("prefix", torch, 10), spec=side_line("spec", torch, 10))
+        if not a.no_cpu and world == 1:
+            n = 2
+            t = cpu_sample(n, L)
+            line["cpu_baseline"] = dict(value=n / t, unit=UNIT, cores=host_cores(), kind="port",
+                                        sample=f"{n} of {B} requests (L={L}), float64 NumPy oracle, {t:.1f} s")
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,76 @@
+"""The C-ABI library without a GPU: it loads, exports every symbol the header declares, and answers
+the host-only entry points (sizes, error strings, argument validation that precedes any launch)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from verified_metal_kernels_b200 import _lib, build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    build.build()
+    return _lib.lib()
+
+
+def header_symbols():
+    text = open(os.path.join(ROOT, "include", "vmk_b200.h")).read()
+    return sorted(set(re.findall(r"VMK_API[^;]*?\b(vmk_\w+)\s*\(", text)))
+
+
+def test_header_and_binding_agree(lib):
+    syms = header_symbols()
+    assert len(syms) >= 14
+    assert sorted(_lib.SIGNATURES) == syms
+    raw = ctypes.CDLL(_lib.LIB_PATH)
+    for s in syms:
+        assert hasattr(raw, s), f"{s} declared in include/vmk_b200.h but not exported"
+
+
+def test_every_declaration_cites_the_reference():
+    text = open(os.path.join(ROOT, "include", "vmk_b200.h")).read()
+    assert text.count("kernels/") >= 6 and "verify.py:" in text
+
+
+def test_version_and_error_strings(lib):
+    assert lib.vmk_version() >= 100
+    seen = {_lib.error_string(c) for c in (0, -1, -2, -3, -4, -5)}
+    assert len(seen) == 6 and "unknown" not in " ".join(seen)
+    assert "unknown" in _lib.error_string(-99)
+
+
+def test_workspace_sizes(lib):
+    assert lib.vmk_prefix_workspace_bytes(8, 32, 8, 128, 4096, 256) > 0
+    assert lib.vmk_prefix_workspace_bytes(8, 32, 8, 64, 4096, 256) == 0       # D != 128
+    assert lib.vmk_prefix_workspace_bytes(8, 32, 7, 128, 4096, 256) == 0       # Hq % Hkv
+    assert lib.vmk_spec_workspace_bytes(4, 64, 32, 8, 128, 32768) > 0
+    a, b = lib.vmk_dsa_workspace_bytes(8, 32768), lib.vmk_dsa_workspace_bytes(8, 65536)
+    assert b - a == 8 * 32768 * 4                                               # fp32 scores grow with L
+    assert lib.vmk_dsa_workspace_bytes(0, 10) == 0
+    big = lib.vmk_prefix_workspace_bytes(256, 32, 8, 128, 32768, 2048)
+    assert 0 < big < 2 << 30
+
+
+def test_bad_arguments_are_rejected_before_any_launch(lib):
+    assert lib.vmk_prefix_decode(None, None, None, None, None, None, None, 1, 32, 8, 128, 8, 8, None, 0, None, None) == -1
+    assert lib.vmk_spec_verify(None, None, None, None, 1, None, 1, 4, 32, 8, 128, 64, None, 0, None, None) == -1
+    assert lib.vmk_dsa_decode(None, None, None, None, None, None, None, None, None, 1, 64, None, 0, None, None) == -1
+    assert lib.vmk_dsa_select(None, None, None, None, 1, 64, None) == -1
+    assert lib.vmk_lse_merge(None, None, None, 2, 4, 128, None, None) == -1
+    # misaligned pointer
+    assert lib.vmk_prefix_decode(8, 16, 16, 16, 16, None, 16, 1, 32, 8, 128, 8, 8, 256, 1 << 20, None, None) == -1
+
+
+def test_kernel_modules_refuse_cpu_only_use():
+    import numpy as np
+    import torch
+    from verified_metal_kernels_b200 import load_kernel, ops
+    if torch.cuda.is_available():
+        pytest.skip("GPU present")
+    inp = ops.load_op("spec").make_inputs(dict(B=1, L=16, k=2), seed=0)
+    with pytest.raises((RuntimeError, ValueError, AssertionError)):
+        load_kernel("spec")(**ops.to_torch(inp, "cpu"))
