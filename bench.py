@@ -62,42 +62,73 @@ def ncu_traffic():
 
 # ------------------------------------------------------------------------------------------------ clocks
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
-    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) every few milliseconds
+    while the timed region runs; falls back to polling nvidia-smi when NVML cannot be loaded."""
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
-    def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index, period=0.005):
+        self.index, self.period, self.rows, self.stop_flag, self.thread = index, period, [], False, None
+        self.max_mhz, self.err = None, None
+
+    def _loop_nvml(self):
+        import pynvml as nv
+        nv.nvmlInit()
+        h = nv.nvmlDeviceGetHandleByIndex(self.index)
+        self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+        while not self.stop_flag:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                try:
+                    rs = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                except Exception:
+                    rs = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                self.rows.append((time.perf_counter(), float(mhz), int(rs)))
+            except Exception as e:          # keep sampling; report the last error
+                self.err = repr(e)
+            time.sleep(self.period)
+
+    def _loop_smi(self):
+        q = "clocks.sm,clocks.max.sm,clocks_event_reasons.active"
+        while not self.stop_flag:
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={q}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                f = [x.strip() for x in out.strip().split(",")]
+                self.max_mhz = float(f[1])
+                self.rows.append((time.perf_counter(), float(f[0]), int(f[2], 16)))
+            except Exception as e:
+                self.err = repr(e)
+                time.sleep(0.05)
+
+    def _loop(self):
+        try:
+            self._loop_nvml()
+        except Exception as e:
+            self.err = repr(e)
+            self._loop_smi()
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except Exception:
-            self.proc = None
+        self.thread = threading.Thread(target=self._loop, daemon=True)
+        self.thread.start()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+    def mark(self):
+        return time.perf_counter()
 
-    def stop(self):
-        if self.proc is None:
-            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active")
-                                                          for r in self.rows)]
-        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
-                    reasons=reasons, samples=len(sm))
+    def stop(self, t0=None, t1=None):
+        self.stop_flag = True
+        if self.thread is not None:
+            self.thread.join(timeout=10)
+        rows = [r for r in self.rows if (t0 is None or r[0] >= t0) and (t1 is None or r[0] <= t1)]
+        window = "timed region"
+        if len(rows) < 3:                       # region shorter than a few samples: widen to the loaded period
+            rows, window = self.rows, "warm-up + timed region"
+        bits = 0
+        for r in rows:
+            bits |= r[2]
+        sm = [r[1] for r in rows]
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=self.max_mhz,
+                    reasons=[n for b, n in self.REASONS.items() if bits & b], samples=len(sm), window=window,
+                    sampler_error=self.err)
 
 
 # ------------------------------------------------------------------------------------------------ inputs
@@ -124,14 +155,15 @@ def dsa_inputs(B, L, device, seed):
 def timed_steps(fn, steps, warmup, dist, torch, sampler=None):
     """W warm-up calls, then K timed calls between barrier + synchronize; returns (max-over-ranks seconds
     for the K steps, per-step milliseconds on this rank)."""
+    if sampler:
+        sampler.start()
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
-    if sampler:
-        sampler.start()
+    t_begin = time.perf_counter()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
     ev[0].record()
     for i in range(steps):
@@ -141,7 +173,7 @@ def timed_steps(fn, steps, warmup, dist, torch, sampler=None):
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
-    clocks = sampler.stop() if sampler else None
+    clocks = sampler.stop(t_begin, time.perf_counter()) if sampler else None
     total_ms = ev[0].elapsed_time(ev[-1])
     per = [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
     if dist is not None:

@@ -1,0 +1,46 @@
+"""The tcgen05 / tensor-memory indexer against the float64 scores and against the mma.sync variant."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import judge, ref64
+from tests import _verify
+from verified_metal_kernels_b200 import load_kernel, ops
+from verified_metal_kernels_b200.kernels import dsa_b200
+
+pytestmark = pytest.mark.gpu
+op = ops.load_op("dsa")
+
+
+@pytest.fixture(autouse=True)
+def _variant():
+    dsa_b200.set_indexer_variant("tcgen05")
+    yield
+    dsa_b200.set_indexer_variant("mma")
+
+
+@pytest.mark.parametrize("B,L", [(1, 2049), (2, 4096), (3, 10007), (1, 65536), (5, 40000)])
+def test_scores(B, L):
+    inp = op.make_inputs(dict(B=B, L=L), seed=23)
+    d = _verify.device_inputs("dsa", inp)
+    s = dsa_b200.indexer(d["iq"], d["ik"], d["w"]).cpu().numpy().astype(np.float64)
+    _verify.assert_clean_status()
+    s64 = ref64.dsa_scores64(inp["iq"], inp["ik"], inp["w"])
+    assert np.abs(s - s64).max() <= 2e-6 * np.abs(s64).max()
+    dsa_b200.set_indexer_variant("mma")
+    s0 = dsa_b200.indexer(d["iq"], d["ik"], d["w"]).cpu().numpy().astype(np.float64)
+    assert np.abs(s - s0).max() <= 2e-6 * np.abs(s64).max()
+
+
+def test_ragged_and_full_op():
+    inp = op.make_inputs(dict(B=3, L=9000), seed=12, dist="ragged")
+    out, res, _ = _verify.run_kernel(load_kernel("dsa"), "dsa", inp, return_selection=True)
+    _verify.assert_clean_status()
+    _, idx, cnt = res
+    idx, cnt = idx.cpu().numpy(), cnt.cpu().numpy()
+    s64 = ref64.dsa_scores64(inp["iq"], inp["ik"], inp["w"])
+    for b in range(3):
+        assert judge.select_check(idx[b], cnt[b], s64[b], int(inp["lens"][b]))["ok"]
+    sel = [idx[b, :cnt[b]].astype(np.int64) for b in range(3)]
+    t = ref64.dsa_ref64(inp["q"], inp["kv"], inp["iq"], inp["ik"], inp["w"], inp["lens"], sel=sel)
+    assert judge.judge_l2(out, t, half=True)["ok"]

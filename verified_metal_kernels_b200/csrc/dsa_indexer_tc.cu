@@ -1,12 +1,254 @@
-// `dsa` stage 1 on the 5th-generation tensor cores (tcgen05 + TMEM).  Placeholder until the kernel
-// lands: the entry reports the variant as unsupported so that callers fall back to nothing silently.
+// `dsa` stage 1 on the 5th-generation tensor cores: scores[b,l] = sum_h w[b,h] * relu(iq[b,h] . ik[b,l]).
+//
+// Per 128-position tile the product T = ik_tile (128 x 128, K-major) . iq^T (64 x 128, K-major) is one
+// tcgen05 accumulator of 128 lanes x 64 fp32 columns in tensor memory.  A CTA owns a contiguous run of
+// tiles of one request and is warp-specialised:
+//   warp 0     TMA producer: 32 KiB ik tiles into a 6-deep shared-memory ring (128-byte swizzle)
+//   warp 1     allocates tensor memory, issues 8 tcgen05.mma (M128 N64 K16) per tile into one of four
+//              accumulator buffers, commits the ring slot back to the producer and the accumulator
+//              to the epilogue
+//   warps 2-5  epilogue: tcgen05.ld of their 32 lanes x 64 columns, fp32 ReLU and head-weighted sum,
+//              one coalesced fp32 score per position
+// Every mbarrier wait is bounded; a wait that runs out sets the status word and the CTA winds down
+// through the common exit, where the allocating warp frees its tensor memory.
 #include "common.cuh"
 
 namespace vmk {
 
-int indexer_tc_launch(const CUtensorMap&, const CUtensorMap&, const float*, const int32_t*, float*, int, int, int32_t*,
-                      cudaStream_t) {
-  return VMK_E_UNSUPPORTED;
+constexpr int kTopK = VMK_DSA_TOPK;
+constexpr int kHI = 64, kDI = 128;
+constexpr int kTile = 128;
+constexpr int kStages = 6;
+constexpr int kAccs = 4;                               // accumulator buffers of 64 columns
+constexpr int kTileBytes = kTile * kDI * 2;            // 32 KiB
+constexpr int kIqBytes = kHI * kDI * 2;                // 16 KiB
+constexpr int kTmemCols = kAccs * kHI;                 // 256
+constexpr int kTcThreads = 192;
+// ring | iq | w | barriers | tmem base
+constexpr int kTcSmem = kStages * kTileBytes + kIqBytes + kHI * 4 + (2 * kStages + 2 * kAccs + 1) * 8 + 16 + 1024;
+
+struct TcParams {
+  CUtensorMap tmIK;      // (B, L, 128) box (64, 128, 1), 128-byte swizzle
+  CUtensorMap tmIQ;      // (B, 64, 128) box (64, 64, 1)
+  const float* w;
+  const int32_t* lens;
+  float* scores;
+  int B, L;
+  int32_t* status;
+};
+
+// Shared-memory matrix descriptor of a K-major operand tile stored as [rows][64 fp16] with the
+// 128-byte swizzle (what TMA writes): 8-row groups 1024 bytes apart, descriptor version 1, layout
+// SWIZZLE_128B.  Advancing along K inside the 128-byte row adds the byte offset to the start address.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);          // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                              // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset: 8 rows x 128 B
+  d |= (uint64_t)1 << 46;                              // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                              // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor: fp16 A and B (both K-major), fp32 accumulate, M = 128, N = 64.
+constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(kHI >> 3) << 17) | ((uint32_t)(kTile >> 4) << 24);
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread (thread = lane)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float relu_nan(float x) { return (x < 0.f) ? 0.f : x; }
+
+__global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_constant__ TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sIQ = smem + kStages * kTileBytes;
+  float* sW = reinterpret_cast<float*>(sIQ + kIqBytes);
+  uint64_t* full = reinterpret_cast<uint64_t*>(sW + kHI);
+  uint64_t* empty = full + kStages;
+  uint64_t* acc_full = empty + kStages;
+  uint64_t* acc_empty = acc_full + kAccs;
+  uint64_t* iq_full = acc_empty + kAccs;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(iq_full + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b = blockIdx.y;
+  int n = p.L;
+  if (p.lens != nullptr) n = max(0, min(p.lens[b], p.L));
+  if (n <= kTopK) return;                                   // uniform: nothing to rank for this request
+  const int tiles = (n + kTile - 1) / kTile;
+  const int per = (tiles + gridDim.x - 1) / gridDim.x;
+  const int t0 = blockIdx.x * per;
+  const int t1 = min(tiles, t0 + per);
+  if (t0 >= t1) return;                                     // uniform
+  const int nt = t1 - t0;
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < kAccs; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);
+    }
+    mbar_init(iq_full, 1);
+    fence_mbar_init();
+  }
+  if (tid < kHI) sW[tid] = p.w[b * kHI + tid];
+  if (warp == 1) {
+    __syncwarp();
+    // one full warp allocates 256 columns of tensor memory; the base address lands in shared memory
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  bool timed_out = false;
+  if (warp == 0) {
+    // ---------------------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(iq_full, kIqBytes);
+      tma_load_3d(sIQ, &p.tmIQ, 0, 0, b, iq_full);
+      tma_load_3d(sIQ + kIqBytes / 2, &p.tmIQ, 64, 0, b, iq_full);
+      for (int j = 0; j < nt; ++j) {
+        const int s = j % kStages;
+        if (j >= kStages && !mbar_wait(&empty[s], (uint32_t)(((j / kStages) - 1) & 1))) {
+          timed_out = true;
+          break;
+        }
+        uint8_t* st = smem + s * kTileBytes;
+        mbar_expect_tx(&full[s], kTileBytes);
+        tma_load_3d(st, &p.tmIK, 0, (t0 + j) * kTile, b, &full[s]);
+        tma_load_3d(st + kTileBytes / 2, &p.tmIK, 64, (t0 + j) * kTile, b, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      if (!mbar_wait(iq_full, 0)) timed_out = true;
+      const uint32_t iq_addr = smem_u32(sIQ);
+      for (int j = 0; j < nt && !timed_out; ++j) {
+        const int s = j % kStages, a = j % kAccs;
+        if (j >= kAccs && !mbar_wait(&acc_empty[a], (uint32_t)(((j / kAccs) - 1) & 1))) {
+          timed_out = true;
+          break;
+        }
+        if (!mbar_wait(&full[s], (uint32_t)((j / kStages) & 1))) {
+          timed_out = true;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + s * kTileBytes);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(a * kHI);
+#pragma unroll
+        for (int k = 0; k < kDI / 16; ++k) {
+          // K step k: 64-element half (k / 4), 32-byte offset (k % 4) inside the 128-byte swizzled row
+          const uint64_t da = umma_desc_sw128(a_addr + (k >> 2) * (kTileBytes / 2) + (k & 3) * 32);
+          const uint64_t db = umma_desc_sw128(iq_addr + (k >> 2) * (kIqBytes / 2) + (k & 3) * 32);
+          umma_f16(d_tmem, da, db, kIdesc, k > 0 ? 1u : 0u);
+        }
+        umma_commit(&empty[s]);        // the ring slot may be refilled once these MMAs have read it
+        umma_commit(&acc_full[a]);     // the accumulator is complete
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------------------- epilogue (warps 2..5)
+    const int quarter = warp & 3;                         // tensor-memory lanes [32 q, 32 q + 32)
+    const int row = quarter * 32 + lane;                  // position inside the tile
+    float* dst = p.scores + (size_t)b * p.L;
+    for (int j = 0; j < nt; ++j) {
+      const int a = j % kAccs;
+      const bool ok = mbar_wait(&acc_full[a], (uint32_t)((j / kAccs) & 1));
+      if (!__all_sync(0xffffffffu, ok)) {
+        timed_out = true;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * kHI);
+      uint32_t r0[32], r1[32];
+      tmem_ld32(taddr, r0);
+      tmem_ld32(taddr + 32, r1);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[a]);          // this warp's quarter has been read out
+      float s = 0.f;
+#pragma unroll
+      for (int h = 0; h < 32; ++h) s += sW[h] * relu_nan(__uint_as_float(r0[h]));
+#pragma unroll
+      for (int h = 0; h < 32; ++h) s += sW[32 + h] * relu_nan(__uint_as_float(r1[h]));
+      const int pos = (t0 + j) * kTile + row;
+      if (pos < n) dst[pos] = s;
+    }
+  }
+  if (timed_out) report(p.status, kStatusTimeout);
+
+  // common exit: every warp arrives here, then the allocating warp frees the tensor memory
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
+                 : "memory");
+  }
+}
+
+int indexer_chunks(int B, int tiles);
+
+int indexer_tc_launch(const CUtensorMap& tmIK, const CUtensorMap& tmIQ, const float* w, const int32_t* lens,
+                      float* scores, int B, int L, int32_t* status, cudaStream_t stream) {
+  TcParams p;
+  memset(&p, 0, sizeof(p));
+  p.tmIK = tmIK;
+  p.tmIQ = tmIQ;
+  p.w = w; p.lens = lens; p.scores = scores; p.B = B; p.L = L; p.status = status;
+  static int configured_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (configured_dev != dev) {
+    cudaError_t e = cudaFuncSetAttribute(indexer_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem);
+    if (e != cudaSuccess) return check_launch(e);
+    configured_dev = dev;
+  }
+  const int chunks = indexer_chunks(B, cdiv(L, kTile));
+  indexer_tc_kernel<<<dim3(chunks, B), kTcThreads, kTcSmem, stream>>>(p);
+  return check_launch(cudaGetLastError());
 }
 
 }  // namespace vmk

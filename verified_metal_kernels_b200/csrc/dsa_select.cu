@@ -14,7 +14,7 @@ constexpr int kSelThreads = 1024;
 
 __device__ __forceinline__ uint32_t score_key(float x) {
   if (x != x) return 0u;                       // NaN: never preferred
-  const uint32_t u = __float_as_uint(x);
+  const uint32_t u = __float_as_uint(x + 0.0f);   // -0.0 and +0.0 compare equal, so they share a key
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 

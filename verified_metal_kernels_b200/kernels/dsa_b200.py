@@ -98,3 +98,9 @@ def attend(q, kv, idx, cnt):
                                 _lib.ptr(ws), ws.numel(), _lib.ptr(_lib.status_word(dev)), stream.cuda_stream)
     _lib.check(rc, "vmk_dsa_attend")
     return out
+
+
+def set_indexer_variant(name):
+    """Chooses the stage-1 implementation: "mma" (mma.sync, warp-level) or "tcgen05" (tensor memory)."""
+    rc = _lib.lib().vmk_dsa_set_indexer_variant({"mma": 0, "tcgen05": 1}[name])
+    _lib.check(rc, "vmk_dsa_set_indexer_variant")
