@@ -1,4 +1,5 @@
-"""The tcgen05 / tensor-memory indexer against the float64 scores and against the mma.sync variant."""
+"""The two stage-1 implementations of `dsa` (tcgen05 + tensor memory, the default; warp-level mma.sync)
+against the float64 scores and against each other."""
 import numpy as np
 import pytest
 import torch
@@ -16,7 +17,7 @@ op = ops.load_op("dsa")
 def _variant():
     dsa_b200.set_indexer_variant("tcgen05")
     yield
-    dsa_b200.set_indexer_variant("mma")
+    dsa_b200.set_indexer_variant("tcgen05")
 
 
 @pytest.mark.parametrize("B,L", [(1, 2049), (2, 4096), (3, 10007), (1, 65536), (5, 40000)])
@@ -29,10 +30,14 @@ def test_scores(B, L):
     assert np.abs(s - s64).max() <= 2e-6 * np.abs(s64).max()
     dsa_b200.set_indexer_variant("mma")
     s0 = dsa_b200.indexer(d["iq"], d["ik"], d["w"]).cpu().numpy().astype(np.float64)
+    _verify.assert_clean_status()
+    assert np.abs(s0 - s64).max() <= 2e-6 * np.abs(s64).max()
     assert np.abs(s - s0).max() <= 2e-6 * np.abs(s64).max()
 
 
-def test_ragged_and_full_op():
+@pytest.mark.parametrize("variant", ["tcgen05", "mma"])
+def test_ragged_and_full_op(variant):
+    dsa_b200.set_indexer_variant(variant)
     inp = op.make_inputs(dict(B=3, L=9000), seed=12, dist="ragged")
     out, res, _ = _verify.run_kernel(load_kernel("dsa"), "dsa", inp, return_selection=True)
     _verify.assert_clean_status()

@@ -514,7 +514,7 @@ static int attend_impl(const void* q, const void* kv, const int32_t* idx, const 
   return check_launch(cudaGetLastError());
 }
 
-static int g_indexer_variant = 0;   // 0 = mma.sync, 1 = tcgen05
+static int g_indexer_variant = 1;   // 0 = mma.sync (warp-level), 1 = tcgen05 + tensor memory (default)
 
 }  // namespace vmk
 

@@ -11,7 +11,7 @@
 //              one coalesced fp32 score per position
 // Every mbarrier wait is bounded; a wait that runs out sets the status word and the CTA winds down
 // through the common exit, where the allocating warp frees its tensor memory.
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace vmk {
 
@@ -37,54 +37,8 @@ struct TcParams {
   int32_t* status;
 };
 
-// Shared-memory matrix descriptor of a K-major operand tile stored as [rows][64 fp16] with the
-// 128-byte swizzle (what TMA writes): 8-row groups 1024 bytes apart, descriptor version 1, layout
-// SWIZZLE_128B.  Advancing along K inside the 128-byte row adds the byte offset to the start address.
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);          // start address, 16-byte units
-  d |= (uint64_t)1 << 16;                              // leading byte offset (unused with swizzle)
-  d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset: 8 rows x 128 B
-  d |= (uint64_t)1 << 46;                              // descriptor version (sm_100)
-  d |= (uint64_t)2 << 61;                              // SWIZZLE_128B
-  return d;
-}
-
 // Instruction descriptor: fp16 A and B (both K-major), fp32 accumulate, M = 128, N = 64.
-constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(kHI >> 3) << 17) | ((uint32_t)(kTile >> 4) << 24);
-
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-      "}\n" ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread (thread = lane)
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+constexpr uint32_t kIdesc = umma_idesc_f16(kTile, kHI, 0);
 
 __device__ __forceinline__ float relu_nan(float x) { return (x < 0.f) ? 0.f : x; }
 
@@ -125,14 +79,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
     fence_mbar_init();
   }
   if (tid < kHI) sW[tid] = p.w[b * kHI + tid];
-  if (warp == 1) {
-    __syncwarp();
-    // one full warp allocates 256 columns of tensor memory; the base address lands in shared memory
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"((uint32_t)kTmemCols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
+  if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -222,10 +169,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
-    __syncwarp();
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
-                 : "memory");
+    tmem_free(tmem_base, kTmemCols);
   }
 }
 
