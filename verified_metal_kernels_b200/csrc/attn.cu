@@ -105,7 +105,14 @@ __global__ void __launch_bounds__(128) lse_merge_kernel(const float* __restrict_
 // ------------------------------------------------------------------------------------------------
 // planning
 // ------------------------------------------------------------------------------------------------
+int launch_attn_tc(const AttnParams& p, int n_cta, cudaStream_t stream);   // attn_tc.cu
+
+static int g_attn_tc = 1;   // 1: row tiles of 128 run on tcgen05 (attn_tc.cu); 0: always the warp-level kernel
+constexpr int kTcRowsMin = 65;     // stacked rows from which the tensor-memory kernel is used
+constexpr int kTcSplitCap = 16;
+
 struct RolePlan {
+  bool tc;                 // tcgen05 kernel (128-row tiles, 128-key blocks)
   int rt, ks;              // warp layout of the role's CTAs
   int row_tiles, MP;
   int nsplit, split_len;
@@ -123,7 +130,32 @@ static void pick_layout(int rows, int* rt, int* ks) {
 }
 
 // Splits the keys of each (group, row tile) so that about `target` CTAs exist, in multiples of 64 keys.
+// tcgen05 path: one CTA per SM, 128-key blocks.  The split count minimises waves x (blocks per CTA +
+// a fixed per-CTA overhead of about three blocks), which avoids a mostly empty last wave.
+static void plan_role_tc(RolePlan* r, int groups, int rows, int keys) {
+  r->tc = true;
+  r->rt = 8; r->ks = 1;
+  r->row_tiles = cdiv(rows, 128);
+  r->MP = r->row_tiles * 128;
+  const int units = groups * r->row_tiles;
+  const int blocks = cdiv(keys > 0 ? keys : 1, 128);
+  const int sms = sm_count();
+  long long best_cost = -1;
+  int best = 1;
+  for (int ns = 1; ns <= kTcSplitCap && ns <= blocks; ++ns) {
+    const int per = cdiv(blocks, ns);
+    const int real = cdiv(blocks, per);
+    const long long cost = (long long)cdiv(units * real, sms) * (per + 3);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = real; }
+  }
+  r->split_len = cdiv(blocks, best) * 128;
+  r->nsplit = cdiv(blocks * 128, r->split_len);
+  r->n_cta = units * r->nsplit;
+}
+
 static void plan_role(RolePlan* r, int groups, int rows, int keys, int target, bool fixed_small) {
+  r->tc = false;
+  if (!fixed_small && g_attn_tc && rows >= kTcRowsMin) { plan_role_tc(r, groups, rows, keys); return; }
   if (fixed_small) { r->rt = 1; r->ks = 4; } else pick_layout(rows, &r->rt, &r->ks);
   const int mt = r->rt * 16;
   r->row_tiles = cdiv(rows, mt);
@@ -174,7 +206,7 @@ static PrefixPlan plan_prefix(int N, int Hq, int Hkv, int P, int S, int key_lo, 
   int target_a = 2 * sms - target_b;
   if (target_a < sms) target_a = sms;
   plan_role(&pl.a, Hkv, N * G, key_hi - key_lo, target_a, false);
-  size_t off = place(&pl.a, Hkv, 0, cdiv(2 * sms, Hkv * pl.a.row_tiles));
+  size_t off = place(&pl.a, Hkv, 0, pl.a.tc ? kTcSplitCap : cdiv(2 * sms, Hkv * pl.a.row_tiles));
   if (pl.has_b) off = place(&pl.b, N * Hkv, off, pl.b.nsplit);
   pl.ws_bytes = align_up(off, 256);
   return pl;
@@ -189,7 +221,8 @@ static SpecPlan plan_spec(int B, int kd, int Hq, int Hkv, int key_lo, int key_hi
   SpecPlan pl;
   const int G = Hq / Hkv;
   plan_role(&pl.a, B * Hkv, kd * G, key_hi - key_lo, 2 * sm_count(), false);
-  pl.ws_bytes = align_up(place(&pl.a, B * Hkv, 0, cdiv(2 * sm_count(), B * Hkv * pl.a.row_tiles)), 256);
+  pl.ws_bytes = align_up(place(&pl.a, B * Hkv, 0, pl.a.tc ? kTcSplitCap
+                                                               : cdiv(2 * sm_count(), B * Hkv * pl.a.row_tiles)), 256);
   return pl;
 }
 
@@ -257,9 +290,10 @@ static int prefix_impl(const void* q, const void* kp, const void* vp, const void
   memset(&p, 0, sizeof(p));
   p.sc = kLog2e / sqrtf((float)D);
   p.status = status;
-  int rc = make_tmap_3d(&p.a.tmK, kp, D, P, Hkv, 64, kBK);
+  const uint32_t box_a = pl.a.tc ? 128 : kBK;
+  int rc = make_tmap_3d(&p.a.tmK, kp, D, P, Hkv, 64, box_a);
   if (rc) return rc;
-  rc = make_tmap_3d(&p.a.tmV, vp, D, P, Hkv, 64, kBK);
+  rc = make_tmap_3d(&p.a.tmV, vp, D, P, Hkv, 64, box_a);
   if (rc) return rc;
   p.a.q = static_cast<const __half*>(q);
   p.a.n_groups = Hkv; p.a.Hkv = Hkv; p.a.G = G; p.a.Hq = Hq;
@@ -279,9 +313,18 @@ static int prefix_impl(const void* q, const void* kp, const void* vp, const void
     p.b.klen = S; p.b.key_lo = 0; p.b.key_hi = S;
     p.b.mask_start = INT_MAX;
     fill_role(&p.b, pl.b, static_cast<uint8_t*>(ws));
-    rc = launch_attn<true>(p, pl.a.rt, pl.a.n_cta + pl.b.n_cta, stream);
+    if (pl.a.tc) {
+      // shared prefix on the tensor-memory kernel, private suffixes on the warp-level kernel
+      rc = launch_attn_tc(p, pl.a.n_cta, stream);
+      if (rc) return rc;
+      AttnParams ps = p;
+      ps.a = p.b;
+      rc = launch_attn<false>(ps, 1, pl.b.n_cta, stream);
+    } else {
+      rc = launch_attn<true>(p, pl.a.rt, pl.a.n_cta + pl.b.n_cta, stream);
+    }
   } else {
-    rc = launch_attn<false>(p, pl.a.rt, pl.a.n_cta, stream);
+    rc = pl.a.tc ? launch_attn_tc(p, pl.a.n_cta, stream) : launch_attn<false>(p, pl.a.rt, pl.a.n_cta, stream);
   }
   if (rc) return rc;
 
@@ -316,9 +359,10 @@ static int spec_impl(const void* q, const void* k, const void* v, const uint32_t
   memset(&p, 0, sizeof(p));
   p.sc = kLog2e / sqrtf((float)D);
   p.status = status;
-  int rc = make_tmap_3d(&p.a.tmK, k, D, L, (uint64_t)B * Hkv, 64, kBK);
+  const uint32_t box_a = pl.a.tc ? 128 : kBK;
+  int rc = make_tmap_3d(&p.a.tmK, k, D, L, (uint64_t)B * Hkv, 64, box_a);
   if (rc) return rc;
-  rc = make_tmap_3d(&p.a.tmV, v, D, L, (uint64_t)B * Hkv, 64, kBK);
+  rc = make_tmap_3d(&p.a.tmV, v, D, L, (uint64_t)B * Hkv, 64, box_a);
   if (rc) return rc;
   p.a.q = static_cast<const __half*>(q);
   p.a.out = static_cast<__half*>(out);
@@ -330,7 +374,7 @@ static int spec_impl(const void* q, const void* k, const void* v, const uint32_t
   p.a.mask_start = L - kd;
   fill_role(&p.a, pl.a, static_cast<uint8_t*>(ws));
   p.a.direct = (out != nullptr && pl.a.nsplit == 1 && key_hi > key_lo) ? 1 : 0;
-  rc = launch_attn<false>(p, pl.a.rt, pl.a.n_cta, stream);
+  rc = pl.a.tc ? launch_attn_tc(p, pl.a.n_cta, stream) : launch_attn<false>(p, pl.a.rt, pl.a.n_cta, stream);
   if (rc || p.a.direct) return rc;
 
   CombineParams c;
@@ -349,6 +393,12 @@ static int spec_impl(const void* q, const void* k, const void* v, const uint32_t
 // C ABI
 // ------------------------------------------------------------------------------------------------
 using namespace vmk;
+
+// Test hook: 1 = row tiles of 128 use the tcgen05 kernel (default), 0 = warp-level kernel everywhere.
+extern "C" VMK_API int vmk_attn_set_tc(int on) {
+  g_attn_tc = on ? 1 : 0;
+  return VMK_OK;
+}
 
 extern "C" size_t vmk_prefix_workspace_bytes(int N, int Hq, int Hkv, int D, int P, int S) {
   if (N <= 0 || Hq <= 0 || Hkv <= 0 || P <= 0 || S < 0 || D != kHD || Hq % Hkv != 0) return 0;
