@@ -215,29 +215,48 @@ def stage_times(inp, steps, torch):
     return out
 
 
-def side_line(opname, torch, steps):
-    """rows/s and HBM fraction of the other two ops on their sweep / tree configurations (1 GPU)."""
+def side_line(config, torch, steps):
+    """rows/s and HBM fraction of one named configuration on one GPU, L2 flushed between iterations.
+    Configurations: prefix_small, spec_chain, spec_tree, dsa_small (the single-GPU ones) and prefix_sweep."""
     from verified_metal_kernels_b200 import load_kernel, ops
-    op = ops.load_op(opname)
     g = torch.Generator(device="cuda")
     g.manual_seed(1)
     r16 = lambda *s: torch.randn(*s, generator=g, device="cuda", dtype=torch.float32).half()
-    if opname == "prefix":
-        N, P, S = PREFIX["N"], PREFIX["P"], PREFIX["S"]
-        slens = torch.randint(0, S + 1, (N,), generator=g, device="cuda", dtype=torch.int32)
-        inp = dict(q=r16(N, 32, 128), kp=r16(8, P, 128), vp=r16(8, P, 128), ks=r16(N, 8, S, 128), vs=r16(N, 8, S, 128),
-                   slens=slens)
-        nbytes = op.algorithmic_bytes(PREFIX, slens.cpu().numpy())
-        rows, name = N, f"prefix N={N} P={P} S~U[0,{S}]"
-        flops = 4.0 * N * 32 * 128 * (P + float(slens.float().mean()))
-    else:
-        B, L, kd = SPEC["B"], SPEC["L"], SPEC["k"]
+    if config in ("prefix_small", "prefix_sweep"):
+        opname = "prefix"
+        op = ops.load_op(opname)
+        shape = dict(N=8, P=4096, S=256) if config == "prefix_small" else PREFIX
+        N, P, S = shape["N"], shape["P"], shape["S"]
+        inp = dict(q=r16(N, 32, 128), kp=r16(8, P, 128), vp=r16(8, P, 128), ks=r16(N, 8, S, 128), vs=r16(N, 8, S, 128))
+        sl = None
+        if config == "prefix_sweep":
+            inp["slens"] = torch.randint(0, S + 1, (N,), generator=g, device="cuda", dtype=torch.int32)
+            sl = inp["slens"].cpu().numpy()
+        nbytes = op.algorithmic_bytes(shape, sl)
+        rows = N
+        name = f"prefix N={N} P={P} " + (f"S~U[0,{S}]" if sl is not None else f"S={S}")
+        flops = 4.0 * N * 32 * 128 * (P + (float(sl.mean()) if sl is not None else S))
+    elif config in ("spec_chain", "spec_tree"):
+        opname = "spec"
+        op = ops.load_op(opname)
+        shape = dict(B=1, L=8192, k=8) if config == "spec_chain" else SPEC
+        B, L, kd = shape["B"], shape["L"], shape["k"]
         rng = np.random.default_rng(0)
-        bits = op.pack_bits([op.tree_bits(kd, rng, 8) for _ in range(B)], kd)
-        inp = dict(q=r16(B, kd, 32, 128), k=r16(B, 8, L, 128), v=r16(B, 8, L, 128), bits=torch.from_numpy(bits).cuda())
-        nbytes = op.algorithmic_bytes(SPEC)
-        rows, name = B * kd, f"spec tree B={B} k={kd} L={L} depth<=8"
+        masks = [op.chain_bits(kd) if config == "spec_chain" else op.tree_bits(kd, rng, 8) for _ in range(B)]
+        inp = dict(q=r16(B, kd, 32, 128), k=r16(B, 8, L, 128), v=r16(B, 8, L, 128),
+                   bits=torch.from_numpy(op.pack_bits(masks, kd)).cuda())
+        nbytes = op.algorithmic_bytes(shape)
+        rows = B * kd
+        name = f"spec {'chain' if config == 'spec_chain' else 'tree depth<=8'} B={B} k={kd} L={L}"
         flops = 4.0 * B * kd * 32 * 128 * L
+    else:
+        opname = "dsa"
+        op = ops.load_op(opname)
+        shape = dict(B=8, L=32768)
+        inp = dsa_inputs(shape["B"], shape["L"], "cuda", seed=5)
+        nbytes = op.algorithmic_bytes(shape)
+        rows, name = shape["B"], "dsa B=8 L=32768"
+        flops = 2.0 * 64 * 128 * shape["L"] * shape["B"] + 2.0 * 128 * (576 + 512) * 2048 * shape["B"]
     fn = load_kernel(opname)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     times = []
@@ -252,9 +271,10 @@ def side_line(opname, torch, steps):
             times.append(a.elapsed_time(b))
     ms = statistics.median(times)
     peak, kind = peaks()
-    return dict(workload=name, rows_per_s=rows / (ms * 1e-3), ms=ms, algorithmic_gb=nbytes / 1e9,
-                hbm_gbs=nbytes / (ms * 1e-3) / 1e9, hbm_frac=nbytes / (ms * 1e-3) / 1e9 / peak, peak=kind,
-                tflops=flops / (ms * 1e-3) / 1e12, l2="flushed between iterations")
+    return dict(workload=name, rows_per_s=rows / (ms * 1e-3), ms=ms, algorithmic_mb=nbytes / 1e6,
+                hbm_gbs=nbytes / (ms * 1e-3) / 1e9, hbm_frac=nbytes / (ms * 1e-3) / 1e9 / peak, peak=f"of {kind}",
+                tflops=flops / (ms * 1e-3) / 1e12, l2="flushed between iterations",
+                timing="CUDA events around one kernel(...) call, host launch overhead included")
 
 
 # ------------------------------------------------------------------------------------------------ CPU arm
@@ -309,6 +329,8 @@ def main():
     ap.add_argument("--no-side", action="store_true", help="skip the prefix / spec side lines")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--side-only", default=None, help="time only one side configuration (prefix_small, spec_chain, "
+                    "spec_tree, dsa_small, prefix_sweep) on one GPU and print its line; used for profiling")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3) if a.impl == "ours" else a.warmup
     if a.impl == "reference":
@@ -325,6 +347,9 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     build.build()
+    if a.side_only:
+        print(json.dumps(side_line(a.side_only, torch, a.steps)))
+        return 0
     fn = load_kernel("dsa")
     op = ops.load_op("dsa")
     B, L = a.batch, a.cache
@@ -377,7 +402,7 @@ def main():
         ach = alg / (st["indexer_ms"] * 1e-3) / 1e9
         tr = ncu_traffic()
         line["roofline"] = dict(kernel="dsa indexer", bound="hbm", achieved=ach, peak=peak, unit="GB/s", frac=ach / peak,
-                                peak_source=f"of {kind}", traffic=(tr or {}).get("indexer_bytes_per_launch"),
+                                peak_source=f"of {kind}", traffic=(tr["indexer_bytes_per_position"] * Bl * L if tr else None),
                                 algorithmic_bytes=alg, launch_ms=st["indexer_ms"])
         total_alg = op.algorithmic_bytes(dict(B=Bl, L=L))
         line["stages_ms"] = st
@@ -386,7 +411,8 @@ def main():
         if not a.no_side and world == 1:
             del inp
             torch.cuda.empty_cache()
-            line["ops"] = dict(prefix=side_line("prefix", torch, 10), spec=side_line("spec", torch, 10))
+            line["ops"] = {c: side_line(c, torch, 10)
+                           for c in ("prefix_small", "spec_chain", "spec_tree", "dsa_small", "prefix_sweep")}
         if not a.no_cpu and world == 1:
             n = 2
             t = cpu_sample(n, L)

@@ -109,7 +109,7 @@ int launch_attn_tc(const AttnParams& p, int n_cta, cudaStream_t stream);   // at
 
 static int g_attn_tc = 1;   // 1: row tiles of 128 run on tcgen05 (attn_tc.cu); 0: always the warp-level kernel
 constexpr int kTcRowsMin = 65;     // stacked rows from which the tensor-memory kernel is used
-constexpr int kTcSplitCap = 16;
+constexpr int kTcSplitCap = 32;
 
 struct RolePlan {
   bool tc;                 // tcgen05 kernel (128-row tiles, 128-key blocks)
@@ -130,26 +130,27 @@ static void pick_layout(int rows, int* rt, int* ks) {
 }
 
 // Splits the keys of each (group, row tile) so that about `target` CTAs exist, in multiples of 64 keys.
-// tcgen05 path: one CTA per SM, 128-key blocks.  The split count minimises waves x (blocks per CTA +
-// a fixed per-CTA overhead of about three blocks), which avoids a mostly empty last wave.
+// tcgen05 path: one CTA per SM, 256-row tiles, 64-key blocks.  The split count minimises
+// waves x (blocks per CTA + a fixed per-CTA overhead of about six blocks), which avoids a mostly empty
+// last wave.
 static void plan_role_tc(RolePlan* r, int groups, int rows, int keys) {
   r->tc = true;
   r->rt = 8; r->ks = 1;
-  r->row_tiles = cdiv(rows, 128);
-  r->MP = r->row_tiles * 128;
+  r->row_tiles = cdiv(rows, 256);
+  r->MP = r->row_tiles * 256;
   const int units = groups * r->row_tiles;
-  const int blocks = cdiv(keys > 0 ? keys : 1, 128);
+  const int blocks = cdiv(keys > 0 ? keys : 1, kBK);
   const int sms = sm_count();
   long long best_cost = -1;
   int best = 1;
   for (int ns = 1; ns <= kTcSplitCap && ns <= blocks; ++ns) {
     const int per = cdiv(blocks, ns);
     const int real = cdiv(blocks, per);
-    const long long cost = (long long)cdiv(units * real, sms) * (per + 3);
+    const long long cost = (long long)cdiv(units * real, sms) * (per + 6);
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = real; }
   }
-  r->split_len = cdiv(blocks, best) * 128;
-  r->nsplit = cdiv(blocks * 128, r->split_len);
+  r->split_len = cdiv(blocks, best) * kBK;
+  r->nsplit = cdiv(blocks * kBK, r->split_len);
   r->n_cta = units * r->nsplit;
 }
 
@@ -290,10 +291,9 @@ static int prefix_impl(const void* q, const void* kp, const void* vp, const void
   memset(&p, 0, sizeof(p));
   p.sc = kLog2e / sqrtf((float)D);
   p.status = status;
-  const uint32_t box_a = pl.a.tc ? 128 : kBK;
-  int rc = make_tmap_3d(&p.a.tmK, kp, D, P, Hkv, 64, box_a);
+  int rc = make_tmap_3d(&p.a.tmK, kp, D, P, Hkv, 64, kBK);
   if (rc) return rc;
-  rc = make_tmap_3d(&p.a.tmV, vp, D, P, Hkv, 64, box_a);
+  rc = make_tmap_3d(&p.a.tmV, vp, D, P, Hkv, 64, kBK);
   if (rc) return rc;
   p.a.q = static_cast<const __half*>(q);
   p.a.n_groups = Hkv; p.a.Hkv = Hkv; p.a.G = G; p.a.Hq = Hq;
@@ -359,10 +359,9 @@ static int spec_impl(const void* q, const void* k, const void* v, const uint32_t
   memset(&p, 0, sizeof(p));
   p.sc = kLog2e / sqrtf((float)D);
   p.status = status;
-  const uint32_t box_a = pl.a.tc ? 128 : kBK;
-  int rc = make_tmap_3d(&p.a.tmK, k, D, L, (uint64_t)B * Hkv, 64, box_a);
+  int rc = make_tmap_3d(&p.a.tmK, k, D, L, (uint64_t)B * Hkv, 64, kBK);
   if (rc) return rc;
-  rc = make_tmap_3d(&p.a.tmV, v, D, L, (uint64_t)B * Hkv, 64, box_a);
+  rc = make_tmap_3d(&p.a.tmV, v, D, L, (uint64_t)B * Hkv, 64, kBK);
   if (rc) return rc;
   p.a.q = static_cast<const __half*>(q);
   p.a.out = static_cast<__half*>(out);

@@ -1,55 +1,73 @@
-// Split-KV decode attention on the 5th-generation tensor cores, for row tiles of 128 stacked rows
-// (many requests sharing a prefix, or a wide speculative tree): the regime where the op is bound by
-// the tensor pipe rather than by HBM.
+// Split-KV decode attention on the 5th-generation tensor cores, for large stacks of query rows (many
+// requests sharing a prefix, or a wide speculative tree): the regime where the op is bound by the
+// tensor pipe rather than by HBM.
 //
-// One CTA = one (key group, 128-row tile, key split), 192 threads, warp-specialised:
-//   warp 0      TMA producer: K and V tiles of 128 keys x 128 (two 64-wide swizzled boxes each) into a
-//               two-stage ring
-//   warp 1      owns tensor memory (512 columns) and issues the MMAs:
-//                 S[j & 1] (128 x 128 fp32) = Q . K_j^T            8 x tcgen05.mma M128 N128 K16, K-major
-//                 O        (128 x 128 fp32) += P_j . V_j           8 x tcgen05.mma, V as an MN-major operand
-//               S is double buffered so Q.K^T of block j+1 runs under the softmax of block j
-//   warps 2-5   softmax, one thread per row: tcgen05.ld of the 128 scores, scale + visibility mask,
-//               running max with LAZY rescaling (O in tensor memory is rescaled only when the max grew
-//               by more than 2^8, so P stays below 256 and exact), P rounded to fp16 into a swizzled
-//               shared-memory tile that the second MMA reads, row sums in fp32
+// One CTA = one (key group, 256-row tile, key split) and handles its rows as TWO 128-row tiles A and B
+// that share every K/V tile brought into shared memory (half the L2 traffic per flop, and two softmax
+// warpgroups to keep the tensor pipe fed).  352 threads, warp-specialised:
+//   warp 0      TMA producer of K tiles (64 keys x 128, two 64-wide swizzled boxes), 3-stage ring released
+//               as soon as both Q.K^T products have consumed a tile, so K runs ahead of the softmax
+//   warp 10     TMA producer of V tiles, ring of its own, released after both P.V products
+//   warp 1      owns tensor memory (512 columns: S_A[2], S_B[2], O_A, O_B) and issues the MMAs
+//                 S_t[j & 1] (128 x 64 fp32)  = Q_t . K_j^T      8 x tcgen05.mma M128 N64 K16, K-major operands
+//                 O_t        (128 x 128 fp32) += P_t . V_j        4 x tcgen05.mma M128 N128 K16, V MN-major
+//               S is double buffered so the Q.K^T of block j+1 runs under the softmax of block j
+//   warps 2-5   softmax of tile A, warps 6-9 softmax of tile B, one thread per row: two passes over the
+//               64 scores in tensor memory (row max, then exp2 / row sum / fp16 P into a swizzled
+//               shared-memory operand tile), LAZY rescaling of O (only when the row max grew by more than
+//               2^8, so P stays below 256 and the result exact)
 // Partials (m, l, o) per row are emitted exactly as by the warp-level kernel, so the combine pass and
-// the multi-GPU merge are shared.  Every mbarrier wait is bounded.
+// the multi-GPU merge are shared.  Every mbarrier wait is bounded; a wait that runs out sets the status
+// word and the CTA winds down through the common exit, where tensor memory is freed.
 #include "attn_core.cuh"
 #include "tcgen05.cuh"
 
 namespace vmk {
 
-constexpr int kTcBK = 128;                       // keys per block
-constexpr int kTcHalf = 128 * 128;               // one swizzled [128 rows][128 B] box
-constexpr int kTcTile = 2 * kTcHalf;             // 32 KiB: a 128 x 128 fp16 operand tile
-constexpr int kTcKvStages = 2;
-constexpr int kTcThreads = 192;
-constexpr int kTcCols = 512;                     // S0 | S1 | O | (unused)
+constexpr int kTcBK = 64;                        // keys per block
+constexpr int kTcRows = 256;                     // rows per CTA (two tiles of 128)
+constexpr int kQHalf = 128 * 128;                // [128 rows][128 B] swizzled box
+constexpr int kQTile = 2 * kQHalf;               // 32 KiB per 128-row query tile
+constexpr int kKvHalf = kTcBK * 128;             // [64 keys][128 B] swizzled box
+constexpr int kKvTile = 2 * kKvHalf;             // 16 KiB
+constexpr int kPTile = 128 * kTcBK * 2;          // 16 KiB: [128 rows][64 keys] fp16, one swizzled box
+constexpr int kTcStages = 3;
+constexpr int kTcThreads = 352;
+constexpr int kTcCols = 512;
+constexpr int kColS = 0;                         // S_A[0], S_A[1], S_B[0], S_B[1]: 4 x 64 columns
+constexpr int kColO = 256;                       // O_A, O_B: 2 x 128 columns
 constexpr float kLazyRescale = 8.f;              // log2 units
-constexpr int kTcBars = 2 * kTcKvStages + 2 + 2 + 3;
-constexpr int kAttnTcSmem = kTcTile * (1 + 2 * kTcKvStages + 1) + kTcBars * 8 + 16 + 1024;
+constexpr int kTcBars = 4 * kTcStages + 4 + 4 + 2 + 2 + 2;
+constexpr int kAttnTcSmem = 2 * kQTile + 2 * kTcStages * kKvTile + 2 * kPTile + kTcBars * 8 + 16 + 1024;
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_constant__ AttnParams p) {
   const AttnRole& R = p.a;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem;
-  uint8_t* sK = sQ + kTcTile;
-  uint8_t* sV = sK + kTcKvStages * kTcTile;
-  uint8_t* sP = sV + kTcKvStages * kTcTile;
-  uint64_t* kv_full = reinterpret_cast<uint64_t*>(sP + kTcTile);
-  uint64_t* kv_empty = kv_full + kTcKvStages;
-  uint64_t* s_full = kv_empty + kTcKvStages;
-  uint64_t* s_empty = s_full + 2;
-  uint64_t* p_full = s_empty + 2;
-  uint64_t* pv_done = p_full + 1;
-  uint64_t* q_full = pv_done + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + 1);
+  uint8_t* sQ = smem;                                   // [2 tiles][32 KiB]
+  uint8_t* sK = sQ + 2 * kQTile;                        // [stages][16 KiB]
+  uint8_t* sV = sK + kTcStages * kKvTile;               // [stages][16 KiB]
+  uint8_t* sP = sV + kTcStages * kKvTile;               // [2 tiles][16 KiB]
+  uint64_t* k_full = reinterpret_cast<uint64_t*>(sP + 2 * kPTile);
+  uint64_t* k_empty = k_full + kTcStages;
+  uint64_t* v_full = k_empty + kTcStages;
+  uint64_t* v_empty = v_full + kTcStages;
+  uint64_t* s_full = v_empty + kTcStages;               // [tile][buffer]
+  uint64_t* s_empty = s_full + 4;                       // [tile][buffer]
+  uint64_t* p_full = s_empty + 4;                       // [tile]
+  uint64_t* pv_done = p_full + 2;                       // [tile]
+  uint64_t* q_full = pv_done + 2;                       // [tile]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-  // ---- which piece of work (same decomposition as the warp-level kernel, 128-key blocks) -------------
+  // ---- which piece of work (same decomposition as the warp-level kernel) ---------------------------
   const int cta = blockIdx.x;
   const int split = cta % R.nsplit;
   const int t2 = cta / R.nsplit;
@@ -57,24 +75,29 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
   const int z = t2 / R.row_tiles;
   const int zg = z / R.Hkv, h = z % R.Hkv;
   const int rows = R.rows_outer * R.G;
-  const int row0 = tile * 128;
+  const int row0 = tile * kTcRows;
+  const bool has_b = row0 + 128 < rows;                 // tile B holds at least one real row
   const int kbeg = R.key_lo + split * R.split_len;
   int kend = min(kbeg + R.split_len, R.key_hi);
   if (R.klens != nullptr) kend = min(kend, max(0, min(R.klens[zg], R.klen)));
   const int nblk = kend > kbeg ? (kend - kbeg + kTcBK - 1) / kTcBK : 0;
 
   if (tid == 0) {
-    for (int s = 0; s < kTcKvStages; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+    for (int s = 0; s < kTcStages; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < 4; ++s) {
       mbar_init(&s_full[s], 1);
       mbar_init(&s_empty[s], 4);
     }
-    mbar_init(p_full, 4);
-    mbar_init(pv_done, 1);
-    mbar_init(q_full, 4);
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&p_full[t], 4);
+      mbar_init(&pv_done[t], 1);
+      mbar_init(&q_full[t], 4);
+    }
     fence_mbar_init();
   }
   if (warp == 1) tmem_alloc(tmem_slot, kTcCols);
@@ -82,94 +105,118 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tO = tmem_base + 256;
 
   bool timed_out = false;
-  if (warp == 0) {
-    // ------------------------------------------------------------------------------ TMA producer
+  if (warp == 0 || warp == 10) {
+    // ------------------------------------------------------------------------------ TMA producers
     if (lane == 0) {
+      const bool is_k = warp == 0;
+      uint64_t* full = is_k ? k_full : v_full;
+      uint64_t* empty = is_k ? k_empty : v_empty;
+      uint8_t* ring = is_k ? sK : sV;
+      const CUtensorMap* tm = is_k ? &R.tmK : &R.tmV;
       for (int j = 0; j < nblk; ++j) {
-        const int s = j % kTcKvStages;
-        if (j >= kTcKvStages && !mbar_wait(&kv_empty[s], (uint32_t)(((j / kTcKvStages) - 1) & 1))) {
+        const int s = j % kTcStages;
+        if (j >= kTcStages && !mbar_wait(&empty[s], (uint32_t)(((j / kTcStages) - 1) & 1))) {
           timed_out = true;
           break;
         }
         const int kb = kbeg + j * kTcBK;
-        uint8_t* k = sK + s * kTcTile;
-        uint8_t* v = sV + s * kTcTile;
-        mbar_expect_tx(&kv_full[s], 2 * kTcTile);
-        tma_load_3d(k, &R.tmK, 0, kb, z, &kv_full[s]);
-        tma_load_3d(k + kTcHalf, &R.tmK, 64, kb, z, &kv_full[s]);
-        tma_load_3d(v, &R.tmV, 0, kb, z, &kv_full[s]);
-        tma_load_3d(v + kTcHalf, &R.tmV, 64, kb, z, &kv_full[s]);
+        uint8_t* dst = ring + s * kKvTile;
+        mbar_expect_tx(&full[s], kKvTile);
+        tma_load_3d(dst, tm, 0, kb, z, &full[s]);
+        tma_load_3d(dst + kKvHalf, tm, 64, kb, z, &full[s]);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------------------ MMA issuer
     if (lane == 0 && nblk > 0) {
-      constexpr uint32_t idesc_qk = umma_idesc_f16(128, 128, 0);
+      constexpr uint32_t idesc_qk = umma_idesc_f16(128, kTcBK, 0);
       constexpr uint32_t idesc_pv = umma_idesc_f16(128, 128, 1);
       const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      const int ntile = has_b ? 2 : 1;
+      // S_t[j & 1] = Q_t . K_j^T for both tiles; releases the K stage
       auto issue_qk = [&](int j) {
-        const int s = j & 1;
-        const uint32_t k_addr = smem_u32(sK + (j % kTcKvStages) * kTcTile);
+        const uint32_t k_addr = smem_u32(sK + (j % kTcStages) * kKvTile);
+        for (int t = 0; t < ntile; ++t) {
+          const uint32_t d = tmem_base + kColS + (t * 2 + (j & 1)) * kTcBK;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t off = (k >> 2) * kTcHalf + (k & 3) * 32;
-          umma_f16(tmem_base + s * 128, umma_desc_sw128(q_addr + off), umma_desc_sw128(k_addr + off), idesc_qk,
-                   k > 0 ? 1u : 0u);
+          for (int k = 0; k < 8; ++k) {
+            const uint64_t da = umma_desc_sw128(q_addr + t * kQTile + (k >> 2) * kQHalf + (k & 3) * 32);
+            const uint64_t db = umma_desc_sw128(k_addr + (k >> 2) * kKvHalf + (k & 3) * 32);
+            umma_f16(d, da, db, idesc_qk, k > 0 ? 1u : 0u);
+          }
+          umma_commit(&s_full[t * 2 + (j & 1)]);
         }
-        umma_commit(&s_full[s]);
+        umma_commit(&k_empty[j % kTcStages]);
       };
-      if (!mbar_wait(q_full, 0) || !mbar_wait(&kv_full[0], 0)) timed_out = true;
+      auto wait_qk_inputs = [&](int j) -> bool {
+        if (!mbar_wait(&k_full[j % kTcStages], (uint32_t)((j / kTcStages) & 1))) return false;
+        if (j >= 2) {
+          for (int t = 0; t < ntile; ++t)
+            if (!mbar_wait(&s_empty[t * 2 + (j & 1)], (uint32_t)(((j >> 1) - 1) & 1))) return false;
+        }
+        return true;
+      };
+      for (int t = 0; t < ntile; ++t)
+        if (!mbar_wait(&q_full[t], 0)) timed_out = true;
+      if (!timed_out && !wait_qk_inputs(0)) timed_out = true;
       if (!timed_out) {
         tc_fence_after();
         issue_qk(0);
       }
       for (int j = 0; j < nblk && !timed_out; ++j) {
         if (j + 1 < nblk) {
-          const int j1 = j + 1, s1 = j1 & 1;
-          if (!mbar_wait(&kv_full[j1 % kTcKvStages], (uint32_t)((j1 / kTcKvStages) & 1))) { timed_out = true; break; }
-          if (j1 >= 2 && !mbar_wait(&s_empty[s1], (uint32_t)(((j1 >> 1) - 1) & 1))) { timed_out = true; break; }
+          if (!wait_qk_inputs(j + 1)) { timed_out = true; break; }
           tc_fence_after();
-          issue_qk(j1);
+          issue_qk(j + 1);
         }
-        if (!mbar_wait(p_full, (uint32_t)(j & 1))) { timed_out = true; break; }
-        tc_fence_after();
-        const uint32_t v_addr = smem_u32(sV + (j % kTcKvStages) * kTcTile);
+        if (!mbar_wait(&v_full[j % kTcStages], (uint32_t)((j / kTcStages) & 1))) { timed_out = true; break; }
+        const uint32_t v_addr = smem_u32(sV + (j % kTcStages) * kKvTile);
+        for (int t = 0; t < ntile; ++t) {
+          if (!mbar_wait(&p_full[t], (uint32_t)(j & 1))) { timed_out = true; break; }
+          tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          // A: P[:, 16k .. 16k+16) K-major; B: V rows 16k .. 16k+16 (keys) x 128 d, MN-major:
-          // 8-key groups 1024 B apart, the two 64-wide d halves kTcHalf apart.
-          const uint64_t da = umma_desc_sw128(p_addr + (k >> 2) * kTcHalf + (k & 3) * 32);
-          const uint64_t db = umma_desc_sw128_mn(v_addr + k * 2048, kTcHalf, 1024);
-          umma_f16(tO, da, db, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < kTcBK / 16; ++k) {
+            // A: P_t[:, 16k .. 16k+16) K-major (one 128-byte swizzled row per query row);
+            // B: V rows 16k .. 16k+16 (keys) x 128 d, MN-major: 8-key groups 1024 B apart, the two 64-wide
+            //    d halves kKvHalf apart.
+            const uint64_t da = umma_desc_sw128(p_addr + t * kPTile + k * 32);
+            const uint64_t db = umma_desc_sw128_mn(v_addr + k * 2048, kKvHalf, 1024);
+            umma_f16(tmem_base + kColO + t * 128, da, db, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&pv_done[t]);
         }
-        umma_commit(&kv_empty[j % kTcKvStages]);
-        umma_commit(pv_done);
+        if (timed_out) break;
+        umma_commit(&v_empty[j % kTcStages]);
       }
     }
-  } else {
+  } else if (warp >= 2 && warp <= 9) {
     // ------------------------------------------------------------------------------ softmax warps
-    const int quarter = warp & 3;
+    const int t = (warp - 2) >> 2;                        // 0: tile A, 1: tile B
+    const int quarter = warp & 3;                         // tensor-memory lanes [32 q, 32 q + 32)
     const int row = quarter * 32 + lane;
-    const int grow = row0 + row;
+    const int grow = row0 + t * 128 + row;
     const bool valid_row = grow < rows;
+    const bool tile_on = t == 0 || has_b;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t tS = lane_base + kColS + t * 2 * kTcBK;
+    const uint32_t tO = lane_base + kColO + t * 128;
     const size_t outer = (size_t)zg * R.rows_outer + (valid_row ? grow / R.G : 0);
     const int head = h * R.G + (valid_row ? grow % R.G : 0);
+    uint8_t* myP = sP + t * kPTile;
 
-    // this thread's query row -> swizzled K-major operand tile
-    {
+    if (tile_on) {
+      // this thread's query row -> swizzled K-major operand tile
       const uint4* src = reinterpret_cast<const uint4*>(R.q + (outer * R.Hq + head) * kHD);
 #pragma unroll
       for (int c = 0; c < 16; ++c) {
         const uint4 v = valid_row ? src[c] : make_uint4(0u, 0u, 0u, 0u);
-        *reinterpret_cast<uint4*>(sQ + (c >> 3) * kTcHalf + swz128(row, c & 7)) = v;
+        *reinterpret_cast<uint4*>(sQ + t * kQTile + (c >> 3) * kQHalf + swz128(row, c & 7)) = v;
       }
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) mbar_arrive(q_full);
+      if (lane == 0) mbar_arrive(&q_full[t]);
     }
     uint32_t mw[kMaxMaskWords];
 #pragma unroll
@@ -179,43 +226,45 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
     }
 
     float m = -INFINITY, l = 0.f;
-    for (int j = 0; j < nblk; ++j) {
+    const int nloop = tile_on ? nblk : 0;
+    for (int j = 0; j < nloop; ++j) {
       const int sb = j & 1;
-      bool ok = mbar_wait(&s_full[sb], (uint32_t)((j >> 1) & 1));
+      bool ok = mbar_wait(&s_full[t * 2 + sb], (uint32_t)((j >> 1) & 1));
       if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
       tc_fence_after();
-      uint32_t sr[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(lane_base + sb * 128 + c * 32, sr[c]);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[sb]);
-
       const int kb = kbeg + j * kTcBK;
       const bool tail = kb + kTcBK > kend;
       const bool edge = tail || (kb + kTcBK > R.mask_start);
+      auto score = [&](uint32_t raw, int key) -> float {
+        float tt = __uint_as_float(raw) * p.sc;
+        if (edge) {
+          bool vis = key < kend;
+          if (vis && key >= R.mask_start) {
+            const int jb = key - R.mask_start;
+            uint32_t word = mw[0];
+#pragma unroll
+            for (int w = 1; w < kMaxMaskWords; ++w) word = ((jb >> 5) == w) ? mw[w] : word;
+            vis = (word >> (jb & 31)) & 1u;
+          }
+          tt = vis ? tt : -INFINITY;
+        }
+        return tt;
+      };
+      // pass 1: row maximum of the 64 scores
+      uint32_t s0[32], s1[32];
+      tmem_ld32(tS + sb * kTcBK, s0);
+      tmem_ld32(tS + sb * kTcBK + 32, s1);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[t * 2 + sb]);    // the scores now live in registers
       float bm = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float t = __uint_as_float(sr[c][i]) * p.sc;
-          if (edge) {
-            const int key = kb + c * 32 + i;
-            bool vis = key < kend;
-            if (vis && key >= R.mask_start) {
-              const int jb = key - R.mask_start;
-              uint32_t word = mw[0];
-#pragma unroll
-              for (int w = 1; w < kMaxMaskWords; ++w) word = ((jb >> 5) == w) ? mw[w] : word;
-              vis = (word >> (jb & 31)) & 1u;
-            }
-            t = vis ? t : -INFINITY;
-          }
-          sr[c][i] = __float_as_uint(t);
-          bm = fmaxf(bm, t);
-        }
+      for (int i = 0; i < 32; ++i) {
+        const float a = score(s0[i], kb + i), b = score(s1[i], kb + 32 + i);
+        s0[i] = __float_as_uint(a);
+        s1[i] = __float_as_uint(b);
+        bm = fmaxf(bm, fmaxf(a, b));
       }
       const float m_new = fmaxf(m, bm);
       float alpha = 1.f;
@@ -223,84 +272,85 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
       if (m == -INFINITY) {
         m = m_new;                                   // nothing accumulated for this row yet
       } else if (m_new > m + kLazyRescale) {
-        alpha = exp2f(m - m_new);
+        alpha = fast_exp2(m - m_new);
         m = m_new;
         rescale = true;
       }
       l *= alpha;
       const float mu = (m == -INFINITY) ? 0.f : m;
-      float ps = 0.f;
+      float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float pv = exp2f(__uint_as_float(sr[c][i]) - mu);
-          ps += pv;
-          sr[c][i] = __float_as_uint(pv);
-        }
+      for (int i = 0; i < 32; ++i) {
+        const float a = fast_exp2(__uint_as_float(s0[i]) - mu), b = fast_exp2(__uint_as_float(s1[i]) - mu);
+        ps0 += a;
+        ps1 += b;
+        s0[i] = __float_as_uint(a);
+        s1[i] = __float_as_uint(b);
       }
-      l += ps;
+      l += ps0 + ps1;
 
-      // O and the P tile are free once P_{j-1} . V_{j-1} has completed
+      // O_t and the P tile are free once P_{j-1} . V_{j-1} has completed
       if (j >= 1) {
-        ok = mbar_wait(pv_done, (uint32_t)((j - 1) & 1));
+        ok = mbar_wait(&pv_done[t], (uint32_t)((j - 1) & 1));
         if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
         tc_fence_after();
       }
       if (__any_sync(0xffffffffu, rescale)) {
-#pragma unroll
+#pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t o[32];
-          tmem_ld32(lane_base + 256 + c * 32, o);
+          tmem_ld32(tO + c * 32, o);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st32(lane_base + 256 + c * 32, o);
+          tmem_st32(tO + c * 32, o);
         }
         tmem_st_wait();
       }
-      if (tail && kend < R.klen) {
-        // keys past kend exist in memory: their V rows must not reach the MMA (0 * Inf would poison the row)
-        ok = mbar_wait(&kv_full[j % kTcKvStages], (uint32_t)((j / kTcKvStages) & 1));
+      if (tail && kend < R.klen && t == 0) {
+        // keys past kend exist in memory: their V rows must not reach the MMA (0 * Inf would poison the
+        // row).  Tile A's warps clear them; tile B's P.V is issued after tile A's p_full.
+        ok = mbar_wait(&v_full[j % kTcStages], (uint32_t)((j / kTcStages) & 1));
         if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
-        uint8_t* v = sV + (j % kTcKvStages) * kTcTile;
+        uint8_t* v = sV + (j % kTcStages) * kKvTile;
         const int r0 = kend - kb;
         for (int i = row; i < (kTcBK - r0) * 16; i += 128) {
           const int r = r0 + (i >> 4), c = i & 15;
-          *reinterpret_cast<uint4*>(v + (c >> 3) * kTcHalf + swz128(r, c & 7)) = make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4*>(v + (c >> 3) * kKvHalf + swz128(r, c & 7)) = make_uint4(0u, 0u, 0u, 0u);
         }
       }
-      // P (fp16) -> swizzled K-major operand tile
+      // P (fp16) -> swizzled K-major operand tile: 64 keys = 8 chunks of 16 bytes per row
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
+      for (int c = 0; c < 8; ++c) {
+        const uint32_t* s8 = (c < 4) ? &s0[c * 8] : &s1[(c - 4) * 8];
         uint4 v;
-        const uint32_t* s8 = &sr[c >> 2][(c & 3) * 8];
         v.x = pack_half2(__uint_as_float(s8[0]), __uint_as_float(s8[1]));
         v.y = pack_half2(__uint_as_float(s8[2]), __uint_as_float(s8[3]));
         v.z = pack_half2(__uint_as_float(s8[4]), __uint_as_float(s8[5]));
         v.w = pack_half2(__uint_as_float(s8[6]), __uint_as_float(s8[7]));
-        *reinterpret_cast<uint4*>(sP + (c >> 3) * kTcHalf + swz128(row, c & 7)) = v;
+        *reinterpret_cast<uint4*>(myP + swz128(row, c)) = v;
       }
       fence_proxy_async();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(&p_full[t]);
     }
 
     // ---- emit this row's partial (or final) result ------------------------------------------------
     bool have_o = false;
-    if (!timed_out && nblk > 0) {
-      const bool ok = mbar_wait(pv_done, (uint32_t)((nblk - 1) & 1));
+    if (!timed_out && nloop > 0) {
+      const bool ok = mbar_wait(&pv_done[t], (uint32_t)((nloop - 1) & 1));
       if (!__all_sync(0xffffffffu, ok)) timed_out = true; else have_o = true;
       tc_fence_after();
     }
-    if (!timed_out) {
+    if (!timed_out && tile_on) {
       const size_t slot = (size_t)z * R.nsplit + split;
-#pragma unroll
+      const float inv = 1.f / l;
+#pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t o[32];
         if (have_o) {
-          tmem_ld32(lane_base + 256 + c * 32, o);
+          tmem_ld32(tO + c * 32, o);
           tmem_ld_wait();
         } else {
 #pragma unroll
@@ -309,7 +359,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
         if (!valid_row) continue;
         if (R.direct) {
           __half* dst = R.out + (outer * R.Hq + head) * kHD + c * 32;
-          const float inv = 1.f / l;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             uint4 v;
