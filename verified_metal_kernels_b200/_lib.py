@@ -6,7 +6,7 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libvmk_b200.so")
+LIB_PATH = os.path.join(HERE, os.environ.get("VMK_LIB_NAME", "libvmk_b200.so"))
 
 _c = ctypes
 _vp, _i, _sz = _c.c_void_p, _c.c_int, _c.c_size_t

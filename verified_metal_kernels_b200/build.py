@@ -6,7 +6,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-LIB = os.path.join(HERE, "libvmk_b200.so")
+LIB = os.path.join(HERE, os.environ.get("VMK_LIB_NAME", "libvmk_b200.so"))   # a debug build may use another name
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", "--extended-lambda",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 
@@ -28,12 +28,13 @@ def build(force=False, verbose=False):
     if not force and not needs_build():
         return LIB
     nvcc = os.environ.get("NVCC", "nvcc")
-    objdir = os.path.join(HERE, "build")
+    extra = os.environ.get("VMK_EXTRA_NVCC_FLAGS", "").split()      # e.g. -DVMK_TC_TIMING for device-side phase timers
+    objdir = os.path.join(HERE, "build" + ("_" + os.path.basename(LIB) if extra else ""))
     os.makedirs(objdir, exist_ok=True)
     procs = []
     for src in sources():
         obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
-        cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+        cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
         procs.append((cmd, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     objs = []
     for cmd, obj, p in procs:

@@ -212,19 +212,26 @@ __device__ __forceinline__ void attn_core(const AttnRole& R, float sc, int32_t* 
     // scale, mask, online softmax
     float bm_lo = -INFINITY, bm_hi = -INFINITY;
     const bool edge = tail || (kb + kBK > R.mask_start);
+    if (!edge) {
+      // interior block: every key visible; no per-element branches in the hot path
 #pragma unroll
-    for (int n = 0; n < NT8; ++n) {
+      for (int n = 0; n < NT8; ++n) {
+        sacc[n][0] *= sc; sacc[n][1] *= sc; sacc[n][2] *= sc; sacc[n][3] *= sc;
+        bm_lo = fmaxf(bm_lo, fmaxf(sacc[n][0], sacc[n][1]));
+        bm_hi = fmaxf(bm_hi, fmaxf(sacc[n][2], sacc[n][3]));
+      }
+    } else {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float t = sacc[n][e] * sc;
-        if (edge) {
+      for (int n = 0; n < NT8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
           const int key = kb + key0 + n * 8 + 2 * (lane & 3) + (e & 1);
           bool ok = key < kend;
           if (ok && key >= R.mask_start) ok = visible((e < 2) ? mw_lo : mw_hi, key - R.mask_start);
-          t = ok ? t : -INFINITY;
+          const float t = ok ? sacc[n][e] * sc : -INFINITY;
+          sacc[n][e] = t;
+          if (e < 2) bm_lo = fmaxf(bm_lo, t); else bm_hi = fmaxf(bm_hi, t);
         }
-        sacc[n][e] = t;
-        if (e < 2) bm_lo = fmaxf(bm_lo, t); else bm_hi = fmaxf(bm_hi, t);
       }
     }
     bm_lo = fmaxf(bm_lo, __shfl_xor_sync(0xffffffffu, bm_lo, 1));

@@ -40,6 +40,16 @@ constexpr float kLazyRescale = 8.f;              // log2 units
 constexpr int kTcBars = 4 * kTcStages + 4 + 4 + 2 + 2 + 2;
 constexpr int kAttnTcSmem = 2 * kQTile + 2 * kTcStages * kKvTile + 2 * kPTile + kTcBars * 8 + 16 + 1024;
 
+#ifdef VMK_TC_TIMING
+// Debug build only: cycles spent per phase by CTA 0 (softmax warp 2 lane 0: slots 0-7, MMA thread: 8-15).
+__device__ long long g_tc_timing[16];
+#define TC_T0() long long _t0 = clock64()
+#define TC_ACC(slot) do { if (blockIdx.x == 0) { long long _t1 = clock64(); g_tc_timing[slot] += _t1 - _t0; _t0 = _t1; } } while (0)
+#else
+#define TC_T0() do {} while (0)
+#define TC_ACC(slot) do {} while (0)
+#endif
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -133,18 +143,25 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
     if (lane == 0 && nblk > 0) {
       constexpr uint32_t idesc_qk = umma_idesc_f16(128, kTcBK, 0);
       constexpr uint32_t idesc_pv = umma_idesc_f16(128, 128, 1);
-      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
       const int ntile = has_b ? 2 : 1;
+      // Descriptor words.  High words are constants of the layout; low words are (address >> 4) plus a
+      // constant per K step: +2 per 32-byte step inside a 128-byte swizzled row, + half-tile / 16 for the
+      // second 64-wide half, +128 per 16-key step of an MN-major V tile.
+      const uint32_t hi_k = (uint32_t)(umma_desc_sw128(0) >> 32);
+      const uint32_t hi_v = (uint32_t)(umma_desc_sw128_mn(0, kKvHalf, 1024) >> 32);
+      const uint32_t lo_k0 = (uint32_t)umma_desc_sw128(0), lo_v0 = (uint32_t)umma_desc_sw128_mn(0, kKvHalf, 1024);
+      const uint32_t q_lo = lo_k0 + (smem_u32(sQ) >> 4), p_lo = lo_k0 + (smem_u32(sP) >> 4);
+      const uint32_t k_lo = lo_k0 + (smem_u32(sK) >> 4), v_lo = lo_v0 + (smem_u32(sV) >> 4);
       // S_t[j & 1] = Q_t . K_j^T for both tiles; releases the K stage
       auto issue_qk = [&](int j) {
-        const uint32_t k_addr = smem_u32(sK + (j % kTcStages) * kKvTile);
+        const uint32_t kb_lo = k_lo + (j % kTcStages) * (kKvTile >> 4);
         for (int t = 0; t < ntile; ++t) {
           const uint32_t d = tmem_base + kColS + (t * 2 + (j & 1)) * kTcBK;
+          const uint32_t qa_lo = q_lo + t * (kQTile >> 4);
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
-            const uint64_t da = umma_desc_sw128(q_addr + t * kQTile + (k >> 2) * kQHalf + (k & 3) * 32);
-            const uint64_t db = umma_desc_sw128(k_addr + (k >> 2) * kKvHalf + (k & 3) * 32);
-            umma_f16(d, da, db, idesc_qk, k > 0 ? 1u : 0u);
+            umma_f16_w(d, qa_lo + (k >> 2) * (kQHalf >> 4) + (k & 3) * 2, hi_k,
+                       kb_lo + (k >> 2) * (kKvHalf >> 4) + (k & 3) * 2, hi_k, idesc_qk, k > 0 ? 1u : 0u);
           }
           umma_commit(&s_full[t * 2 + (j & 1)]);
         }
@@ -165,27 +182,32 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
         tc_fence_after();
         issue_qk(0);
       }
+      TC_T0();
       for (int j = 0; j < nblk && !timed_out; ++j) {
         if (j + 1 < nblk) {
           if (!wait_qk_inputs(j + 1)) { timed_out = true; break; }
+          TC_ACC(8);
           tc_fence_after();
           issue_qk(j + 1);
+          TC_ACC(9);
         }
         if (!mbar_wait(&v_full[j % kTcStages], (uint32_t)((j / kTcStages) & 1))) { timed_out = true; break; }
-        const uint32_t v_addr = smem_u32(sV + (j % kTcStages) * kKvTile);
+        TC_ACC(10);
+        const uint32_t vb_lo = v_lo + (j % kTcStages) * (kKvTile >> 4);
         for (int t = 0; t < ntile; ++t) {
           if (!mbar_wait(&p_full[t], (uint32_t)(j & 1))) { timed_out = true; break; }
+          TC_ACC(11 + t);
           tc_fence_after();
 #pragma unroll
           for (int k = 0; k < kTcBK / 16; ++k) {
             // A: P_t[:, 16k .. 16k+16) K-major (one 128-byte swizzled row per query row);
             // B: V rows 16k .. 16k+16 (keys) x 128 d, MN-major: 8-key groups 1024 B apart, the two 64-wide
             //    d halves kKvHalf apart.
-            const uint64_t da = umma_desc_sw128(p_addr + t * kPTile + k * 32);
-            const uint64_t db = umma_desc_sw128_mn(v_addr + k * 2048, kKvHalf, 1024);
-            umma_f16(tmem_base + kColO + t * 128, da, db, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+            umma_f16_w(tmem_base + kColO + t * 128, p_lo + t * (kPTile >> 4) + k * 2, hi_k, vb_lo + k * (2048 >> 4), hi_v,
+                       idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&pv_done[t]);
+          TC_ACC(13);
         }
         if (timed_out) break;
         umma_commit(&v_empty[j % kTcStages]);
@@ -227,29 +249,22 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
 
     float m = -INFINITY, l = 0.f;
     const int nloop = tile_on ? nblk : 0;
+#ifdef VMK_TC_TIMING
+    const bool tc_probe = warp == 2 && lane == 0;
+    long long _t0 = clock64();
+#define SM_ACC(slot) do { if (tc_probe && blockIdx.x == 0) { long long _t1 = clock64(); g_tc_timing[slot] += _t1 - _t0; _t0 = _t1; } } while (0)
+#else
+#define SM_ACC(slot) do {} while (0)
+#endif
     for (int j = 0; j < nloop; ++j) {
       const int sb = j & 1;
       bool ok = mbar_wait(&s_full[t * 2 + sb], (uint32_t)((j >> 1) & 1));
       if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
+      SM_ACC(0);
       tc_fence_after();
       const int kb = kbeg + j * kTcBK;
       const bool tail = kb + kTcBK > kend;
       const bool edge = tail || (kb + kTcBK > R.mask_start);
-      auto score = [&](uint32_t raw, int key) -> float {
-        float tt = __uint_as_float(raw) * p.sc;
-        if (edge) {
-          bool vis = key < kend;
-          if (vis && key >= R.mask_start) {
-            const int jb = key - R.mask_start;
-            uint32_t word = mw[0];
-#pragma unroll
-            for (int w = 1; w < kMaxMaskWords; ++w) word = ((jb >> 5) == w) ? mw[w] : word;
-            vis = (word >> (jb & 31)) & 1u;
-          }
-          tt = vis ? tt : -INFINITY;
-        }
-        return tt;
-      };
       // pass 1: row maximum of the 64 scores
       uint32_t s0[32], s1[32];
       tmem_ld32(tS + sb * kTcBK, s0);
@@ -258,13 +273,47 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[t * 2 + sb]);    // the scores now live in registers
+      SM_ACC(1);
       float bm = -INFINITY;
+      if (!edge) {
+        // interior block: every key visible.  Kept free of per-element branches so the hot loop is a
+        // short straight-line sequence.
+        float bm1 = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float a = score(s0[i], kb + i), b = score(s1[i], kb + 32 + i);
-        s0[i] = __float_as_uint(a);
-        s1[i] = __float_as_uint(b);
-        bm = fmaxf(bm, fmaxf(a, b));
+        for (int i = 0; i < 32; ++i) {
+          const float a = __uint_as_float(s0[i]) * p.sc, b = __uint_as_float(s1[i]) * p.sc;
+          s0[i] = __float_as_uint(a);
+          s1[i] = __float_as_uint(b);
+          bm = fmaxf(bm, a);
+          bm1 = fmaxf(bm1, b);
+        }
+        bm = fmaxf(bm, bm1);
+      } else {
+        // block touching the end of the key range or the draft positions: per-key visibility
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = kb + half * 32 + i;
+            bool vis = key < kend;
+            if (vis && key >= R.mask_start) {
+              const int jb = key - R.mask_start;
+              uint32_t word = mw[0];
+#pragma unroll
+              for (int w = 1; w < kMaxMaskWords; ++w) word = ((jb >> 5) == w) ? mw[w] : word;
+              vis = (word >> (jb & 31)) & 1u;
+            }
+            if (half == 0) {
+              const float a = vis ? __uint_as_float(s0[i]) * p.sc : -INFINITY;
+              s0[i] = __float_as_uint(a);
+              bm = fmaxf(bm, a);
+            } else {
+              const float a = vis ? __uint_as_float(s1[i]) * p.sc : -INFINITY;
+              s1[i] = __float_as_uint(a);
+              bm = fmaxf(bm, a);
+            }
+          }
+        }
       }
       const float m_new = fmaxf(m, bm);
       float alpha = 1.f;
@@ -288,6 +337,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
         s1[i] = __float_as_uint(b);
       }
       l += ps0 + ps1;
+      SM_ACC(2);
 
       // O_t and the P tile are free once P_{j-1} . V_{j-1} has completed
       if (j >= 1) {
@@ -295,6 +345,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
         if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
         tc_fence_after();
       }
+      SM_ACC(3);
       if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
@@ -319,6 +370,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
           *reinterpret_cast<uint4*>(v + (c >> 3) * kKvHalf + swz128(r, c & 7)) = make_uint4(0u, 0u, 0u, 0u);
         }
       }
+      SM_ACC(4);
       // P (fp16) -> swizzled K-major operand tile: 64 keys = 8 chunks of 16 bytes per row
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
@@ -334,6 +386,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[t]);
+      SM_ACC(5);
     }
 
     // ---- emit this row's partial (or final) result ------------------------------------------------
@@ -391,6 +444,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
     tmem_free(tmem_base, kTcCols);
   }
 }
+
+#ifdef VMK_TC_TIMING
+extern "C" VMK_API int vmk_debug_tc_timing(long long* out, int reset) {
+  long long zero[16] = {0};
+  cudaDeviceSynchronize();
+  if (out) cudaMemcpyFromSymbol(out, g_tc_timing, sizeof(zero));
+  if (reset) cudaMemcpyToSymbol(g_tc_timing, zero, sizeof(zero));
+  return 0;
+}
+#endif
 
 int launch_attn_tc(const AttnParams& p, int n_cta, cudaStream_t stream) {
   static int configured_dev = -1;
