@@ -130,6 +130,14 @@ static void pick_layout(int rows, int* rt, int* ks) {
 }
 
 // Splits the keys of each (group, row tile) so that about `target` CTAs exist, in multiples of 64 keys.
+// Upper bound of the split count of the tcgen05 path; also sizes its share of the workspace, so that
+// one workspace size serves every key range.
+static int tc_split_cap(int units) {
+  int cap = cdiv(2 * sm_count(), units > 0 ? units : 1);
+  if (cap > kTcSplitCap) cap = kTcSplitCap;
+  return cap < 1 ? 1 : cap;
+}
+
 // tcgen05 path: one CTA per SM, 256-row tiles, 64-key blocks.  The split count minimises
 // waves x (blocks per CTA + a fixed per-CTA overhead of about six blocks), which avoids a mostly empty
 // last wave.
@@ -137,13 +145,14 @@ static void plan_role_tc(RolePlan* r, int groups, int rows, int keys) {
   r->tc = true;
   r->rt = 8; r->ks = 1;
   r->row_tiles = cdiv(rows, 256);
-  r->MP = r->row_tiles * 256;
+  r->MP = rows;                      // partial rows are indexed by the real row, no padding needed
   const int units = groups * r->row_tiles;
   const int blocks = cdiv(keys > 0 ? keys : 1, kBK);
   const int sms = sm_count();
+  const int cap = tc_split_cap(units);
   long long best_cost = -1;
   int best = 1;
-  for (int ns = 1; ns <= kTcSplitCap && ns <= blocks; ++ns) {
+  for (int ns = 1; ns <= cap && ns <= blocks; ++ns) {
     const int per = cdiv(blocks, ns);
     const int real = cdiv(blocks, per);
     const long long cost = (long long)cdiv(units * real, sms) * (per + 6);
@@ -160,7 +169,7 @@ static void plan_role(RolePlan* r, int groups, int rows, int keys, int target, b
   if (fixed_small) { r->rt = 1; r->ks = 4; } else pick_layout(rows, &r->rt, &r->ks);
   const int mt = r->rt * 16;
   r->row_tiles = cdiv(rows, mt);
-  r->MP = r->row_tiles * mt;
+  r->MP = rows;                      // partial rows are indexed by the real row, no padding needed
   const int units = groups * r->row_tiles;
   const int blocks = cdiv(keys > 0 ? keys : 1, kBK);
   int want = cdiv(target > 0 ? target : 1, units > 0 ? units : 1);
@@ -207,7 +216,7 @@ static PrefixPlan plan_prefix(int N, int Hq, int Hkv, int P, int S, int key_lo, 
   int target_a = 2 * sms - target_b;
   if (target_a < sms) target_a = sms;
   plan_role(&pl.a, Hkv, N * G, key_hi - key_lo, target_a, false);
-  size_t off = place(&pl.a, Hkv, 0, pl.a.tc ? kTcSplitCap : cdiv(2 * sms, Hkv * pl.a.row_tiles));
+  size_t off = place(&pl.a, Hkv, 0, pl.a.tc ? tc_split_cap(Hkv * pl.a.row_tiles) : cdiv(2 * sms, Hkv * pl.a.row_tiles));
   if (pl.has_b) off = place(&pl.b, N * Hkv, off, pl.b.nsplit);
   pl.ws_bytes = align_up(off, 256);
   return pl;
@@ -222,7 +231,7 @@ static SpecPlan plan_spec(int B, int kd, int Hq, int Hkv, int key_lo, int key_hi
   SpecPlan pl;
   const int G = Hq / Hkv;
   plan_role(&pl.a, B * Hkv, kd * G, key_hi - key_lo, 2 * sm_count(), false);
-  pl.ws_bytes = align_up(place(&pl.a, B * Hkv, 0, pl.a.tc ? kTcSplitCap
+  pl.ws_bytes = align_up(place(&pl.a, B * Hkv, 0, pl.a.tc ? tc_split_cap(B * Hkv * pl.a.row_tiles)
                                                                : cdiv(2 * sm_count(), B * Hkv * pl.a.row_tiles)), 256);
   return pl;
 }
