@@ -41,6 +41,7 @@ extern "C" {
 #define VMK_E_WORKSPACE (-3)    /* ws_bytes smaller than vmk_<op>_workspace_bytes(...) */
 #define VMK_E_LAUNCH (-4)       /* the CUDA runtime rejected a launch */
 #define VMK_E_DRIVER (-5)       /* tensor-map encoding failed / driver entry point missing */
+#define VMK_E_TOO_LARGE (-6)    /* the problem needs more scratch than a built-in static buffer holds */
 
 #define VMK_DSA_TOPK 2048
 #define VMK_SPEC_MAX_DRAFTS 128
@@ -71,6 +72,26 @@ VMK_API size_t vmk_spec_workspace_bytes(int B, int kd, int Hq, int Hkv, int D, i
 VMK_API int vmk_spec_verify(const void* q, const void* k, const void* v, const uint32_t* bits, int bits_words,
                     void* out, int B, int kd, int Hq, int Hkv, int D, int L, void* ws, size_t ws_bytes,
                     int32_t* status, void* stream);
+
+/* vmk_spec_verify without any caller-provided scratch.  This entry point has no counterpart in the
+ * reference; it exists for hosts that may not allocate device memory around the call: a serving runtime
+ * that hands every byte of HBM to its own pools at start-up and loads this library as a plug-in with no
+ * allocator to call back into, or a latency-critical loop whose rules forbid cudaMalloc once it is
+ * running.  The split partials live in a static device array inside the library image
+ * (VMK_SPEC_NOALLOC_SCRATCH_BYTES on every GPU that loads the library, held until the process exits),
+ * so there is neither `ws` nor `ws_bytes`; inputs and output are still the caller's.
+ *   - A shape whose partials would not fit is refused with VMK_E_TOO_LARGE before anything is launched;
+ *     vmk_spec_workspace_bytes(...) <= VMK_SPEC_NOALLOC_SCRATCH_BYTES tells in advance.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress); make
+ *     that first call before any stream capture begins on that device.
+ *   - All calls on a device share the one array and it keeps the previous call's contents.  Nothing in
+ *     it needs clearing, but calls whose kernels overlap on the GPU (different streams) race on it:
+ *     serialise them, or use vmk_spec_verify with separate workspaces.
+ *   - It performs no cudaMalloc / cudaFree and calls no allocating library routine. */
+#define VMK_SPEC_NOALLOC_SCRATCH_BYTES (32u << 20)
+VMK_API int vmk_spec_verify_noalloc(const void* q, const void* k, const void* v, const uint32_t* bits,
+                                    int bits_words, void* out, int B, int kd, int Hq, int Hkv, int D, int L,
+                                    int32_t* status, void* stream);
 
 /* ---- dsa: DeepSeek sparse attention decode ----------------------------------------------------
  * Replaces the reference's indexer / select / gather+QK / softmax / PV / reduce launches

@@ -60,6 +60,7 @@ extern "C" const char* vmk_error_string(int code) {
     case VMK_E_WORKSPACE: return "workspace smaller than vmk_<op>_workspace_bytes()";
     case VMK_E_LAUNCH: return "CUDA launch failed";
     case VMK_E_DRIVER: return "tensor-map encoding failed or the driver entry point is missing";
+    case VMK_E_TOO_LARGE: return "the problem needs more scratch than the library's built-in static buffer holds";
     default: return "unknown error code";
   }
 }

@@ -452,6 +452,47 @@ extern "C" int vmk_spec_partial(const void* q, const void* k, const void* v, con
                    ws, ws_bytes, status, static_cast<cudaStream_t>(stream));
 }
 
+// ------------------------------------------------------------------------------------------------
+// vmk_spec_verify_noalloc: the same kernels, with the split partials in a buffer that is part of the
+// library image instead of caller-provided scratch.
+//
+// g_spec_scratch is a file-scope device array: every GPU that loads the library reserves these bytes
+// until the process exits.  In host code the name is only a handle; the device address comes from
+// cudaGetSymbolAddress, taken once per device with that device current.  Every call on a device uses
+// the same bytes, which still hold the previous call's partials: the kernels write each partial before
+// the combine pass reads it, so nothing has to be cleared -- but two calls whose kernels overlap on the
+// GPU (different streams) would overwrite each other's partials.
+// ------------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_spec_scratch[VMK_SPEC_NOALLOC_SCRATCH_BYTES];
+
+static int spec_scratch_address(void** out) {
+  static void* cached[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return VMK_E_LAUNCH;
+  void* ptr = __atomic_load_n(&cached[dev], __ATOMIC_ACQUIRE);
+  if (ptr == nullptr) {
+    // first call on this device: resolve the array's device address (not to be done during stream capture)
+    if (cudaGetSymbolAddress(&ptr, g_spec_scratch) != cudaSuccess || ptr == nullptr) return VMK_E_LAUNCH;
+    __atomic_store_n(&cached[dev], ptr, __ATOMIC_RELEASE);
+  }
+  *out = ptr;
+  return VMK_OK;
+}
+
+extern "C" int vmk_spec_verify_noalloc(const void* q, const void* k, const void* v, const uint32_t* bits,
+                                       int bits_words, void* out, int B, int kd, int Hq, int Hkv, int D, int L,
+                                       int32_t* status, void* stream) {
+  if (!out) return VMK_E_BADARG;
+  if (B <= 0 || kd <= 0 || Hq <= 0 || Hkv <= 0 || L <= 0 || bits_words <= 0) return VMK_E_BADARG;
+  if (D != kHD || Hq % Hkv != 0 || Hq / Hkv > 16) return VMK_E_UNSUPPORTED;
+  if (plan_spec(B, kd, Hq, Hkv, 0, L).ws_bytes > (size_t)VMK_SPEC_NOALLOC_SCRATCH_BYTES) return VMK_E_TOO_LARGE;
+  void* ws = nullptr;
+  const int rc = spec_scratch_address(&ws);
+  if (rc) return rc;
+  return spec_impl(q, k, v, bits, bits_words, out, B, kd, Hq, Hkv, D, L, 0, L, nullptr, nullptr, nullptr, ws,
+                   (size_t)VMK_SPEC_NOALLOC_SCRATCH_BYTES, status, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int vmk_lse_merge(const float* m, const float* l, const float* o, int parts, int rows, int D, void* out,
                              void* stream) {
   if (!m || !l || !o || !out || parts <= 0 || rows <= 0 || D <= 0) return VMK_E_BADARG;
