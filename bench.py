@@ -210,7 +210,12 @@ def stage_times(inp, steps, torch):
     status = _lib.status_word(inp["ik"].device)
     out["indexer_ms"] = avg(lambda: L.vmk_dsa_indexer(inp["iq"].data_ptr(), inp["ik"].data_ptr(), inp["w"].data_ptr(),
                                                       None, scores.data_ptr(), B, Lk, status.data_ptr(), st))
-    out["select_ms"] = avg(lambda: L.vmk_dsa_select(scores.data_ptr(), None, idx.data_ptr(), cnt.data_ptr(), B, Lk, st))
+    hist = torch.empty(B, 2048, dtype=torch.int32, device=scores.device)
+    out["indexer_ms"] = avg(lambda: L.vmk_dsa_indexer_hist(inp["iq"].data_ptr(), inp["ik"].data_ptr(),
+                                                           inp["w"].data_ptr(), None, scores.data_ptr(), hist.data_ptr(),
+                                                           B, Lk, status.data_ptr(), st))
+    out["select_ms"] = avg(lambda: L.vmk_dsa_select_hist(scores.data_ptr(), hist.data_ptr(), None, idx.data_ptr(),
+                                                         cnt.data_ptr(), B, Lk, st))
     out["attend_ms"] = avg(lambda: dsa_b200.attend(inp["q"], inp["kv"], idx, cnt))
     return out
 
@@ -269,12 +274,70 @@ def side_line(config, torch, steps):
         torch.cuda.synchronize()
         if i >= 3:
             times.append(a.elapsed_time(b))
-    ms = statistics.median(times)
+    ms_call = statistics.median(times)
+    # The reference's timing method (bench.py:61-76 there): a chain of 16 "layers" on distinct input sets, each
+    # layer's query being the previous layer's output, here captured once in a CUDA graph and replayed after an
+    # L2 flush, so that host launch overhead is off the clock.
+    ms = None
+    try:
+        ms = chain_time(opname, fn, inp, flush, torch, steps)
+    except Exception as e:                        # a capture problem must not lose the per-call number
+        chain_err = f"{type(e).__name__}: {str(e)[:200]}"
     peak, kind = peaks()
-    return dict(workload=name, rows_per_s=rows / (ms * 1e-3), ms=ms, algorithmic_mb=nbytes / 1e6,
-                hbm_gbs=nbytes / (ms * 1e-3) / 1e9, hbm_frac=nbytes / (ms * 1e-3) / 1e9 / peak, peak=f"of {kind}",
-                tflops=flops / (ms * 1e-3) / 1e12, l2="flushed between iterations",
-                timing="CUDA events around one kernel(...) call, host launch overhead included")
+    line = dict(workload=name, algorithmic_mb=nbytes / 1e6, peak=f"of {kind}", l2="flushed between iterations",
+                ms_single_call=ms_call, single_call_hbm_frac=nbytes / (ms_call * 1e-3) / 1e9 / peak)
+    if ms is None:
+        ms, line["chain_error"] = ms_call, chain_err
+        line["timing"] = "CUDA events around one kernel(...) call, host launch overhead included"
+    else:
+        line["timing"] = "per layer of a 16-layer chain (output -> next query) replayed as a CUDA graph"
+    line.update(rows_per_s=rows / (ms * 1e-3), ms=ms, hbm_gbs=nbytes / (ms * 1e-3) / 1e9,
+                hbm_frac=nbytes / (ms * 1e-3) / 1e9 / peak, tflops=flops / (ms * 1e-3) / 1e12)
+    return line
+
+
+def chain_time(opname, fn, inp, flush, torch, rounds, layers=16):
+    """Median time per layer of a `layers`-long chain over up to 8 distinct copies of the inputs (within
+    1.5 GiB), replayed from a CUDA graph; the L2 is flushed before every replay."""
+    per_set = sum(v.numel() * v.element_size() for v in inp.values() if v is not None)
+    n_distinct = int(max(1, min(8, (3 << 29) // max(per_set, 1))))
+    g = torch.Generator(device="cuda")
+    g.manual_seed(77)
+    sets = [inp]
+    for _ in range(1, n_distinct):
+        cp = {}
+        for k, v in inp.items():
+            if v is None or not v.is_floating_point() or k in ("w",):
+                cp[k] = v
+            else:
+                cp[k] = torch.randn(v.shape, generator=g, device="cuda", dtype=torch.float32).to(v.dtype)
+        sets.append(cp)
+
+    def run_chain():
+        q = sets[0]["q"]
+        for i in range(layers):
+            kw = dict(sets[i % n_distinct])
+            kw["q"] = q
+            out = fn(**kw)
+            q = torch.cat([out, kw["q"][..., 512:]], dim=-1) if opname == "dsa" else out
+        return q
+
+    run_chain()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        run_chain()
+    times = []
+    for i in range(rounds + 2):
+        flush.fill_(i & 0xff)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        if i >= 2:
+            times.append(a.elapsed_time(b) / layers)
+    return statistics.median(times)
 
 
 # ------------------------------------------------------------------------------------------------ CPU arm

@@ -117,6 +117,15 @@ VMK_API int vmk_dsa_indexer(const void* iq, const void* ik, const float* w, cons
  * idx (B,2048) ascending, entries beyond cnt[b] are 0. */
 VMK_API int vmk_dsa_select(const float* scores, const int32_t* lens, int32_t* idx, int32_t* cnt, int B, int L,
                    void* stream);
+/* Stages 1 and 2 with the first level of the select fused into the indexer, as vmk_dsa_decode runs them
+ * (the reference fuses a histogram of the top key bits into its indexer the same way,
+ * kernels/dsa_opus55_v7.py:629-661, and its select starts from it, 124-150).  hist (B,2048) uint32 is
+ * zeroed and then filled by vmk_dsa_indexer_hist: hist[b][k] counts the valid positions of request b whose
+ * score key has k as its top 11 bits (key = order-preserving map of the fp32 score, NaN -> 0, -0 = +0). */
+VMK_API int vmk_dsa_indexer_hist(const void* iq, const void* ik, const float* w, const int32_t* lens,
+                                 float* scores, uint32_t* hist, int B, int L, int32_t* status, void* stream);
+VMK_API int vmk_dsa_select_hist(const float* scores, const uint32_t* hist, const int32_t* lens, int32_t* idx,
+                                int32_t* cnt, int B, int L, void* stream);
 /* Stage 3 (kernels/dsa_opus55_v7.py:839-871): absorbed-MLA attention over the selected rows. */
 VMK_API size_t vmk_dsa_attend_workspace_bytes(int B);
 VMK_API int vmk_dsa_attend(const void* q, const void* kv, const int32_t* idx, const int32_t* cnt, void* out,

@@ -120,6 +120,28 @@ def test_indexer_stage(B, L):
     assert np.abs(s - s64).max() <= 2e-6 * np.abs(s64).max()
 
 
+@pytest.mark.parametrize("B,L,dist", [(2, 4096, "randn"), (3, 9000, "ragged"), (1, 70001, "randn"), (2, 40000, "needle")])
+def test_fused_histogram_and_select_from_it(B, L, dist):
+    """The histogram the indexer accumulates is exactly the histogram of the top 11 key bits of the scores
+    it wrote, and the select that starts from it returns the same list as the select that builds its own."""
+    inp = op.make_inputs(dict(B=B, L=L), seed=29, dist=dist)
+    d = _verify.device_inputs("dsa", inp)
+    scores, hist = dsa_b200.indexer_hist(d["iq"], d["ik"], d["w"], d["lens"])
+    _verify.assert_clean_status()
+    s, h = scores.cpu().numpy(), hist.cpu().numpy()
+    for b in range(B):
+        n = L if inp["lens"] is None else int(inp["lens"][b])
+        if n <= 2048:
+            assert (h[b] == 0).all()
+            continue
+        u = (s[b, :n] + np.float32(0.0)).view(np.uint32)
+        key = np.where(u & 0x80000000, ~u, u | 0x80000000).astype(np.uint32)
+        assert np.array_equal(np.bincount(key >> 21, minlength=2048), h[b])
+    a_idx, a_cnt = dsa_b200.select(scores, d["lens"], hist=hist)
+    b_idx, b_cnt = dsa_b200.select(scores, d["lens"])
+    assert torch.equal(a_idx, b_idx) and torch.equal(a_cnt, b_cnt)
+
+
 def test_indexer_ragged_leaves_tail_untouched():
     inp = op.make_inputs(dict(B=3, L=6000), seed=18, dist="ragged")
     d = _verify.device_inputs("dsa", inp)

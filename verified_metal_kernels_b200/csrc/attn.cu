@@ -35,42 +35,48 @@ struct CombineParams {
   float* po;
 };
 
-// One CTA of 128 threads per output row (outer, head); thread d merges column d over every split.
+constexpr int kMaxParts = 640;     // upper bound of splits merged into one row (both sides together)
+
+// One CTA of 128 threads per output row (outer, head).  The (m, l) pairs of every split are fetched in
+// parallel (one per thread) into shared memory, turned into weights 2^(m - M), and thread d then merges
+// column d with independent loads.  Launched with programmatic stream serialisation: the grid may be
+// scheduled while the split kernel is still running and waits here for its results.
 __global__ void __launch_bounds__(128) combine_kernel(const CombineParams p) {
+  __shared__ float s_w[kMaxParts], s_l[kMaxParts];
+  __shared__ const float* s_o[kMaxParts];
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int row = blockIdx.x;
   const int d = threadIdx.x;
   const int outer = row / p.Hq, hq = row % p.Hq;
   const int h = hq / p.G, g = hq % p.G;
+  const int nA = p.a.nsplit, nB = p.has_b ? p.b.nsplit : 0;
+  const int total = min(nA + nB, kMaxParts);
+  for (int t = d; t < total; t += 128) {
+    const CombineSide& sd = t < nA ? p.a : p.b;
+    const int s = t < nA ? t : t - nA;
+    const int z = (outer / sd.rows_outer) * p.Hkv + h;
+    const int r = (outer % sd.rows_outer) * p.G + g;
+    const size_t i = ((size_t)z * sd.nsplit + s) * sd.MP + r;
+    const float2 ml = *reinterpret_cast<const float2*>(sd.part_ml + i * 2);
+    s_w[t] = ml.x;
+    s_l[t] = ml.y;
+    s_o[t] = sd.part_o + i * kHD;
+  }
+  __syncthreads();
   float M = -INFINITY;
-  size_t baseA, baseB = 0;
-  {
-    const int z = (outer / p.a.rows_outer) * p.Hkv + h;
-    const int r = (outer % p.a.rows_outer) * p.G + g;
-    baseA = ((size_t)z * p.a.nsplit) * p.a.MP + r;
-    for (int s = 0; s < p.a.nsplit; ++s) M = fmaxf(M, p.a.part_ml[(baseA + (size_t)s * p.a.MP) * 2]);
+  for (int t = 0; t < total; ++t) M = fmaxf(M, s_w[t]);
+  __syncthreads();
+  for (int t = d; t < total; t += 128) {
+    const float m = s_w[t];
+    s_w[t] = (m == -INFINITY) ? 0.f : exp2f(m - M);
   }
-  if (p.has_b) {
-    const int z = (outer / p.b.rows_outer) * p.Hkv + h;
-    const int r = (outer % p.b.rows_outer) * p.G + g;
-    baseB = ((size_t)z * p.b.nsplit) * p.b.MP + r;
-    for (int s = 0; s < p.b.nsplit; ++s) M = fmaxf(M, p.b.part_ml[(baseB + (size_t)s * p.b.MP) * 2]);
-  }
+  __syncthreads();
   float acc = 0.f, lsum = 0.f;
-  for (int s = 0; s < p.a.nsplit; ++s) {
-    const size_t i = baseA + (size_t)s * p.a.MP;
-    const float m = p.a.part_ml[i * 2];
-    const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
-    acc += w * p.a.part_o[i * kHD + d];
-    lsum += w * p.a.part_ml[i * 2 + 1];
-  }
-  if (p.has_b) {
-    for (int s = 0; s < p.b.nsplit; ++s) {
-      const size_t i = baseB + (size_t)s * p.b.MP;
-      const float m = p.b.part_ml[i * 2];
-      const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
-      acc += w * p.b.part_o[i * kHD + d];
-      lsum += w * p.b.part_ml[i * 2 + 1];
-    }
+#pragma unroll 8
+  for (int t = 0; t < total; ++t) {
+    const float w = s_w[t];
+    acc += w * s_o[t][d];
+    lsum += w * s_l[t];
   }
   if (p.out != nullptr) {
     p.out[(size_t)row * kHD + d] = __float2half(acc / lsum);
@@ -81,6 +87,22 @@ __global__ void __launch_bounds__(128) combine_kernel(const CombineParams p) {
       p.pl[row] = lsum;
     }
   }
+}
+
+// Launch of the combine pass as a programmatic dependent of the kernel enqueued just before it.
+static int launch_combine(const CombineParams& c, int rows, cudaStream_t stream) {
+  if (c.a.nsplit + (c.has_b ? c.b.nsplit : 0) > kMaxParts) return VMK_E_UNSUPPORTED;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(rows);
+  cfg.blockDim = dim3(128);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return check_launch(cudaLaunchKernelEx(&cfg, combine_kernel, c));
 }
 
 // Merge of `parts` partials per row (used after an exchange between GPUs).
@@ -345,8 +367,7 @@ static int prefix_impl(const void* q, const void* kp, const void* vp, const void
   c.Hkv = Hkv; c.G = G; c.Hq = Hq;
   c.out = static_cast<__half*>(out);
   c.pm = pm; c.pl = plv; c.po = po;
-  combine_kernel<<<N * Hq, 128, 0, stream>>>(c);
-  return check_launch(cudaGetLastError());
+  return launch_combine(c, N * Hq, stream);
 }
 
 static int spec_impl(const void* q, const void* k, const void* v, const uint32_t* bits, int bits_words, void* out,
@@ -391,8 +412,7 @@ static int spec_impl(const void* q, const void* k, const void* v, const uint32_t
   c.Hkv = Hkv; c.G = G; c.Hq = Hq;
   c.out = static_cast<__half*>(out);
   c.pm = pm; c.pl = plv; c.po = po;
-  combine_kernel<<<B * kd * Hq, 128, 0, stream>>>(c);
-  return check_launch(cudaGetLastError());
+  return launch_combine(c, B * kd * Hq, stream);
 }
 
 }  // namespace vmk

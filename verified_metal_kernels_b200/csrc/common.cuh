@@ -89,6 +89,22 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* tm, in
       : "memory");
 }
 
+// L2 eviction policies for streaming loads: data read once should not push reusable data out of L2.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+
+__device__ __forceinline__ void tma_load_3d_hint(void* dst, const CUtensorMap* tm, int x, int y, int z, uint64_t* bar,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, "
+      "%5}], [%2], %6;" ::"r"(smem_u32(dst)),
+      "l"(tm), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "l"(policy)
+      : "memory");
+}
+
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* tm, int x, int y, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -149,6 +165,16 @@ __device__ __forceinline__ float warp_sum(float v) {
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
+
+// Order-preserving 32-bit key of an fp32 score (larger score = larger key); NaN ranks last and the two
+// zeros share a key.  Used by the dsa indexer's fused histogram and by the top-k select.
+__device__ __forceinline__ uint32_t score_key(float x) {
+  if (x != x) return 0u;
+  const uint32_t u = __float_as_uint(x + 0.0f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+constexpr int kSelBins = 2048;        // first radix level: the top 11 bits of the key
+constexpr int kSelShift = 21;
 
 // ------------------------------------------------------------------------------------------------
 // host side

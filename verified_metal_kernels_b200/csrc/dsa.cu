@@ -12,7 +12,9 @@ constexpr int kDK = 576;       // latent row: 512 latent + 64 rope
 constexpr int kDV = 512;       // value = first 512 columns of the row
 
 int indexer_tc_launch(const CUtensorMap& tmIK, const CUtensorMap& tmIQ, const float* w, const int32_t* lens,
-                      float* scores, int B, int L, int32_t* status, cudaStream_t stream);
+                      float* scores, uint32_t* hist, int B, int L, int32_t* status, cudaStream_t stream);
+int select_launch(const float* scores, const uint32_t* hist, const int32_t* lens, int32_t* idx, int32_t* cnt, int B,
+                  int L, cudaStream_t stream);
 
 // ================================================================================================
 // Stage 1, mma.sync variant: scores[b,l] = sum_h w[b,h] * relu(iq[b,h] . ik[b,l])
@@ -412,7 +414,7 @@ static int mla_splits(int B) {
 }
 
 struct DsaPlan {
-  size_t off_scores, off_idx, off_cnt, off_attend, ws_bytes;
+  size_t off_scores, off_idx, off_cnt, off_hist, off_attend, ws_bytes;
 };
 
 static size_t attend_ws(int B) {
@@ -426,7 +428,8 @@ static DsaPlan plan_dsa(int B, int L) {
   pl.off_scores = 0;
   pl.off_idx = align_up((size_t)B * L * 4, 256);
   pl.off_cnt = pl.off_idx + align_up((size_t)B * kTopK * 4, 256);
-  pl.off_attend = pl.off_cnt + align_up((size_t)B * 4, 256);
+  pl.off_hist = pl.off_cnt + align_up((size_t)B * 4, 256);
+  pl.off_attend = pl.off_hist + align_up((size_t)B * kSelBins * 4, 256);
   pl.ws_bytes = pl.off_attend + attend_ws(B);
   return pl;
 }
@@ -453,8 +456,8 @@ int indexer_chunks(int B, int tiles) {
   return best;
 }
 
-static int indexer_impl(const void* iq, const void* ik, const float* w, const int32_t* lens, float* scores, int B,
-                        int L, int32_t* status, cudaStream_t stream, int variant) {
+static int indexer_impl(const void* iq, const void* ik, const float* w, const int32_t* lens, float* scores,
+                        uint32_t* hist, int B, int L, int32_t* status, cudaStream_t stream, int variant) {
   if (!iq || !ik || !w || !scores || B <= 0 || L <= 0) return VMK_E_BADARG;
   if (!aligned16(iq) || !aligned16(ik) || B > 65535) return VMK_E_BADARG;
   if (L <= kTopK) return VMK_OK;                        // nothing to rank
@@ -464,7 +467,7 @@ static int indexer_impl(const void* iq, const void* ik, const float* w, const in
   if (rc) return rc;
   rc = make_tmap_3d(&p.tmIQ, iq, kDI, kHI, B, 64, kHI);
   if (rc) return rc;
-  if (variant == 1) return indexer_tc_launch(p.tmIK, p.tmIQ, w, lens, scores, B, L, status, stream);
+  if (variant == 1) return indexer_tc_launch(p.tmIK, p.tmIQ, w, lens, scores, hist, B, L, status, stream);
   p.w = w; p.lens = lens; p.scores = scores; p.B = B; p.L = L; p.status = status;
   static int configured_dev = -1;
   int dev = 0;
@@ -529,7 +532,22 @@ extern "C" VMK_API int vmk_dsa_set_indexer_variant(int v) {
 
 extern "C" int vmk_dsa_indexer(const void* iq, const void* ik, const float* w, const int32_t* lens, float* scores,
                                int B, int L, int32_t* status, void* stream) {
-  return indexer_impl(iq, ik, w, lens, scores, B, L, status, static_cast<cudaStream_t>(stream), g_indexer_variant);
+  return indexer_impl(iq, ik, w, lens, scores, nullptr, B, L, status, static_cast<cudaStream_t>(stream),
+                      g_indexer_variant);
+}
+
+extern "C" int vmk_dsa_indexer_hist(const void* iq, const void* ik, const float* w, const int32_t* lens, float* scores,
+                                    uint32_t* hist, int B, int L, int32_t* status, void* stream) {
+  if (!hist) return VMK_E_BADARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(hist, 0, (size_t)B * kSelBins * 4, st) != cudaSuccess) return VMK_E_LAUNCH;
+  return indexer_impl(iq, ik, w, lens, scores, hist, B, L, status, st, 1);
+}
+
+extern "C" int vmk_dsa_select_hist(const float* scores, const uint32_t* hist, const int32_t* lens, int32_t* idx,
+                                   int32_t* cnt, int B, int L, void* stream) {
+  if (!hist) return VMK_E_BADARG;
+  return select_launch(scores, hist, lens, idx, cnt, B, L, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" size_t vmk_dsa_attend_workspace_bytes(int B) { return B > 0 ? attend_ws(B) : 0; }
@@ -551,9 +569,18 @@ extern "C" int vmk_dsa_decode(const void* q, const void* kv, const void* iq, con
   float* scores = reinterpret_cast<float*>(base + pl.off_scores);
   int32_t* idx = idx_out ? idx_out : reinterpret_cast<int32_t*>(base + pl.off_idx);
   int32_t* cnt = cnt_out ? cnt_out : reinterpret_cast<int32_t*>(base + pl.off_cnt);
-  int rc = vmk_dsa_indexer(iq, ik, w, lens, scores, B, L, status, stream);
+  // The tcgen05 indexer also accumulates the first radix level of the select (a 2048-bin histogram per
+  // request); the mma.sync variant does not, and the select then builds it in a pass of its own.
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint32_t* hist = nullptr;
+  if (g_indexer_variant == 1 && L > kTopK) {
+    hist = reinterpret_cast<uint32_t*>(base + pl.off_hist);
+    if (cudaMemsetAsync(hist, 0, (size_t)B * kSelBins * 4, st) != cudaSuccess) return VMK_E_LAUNCH;
+  }
+  int rc = indexer_impl(iq, ik, w, lens, scores, hist, B, L, status, st, g_indexer_variant);
   if (rc) return rc;
-  rc = vmk_dsa_select(scores, lens, idx, cnt, B, L, stream);
+  if (!idx || !cnt) return VMK_E_BADARG;
+  rc = select_launch(scores, hist, lens, idx, cnt, B, L, st);
   if (rc) return rc;
   return vmk_dsa_attend(q, kv, idx, cnt, out, B, L, base + pl.off_attend, attend_ws(B), status, stream);
 }

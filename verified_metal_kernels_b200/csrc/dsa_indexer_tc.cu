@@ -24,8 +24,9 @@ constexpr int kTileBytes = kTile * kDI * 2;            // 32 KiB
 constexpr int kIqBytes = kHI * kDI * 2;                // 16 KiB
 constexpr int kTmemCols = kAccs * kHI;                 // 256
 constexpr int kTcThreads = 192;
-// ring | iq | w | barriers | tmem base
-constexpr int kTcSmem = kStages * kTileBytes + kIqBytes + kHI * 4 + (2 * kStages + 2 * kAccs + 1) * 8 + 16 + 1024;
+// ring | iq | w | histogram | barriers | tmem base
+constexpr int kTcSmem =
+    kStages * kTileBytes + kIqBytes + kHI * 4 + kSelBins * 4 + (2 * kStages + 2 * kAccs + 1) * 8 + 16 + 1024;
 
 struct TcParams {
   CUtensorMap tmIK;      // (B, L, 128) box (64, 128, 1), 128-byte swizzle
@@ -33,6 +34,7 @@ struct TcParams {
   const float* w;
   const int32_t* lens;
   float* scores;
+  uint32_t* hist;        // (B, 2048) counts of the top 11 key bits, accumulated with atomics; nullable
   int B, L;
   int32_t* status;
 };
@@ -47,7 +49,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sIQ = smem + kStages * kTileBytes;
   float* sW = reinterpret_cast<float*>(sIQ + kIqBytes);
-  uint64_t* full = reinterpret_cast<uint64_t*>(sW + kHI);
+  uint32_t* sHist = reinterpret_cast<uint32_t*>(sW + kHI);
+  uint64_t* full = reinterpret_cast<uint64_t*>(sHist + kSelBins);
   uint64_t* empty = full + kStages;
   uint64_t* acc_full = empty + kStages;
   uint64_t* acc_empty = acc_full + kAccs;
@@ -79,6 +82,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
     fence_mbar_init();
   }
   if (tid < kHI) sW[tid] = p.w[b * kHI + tid];
+  if (p.hist != nullptr)
+    for (int i = tid; i < kSelBins; i += kTcThreads) sHist[i] = 0u;
   if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
   tc_fence_before();
   __syncthreads();
@@ -160,7 +165,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
 #pragma unroll
       for (int h = 0; h < 32; ++h) s += sW[32 + h] * relu_nan(__uint_as_float(r1[h]));
       const int pos = (t0 + j) * kTile + row;
-      if (pos < n) dst[pos] = s;
+      if (pos < n) {
+        dst[pos] = s;
+        // first level of the top-k radix select, fused here so that the select pass starts one level down
+        if (p.hist != nullptr) atomicAdd(&sHist[score_key(s) >> kSelShift], 1u);
+      }
     }
   }
   if (timed_out) report(p.status, kStatusTimeout);
@@ -172,17 +181,23 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
     tc_fence_after();
     tmem_free(tmem_base, kTmemCols);
   }
+  if (p.hist != nullptr) {
+    for (int i = tid; i < kSelBins; i += kTcThreads) {
+      const uint32_t c = sHist[i];
+      if (c != 0u) atomicAdd(&p.hist[(size_t)b * kSelBins + i], c);
+    }
+  }
 }
 
 int indexer_chunks(int B, int tiles);
 
 int indexer_tc_launch(const CUtensorMap& tmIK, const CUtensorMap& tmIQ, const float* w, const int32_t* lens,
-                      float* scores, int B, int L, int32_t* status, cudaStream_t stream) {
+                      float* scores, uint32_t* hist, int B, int L, int32_t* status, cudaStream_t stream) {
   TcParams p;
   memset(&p, 0, sizeof(p));
   p.tmIK = tmIK;
   p.tmIQ = tmIQ;
-  p.w = w; p.lens = lens; p.scores = scores; p.B = B; p.L = L; p.status = status;
+  p.w = w; p.lens = lens; p.scores = scores; p.hist = hist; p.B = B; p.L = L; p.status = status;
   static int configured_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);

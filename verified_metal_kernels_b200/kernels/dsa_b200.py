@@ -67,16 +67,37 @@ def indexer(iq, ik, w, lens=None):
     return scores
 
 
-def select(scores, lens=None):
-    """Stage 2 alone: (idx (B,2048) int32 ascending, cnt (B,) int32)."""
+def indexer_hist(iq, ik, w, lens=None):
+    """Stage 1 with the fused first radix level: (scores (B,L) fp32, hist (B,2048) int32)."""
+    B, L = ik.shape[0], ik.shape[1]
+    need(iq, "iq", torch.float16, shape=(B, HI, DI))
+    need(ik, "ik", torch.float16, shape=(B, L, DI))
+    need(w, "w", torch.float32, shape=(B, HI))
+    lib = _lib.lib()
+    with torch.cuda.device(ik.device):
+        scores = torch.zeros(B, L, dtype=torch.float32, device=ik.device)
+        hist = torch.empty(B, 2048, dtype=torch.int32, device=ik.device)
+        rc = lib.vmk_dsa_indexer_hist(_lib.ptr(iq), _lib.ptr(ik), _lib.ptr(w), _lib.ptr(lens), _lib.ptr(scores),
+                                      _lib.ptr(hist), B, L, _lib.ptr(_lib.status_word(ik.device)),
+                                      torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "vmk_dsa_indexer_hist")
+    return scores, hist
+
+
+def select(scores, lens=None, hist=None):
+    """Stage 2 alone: (idx (B,2048) int32 ascending, cnt (B,) int32).  `hist` is stage 1's fused histogram."""
     need(scores, "scores", torch.float32, dims=2)
     B, L = scores.shape
     lib = _lib.lib()
     with torch.cuda.device(scores.device):
         idx = torch.empty(B, TOPK, dtype=torch.int32, device=scores.device)
         cnt = torch.empty(B, dtype=torch.int32, device=scores.device)
-        rc = lib.vmk_dsa_select(_lib.ptr(scores), _lib.ptr(lens), _lib.ptr(idx), _lib.ptr(cnt), B, L,
-                                torch.cuda.current_stream().cuda_stream)
+        if hist is None:
+            rc = lib.vmk_dsa_select(_lib.ptr(scores), _lib.ptr(lens), _lib.ptr(idx), _lib.ptr(cnt), B, L,
+                                    torch.cuda.current_stream().cuda_stream)
+        else:
+            rc = lib.vmk_dsa_select_hist(_lib.ptr(scores), _lib.ptr(hist), _lib.ptr(lens), _lib.ptr(idx), _lib.ptr(cnt),
+                                         B, L, torch.cuda.current_stream().cuda_stream)
     _lib.check(rc, "vmk_dsa_select")
     return idx, cnt
 
