@@ -248,19 +248,34 @@ __global__ void __launch_bounds__(256, 1) mla_kernel(const MlaParams p) {
     const uint8_t* st = sK + (j & 1) * kMlaStageBytes;
 
     // S = Q K^T : 16 heads x 16 keys, K = 576
-    float sacc[2][4];
+    // Two accumulator sets (even / odd K steps) halve the dependent-MMA chain of the 36-step reduction.
+    float sacc[2][4], sodd[2][4];
 #pragma unroll
-    for (int n = 0; n < 2; ++n) sacc[n][0] = sacc[n][1] = sacc[n][2] = sacc[n][3] = 0.f;
-#pragma unroll 4
-    for (int kk = 0; kk < kDK / 16; ++kk) {
-      uint32_t a[4], bb[4];
-      ldsm_x4(a, smem_u32(sQ + (rt * 16 + (lane & 15)) * kRowStride + (kk * 2 + (lane >> 4)) * 16));
-      const int mi = lane >> 3;
-      const int key = sl * 16 + (mi >> 1) * 8 + (lane & 7);
-      ldsm_x4(bb, smem_u32(st + key * kRowStride + (kk * 2 + (mi & 1)) * 16));
-      mma_16816(sacc[0], a, bb[0], bb[1]);
-      mma_16816(sacc[1], a, bb[2], bb[3]);
+    for (int n = 0; n < 2; ++n) {
+      sacc[n][0] = sacc[n][1] = sacc[n][2] = sacc[n][3] = 0.f;
+      sodd[n][0] = sodd[n][1] = sodd[n][2] = sodd[n][3] = 0.f;
     }
+    {
+      const int mi = lane >> 3;
+      const uint32_t qa = smem_u32(sQ + (rt * 16 + (lane & 15)) * kRowStride + (lane >> 4) * 16);
+      const uint32_t ka = smem_u32(st + (sl * 16 + (mi >> 1) * 8 + (lane & 7)) * kRowStride + (mi & 1) * 16);
+#pragma unroll 6
+      for (int kk = 0; kk < kDK / 16; kk += 2) {
+        uint32_t a0[4], b0[4], a1[4], b1[4];
+        ldsm_x4(a0, qa + kk * 32);
+        ldsm_x4(b0, ka + kk * 32);
+        ldsm_x4(a1, qa + kk * 32 + 32);
+        ldsm_x4(b1, ka + kk * 32 + 32);
+        mma_16816(sacc[0], a0, b0[0], b0[1]);
+        mma_16816(sacc[1], a0, b0[2], b0[3]);
+        mma_16816(sodd[0], a1, b1[0], b1[1]);
+        mma_16816(sodd[1], a1, b1[2], b1[3]);
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sacc[n][e] += sodd[n][e];
     float bm_lo = -INFINITY, bm_hi = -INFINITY;
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
