@@ -33,7 +33,7 @@ SIGNATURES = {
     "vmk_spec_partial": (_i, [_vp] * 4 + [_i] + [_i] * 8 + [_vp] * 3 + [_vp, _sz, _vp, _vp]),
 }
 # exported for experiments, not part of the documented ABI
-_EXTRA = {"vmk_dsa_set_indexer_variant": (_i, [_i]), "vmk_attn_set_tc": (_i, [_i])}
+_EXTRA = {"vmk_dsa_set_indexer_variant": (_i, [_i]), "vmk_attn_set_tc": (_i, [_i]), "vmk_dsa_set_attend_variant": (_i, [_i])}
 
 _lib = None
 

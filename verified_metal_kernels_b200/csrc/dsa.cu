@@ -13,6 +13,19 @@ constexpr int kDV = 512;       // value = first 512 columns of the row
 
 int indexer_tc_launch(const CUtensorMap& tmIK, const CUtensorMap& tmIQ, const float* w, const int32_t* lens,
                       float* scores, uint32_t* hist, int B, int L, int32_t* status, cudaStream_t stream);
+struct MlaTcParams {
+  const __half* q;
+  const __half* kv;
+  const int32_t* idx;
+  const int32_t* cnt;
+  __half* out;
+  float* part_o;
+  float* part_ml;
+  int B, L, nsplit, split_len;
+  float sc;
+  int32_t* status;
+};
+int mla_tc_launch(const MlaTcParams& p, cudaStream_t stream);   // dsa_mla_tc.cu
 int select_launch(const float* scores, const uint32_t* hist, const int32_t* lens, int32_t* idx, int32_t* cnt, int B,
                   int L, cudaStream_t stream);
 
@@ -421,7 +434,28 @@ __global__ void __launch_bounds__(128) mla_combine_kernel(const float* __restric
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+static int g_attend_variant = 1;    // 0 = warp-level mma.sync kernel, 1 = tcgen05 kernel (default)
+
+// Key splits of the tcgen05 kernel: 2 CTAs (value halves) per request and split, one CTA per SM.  Minimises
+// waves x (blocks per split + a fixed cost of about four blocks for loading Q and draining), and avoids
+// splitting large batches, whose fp32 partials would cost more traffic than the rows themselves.
+static int mla_tc_splits(int B) {
+  const int sms = sm_count();
+  const int blocks = kTopK / 64;
+  if (2 * B >= sms) return 1;
+  long long best_cost = -1;
+  int best = 1;
+  for (int ns = 1; ns <= 16; ++ns) {
+    const int per = cdiv(blocks, ns);
+    const int real = cdiv(blocks, per);
+    const long long cost = (long long)cdiv(2 * B * real, sms) * (per + 4);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = real; }
+  }
+  return best;
+}
+
 static int mla_splits(int B) {
+  if (g_attend_variant == 1) return mla_tc_splits(B);
   int s = sm_count() / (B * (kMH / kMlaHeads));
   if (s < 1) s = 1;
   if (s > kTopK / (2 * kMlaBK)) s = kTopK / (2 * kMlaBK);   // at least two blocks per split
@@ -517,6 +551,15 @@ static int attend_impl(const void* q, const void* kv, const int32_t* idx, const 
     p.part_o = static_cast<float*>(ws);
     p.part_ml = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + align_up((size_t)B * ns * kMH * kDV * 4, 256));
   }
+  if (g_attend_variant == 1) {
+    MlaTcParams t;
+    t.q = p.q; t.kv = p.kv; t.idx = p.idx; t.cnt = p.cnt; t.out = p.out; t.part_o = p.part_o; t.part_ml = p.part_ml;
+    t.B = B; t.L = L; t.nsplit = ns; t.split_len = cdiv(cdiv(kTopK, ns), 64) * 64; t.sc = p.sc; t.status = status;
+    int rc = mla_tc_launch(t, stream);
+    if (rc || ns == 1) return rc;
+    mla_combine_kernel<<<dim3(kMH, B), 128, 0, stream>>>(p.part_o, p.part_ml, ns, p.out);
+    return check_launch(cudaGetLastError());
+  }
   static int configured_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -537,6 +580,13 @@ static int g_indexer_variant = 1;   // 0 = mma.sync (warp-level), 1 = tcgen05 + 
 }  // namespace vmk
 
 using namespace vmk;
+
+// Test hook: chooses the stage-3 implementation (0 = warp-level mma.sync, 1 = tcgen05).
+extern "C" VMK_API int vmk_dsa_set_attend_variant(int v) {
+  if (v != 0 && v != 1) return VMK_E_BADARG;
+  g_attend_variant = v;
+  return VMK_OK;
+}
 
 // Test hook: chooses the stage-1 implementation (0 = mma.sync, 1 = tcgen05).
 extern "C" VMK_API int vmk_dsa_set_indexer_variant(int v) {

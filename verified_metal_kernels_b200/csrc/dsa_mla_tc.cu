@@ -1,0 +1,379 @@
+// `dsa` stage 3 on the 5th-generation tensor cores: absorbed-MLA attention over the selected rows.
+//
+// The shapes fight the machine: 128 heads x 512 fp32 of output is all of tensor memory, and a 128 x 576
+// fp16 query tile is 147 KB of shared memory.  This kernel therefore
+//   * keeps Q in TENSOR MEMORY (288 columns of packed fp16 pairs) and feeds it to the MMA as the A operand
+//     straight from there, so shared memory only holds the gathered rows;
+//   * gives each CTA all 128 heads but only HALF of the value columns (grid.y = 2), and accumulates that
+//     half of the output in REGISTERS: every 64-key block the product P.V is written to a 128-column
+//     scratch area of tensor memory, read back and added, first for value columns [0,128) of the half by
+//     softmax group A, then for [128,256) by group B.
+// One CTA = (key split, value half, request), 320 threads:
+//   warps 0-3   softmax group A, warps 4-7 group B: one thread per head and group.  Both groups read the
+//               64 scores of their head from tensor memory (two passes: row max, then exp2 and row sum);
+//               group A also stores P (packed fp16) to tensor memory, the A operand of P.V
+//   warp 8      gathers the selected 576-wide rows by index (cp.async, 8 lanes per row) into a three-stage
+//               ring laid out as nine [64 keys][128 B] blocks with the 128-byte swizzle, i.e. the K-major
+//               operand of Q.K^T and, for its first eight blocks, the MN-major operand of P.V
+//   warp 9      owns tensor memory and issues the MMAs: 36 x (M128 N64 K16, A from tensor memory) for
+//               S = Q.K^T, then 4 + 4 x (M128 N128 K16, A = P from tensor memory) for the two parts of P.V
+// Every mbarrier wait is bounded; a wait that runs out sets the status word and the CTA winds down
+// through the common exit, where tensor memory is freed.
+#include "tcgen05.cuh"
+
+namespace vmk {
+
+constexpr int kMlaTopK = VMK_DSA_TOPK;
+constexpr int kMH = 128, kDK = 576, kDV = 512;
+constexpr int kBK = 64;                               // keys per block
+constexpr int kBlkBytes = kBK * 128;                  // one [64 keys][128 B] swizzled block
+constexpr int kKTile = 9 * kBlkBytes;                 // 72 KiB: 64 gathered rows of 576 fp16
+constexpr int kMlaStages = 3;
+constexpr int kMlaThreads = 320;
+constexpr int kColQ = 0;                              // 288 columns: Q as packed fp16 pairs
+constexpr int kColS = 288;                            // 64 columns: scores
+constexpr int kColT = 352;                            // 128 columns: P.V scratch
+constexpr int kColP = 480;                            // 32 columns: P as packed fp16 pairs
+constexpr int kMlaCols = 512;
+constexpr int kMlaBars = 2 * kMlaStages + 8;
+constexpr int kMlaTcSmem = kMlaStages * kKTile + kMlaBars * 8 + 16 + 1024;
+
+struct MlaTcParams {
+  const __half* q;
+  const __half* kv;
+  const int32_t* idx;
+  const int32_t* cnt;
+  __half* out;
+  float* part_o;       // ((b * nsplit + split) * 128 + head) * 512
+  float* part_ml;      // ((b * nsplit + split) * 128 + head) * 2
+  int B, L, nsplit, split_len;
+  float sc;
+  int32_t* status;
+};
+
+// D[tmem] (+)= A[tmem] * B[smem descriptor]
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 db;\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "mov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n"
+      "}\n" ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;                                   // [stages][9 blocks][64 keys][128 B]
+  uint64_t* full = reinterpret_cast<uint64_t*>(sK + kMlaStages * kKTile);   // gathered tile landed (32 producer lanes)
+  uint64_t* empty = full + kMlaStages;                  // tile consumed by Q.K^T and P.V       (MMA commit)
+  uint64_t* q_full = empty + kMlaStages;                // Q stored to tensor memory            (4 warps)
+  uint64_t* s_full = q_full + 1;                        // scores ready                         (MMA commit)
+  uint64_t* s_free = s_full + 1;                        // scores consumed                      (8 warps)
+  uint64_t* p_full = s_free + 1;                        // P stored to tensor memory            (4 warps)
+  uint64_t* pva_done = p_full + 1;                      // first half of P.V in the scratch     (MMA commit)
+  uint64_t* pvb_done = pva_done + 1;                    // second half                          (MMA commit)
+  uint64_t* ta_free = pvb_done + 1;                     // group A has read the scratch         (4 warps)
+  uint64_t* tb_free = ta_free + 1;                      // group B has read the scratch         (4 warps)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tb_free + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int split = blockIdx.x, half = blockIdx.y, b = blockIdx.z;
+  const int nb = max(0, min(p.cnt[b], kMlaTopK));
+  const int k0 = split * p.split_len;
+  const int k1 = min(nb, k0 + p.split_len);
+  const int nblk = k1 > k0 ? (k1 - k0 + kBK - 1) / kBK : 0;
+
+  if (tid == 0) {
+    for (int s = 0; s < kMlaStages; ++s) {
+      mbar_init(&full[s], 32);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(q_full, 4);
+    mbar_init(s_full, 1);
+    mbar_init(s_free, 8);
+    mbar_init(p_full, 4);
+    mbar_init(pva_done, 1);
+    mbar_init(pvb_done, 1);
+    mbar_init(ta_free, 4);
+    mbar_init(tb_free, 4);
+    fence_mbar_init();
+  }
+  if (warp == 9) tmem_alloc(tmem_slot, kMlaCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  bool timed_out = false;
+  if (warp == 8) {
+    // ------------------------------------------------------------------------------ gather producer
+    const __half* kvb = p.kv + (size_t)b * p.L * kDK;
+    const int32_t* idxb = p.idx + (size_t)b * kMlaTopK;
+    const int rsub = lane >> 3, c8 = lane & 7;          // 4 rows per instruction, 8 lanes (128 B) per row
+    for (int j = 0; j < nblk; ++j) {
+      const int s = j % kMlaStages;
+      if (j >= kMlaStages) {
+        const bool ok = mbar_wait(&empty[s], (uint32_t)(((j / kMlaStages) - 1) & 1));
+        if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
+      }
+      uint8_t* st = sK + s * kKTile;
+      // this lane's two candidate row indices of the block: rows lane and lane + 32
+      const int ka = k0 + j * kBK + lane, kb2 = ka + 32;
+      int ia = ka < k1 ? idxb[ka] : -1, ib = kb2 < k1 ? idxb[kb2] : -1;
+      if (ia >= p.L || ib >= p.L) {
+        report(p.status, kStatusBadIndex);
+        ia = ia >= p.L ? 0 : ia;
+        ib = ib >= p.L ? 0 : ib;
+      }
+#pragma unroll 4
+      for (int g = 0; g < 16; ++g) {
+        const int row = g * 4 + rsub;
+        const int ridx = (g < 8) ? __shfl_sync(0xffffffffu, ia, row & 31) : __shfl_sync(0xffffffffu, ib, row & 31);
+        const bool valid = ridx >= 0;
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(kvb + (size_t)(valid ? ridx : 0) * kDK) + c8 * 16;
+        uint8_t* dst = st + row * 128 + ((c8 ^ (row & 7)) << 4);
+#pragma unroll
+        for (int blk = 0; blk < 9; ++blk) cp_async16(dst + blk * kBlkBytes, src + blk * 128, valid ? 16 : 0);
+      }
+      cp_async_commit();
+      if (j >= 1) {                                     // block j-1 has landed: publish it to the async proxy
+        cp_async_wait<1>();
+        fence_proxy_async();
+        mbar_arrive(&full[(j - 1) % kMlaStages]);
+      }
+    }
+    if (nblk > 0 && !timed_out) {
+      cp_async_wait<0>();
+      fence_proxy_async();
+      mbar_arrive(&full[(nblk - 1) % kMlaStages]);
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && nblk > 0) {
+      constexpr uint32_t idesc_qk = umma_idesc_f16(128, kBK, 0);
+      constexpr uint32_t idesc_pv = umma_idesc_f16(128, 128, 1);
+      const uint32_t hi_k = (uint32_t)(umma_desc_sw128(0) >> 32);
+      const uint32_t hi_v = (uint32_t)(umma_desc_sw128_mn(0, kBlkBytes, 1024) >> 32);
+      const uint32_t lo_k0 = (uint32_t)umma_desc_sw128(0), lo_v0 = (uint32_t)umma_desc_sw128_mn(0, kBlkBytes, 1024);
+      const uint32_t k_lo = lo_k0 + (smem_u32(sK) >> 4), v_lo = lo_v0 + (smem_u32(sK) >> 4);
+      const uint32_t tQ = tmem_base + kColQ, tS = tmem_base + kColS, tT = tmem_base + kColT, tP = tmem_base + kColP;
+      // both 128-column parts of P_i . V_i, through the scratch; releases the tile
+      auto issue_pv = [&](int i) -> bool {
+        const uint32_t vb = v_lo + (i % kMlaStages) * (kKTile >> 4) + (half * 4) * (kBlkBytes >> 4);
+        if (!mbar_wait(p_full, (uint32_t)(i & 1))) return false;
+        if (i >= 1 && !mbar_wait(tb_free, (uint32_t)((i - 1) & 1))) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_f16_ts(tT, tP + k * 8, vb + k * (2048 >> 4), hi_v, idesc_pv, k > 0 ? 1u : 0u);
+        umma_commit(pva_done);
+        if (!mbar_wait(ta_free, (uint32_t)(i & 1))) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_f16_ts(tT, tP + k * 8, vb + 2 * (kBlkBytes >> 4) + k * (2048 >> 4), hi_v, idesc_pv, k > 0 ? 1u : 0u);
+        umma_commit(pvb_done);
+        umma_commit(&empty[i % kMlaStages]);
+        return true;
+      };
+      if (!mbar_wait(q_full, 0)) timed_out = true;
+      for (int j = 0; j < nblk && !timed_out; ++j) {
+        if (!mbar_wait(&full[j % kMlaStages], (uint32_t)((j / kMlaStages) & 1))) { timed_out = true; break; }
+        if (j >= 1 && !mbar_wait(s_free, (uint32_t)((j - 1) & 1))) { timed_out = true; break; }
+        tc_fence_after();
+        const uint32_t kb_lo = k_lo + (j % kMlaStages) * (kKTile >> 4);
+#pragma unroll 4
+        for (int kk = 0; kk < kDK / 16; ++kk)
+          umma_f16_ts(tS, tQ + kk * 8, kb_lo + (kk >> 2) * (kBlkBytes >> 4) + (kk & 3) * 2, hi_k, idesc_qk,
+                      kk > 0 ? 1u : 0u);
+        umma_commit(s_full);
+        if (j >= 1 && !issue_pv(j - 1)) { timed_out = true; break; }
+      }
+      if (!timed_out && !issue_pv(nblk - 1)) timed_out = true;
+    }
+  } else if (warp < 8) {
+    // ------------------------------------------------------------------------------ softmax groups
+    const int grp = warp >> 2;                            // 0: A (also writes P), 1: B
+    const int quarter = warp & 3;
+    const int head = quarter * 32 + lane;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t tS = lane_base + kColS, tT = lane_base + kColT;
+    uint64_t* my_done = grp == 0 ? pva_done : pvb_done;
+    uint64_t* my_free = grp == 0 ? ta_free : tb_free;
+
+    if (grp == 0) {
+      // this head's query row -> tensor memory, two fp16 per 32-bit column
+      const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)b * kMH + head) * kDK);
+#pragma unroll 1
+      for (int c = 0; c < 9; ++c) {
+        uint32_t r[32];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint4 v = src[c * 8 + i];
+          r[4 * i] = v.x; r[4 * i + 1] = v.y; r[4 * i + 2] = v.z; r[4 * i + 3] = v.w;
+        }
+        tmem_st32(lane_base + kColQ + c * 32, r);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(q_full);
+    }
+
+    float m = -INFINITY, l = 0.f;
+    float o[128];
+#pragma unroll
+    for (int i = 0; i < 128; ++i) o[i] = 0.f;
+
+    // adds the scratch (this group's 128 value columns of P_i . V_i) into the register accumulator
+    auto accumulate = [&](int i) -> bool {
+      const bool ok = mbar_wait(my_done, (uint32_t)(i & 1));
+      if (!__all_sync(0xffffffffu, ok)) return false;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {                       // 16 columns at a time keeps the live registers low
+        uint32_t t[16];
+        tmem_ld16(tT + c * 16, t);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 16; ++e) o[c * 16 + e] += __uint_as_float(t[e]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(my_free);
+      return true;
+    };
+
+    for (int j = 0; j < nblk; ++j) {
+      if (j >= 1 && !accumulate(j - 1)) { timed_out = true; break; }
+      bool ok = mbar_wait(s_full, (uint32_t)(j & 1));
+      if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
+      tc_fence_after();
+      const int kb = k0 + j * kBK;
+      const bool tail = kb + kBK > k1;
+      // pass 1: row maximum
+      float bm = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t s[16];
+        tmem_ld16(tS + c * 16, s);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          float t = __uint_as_float(s[e]) * p.sc;
+          if (tail && kb + c * 16 + e >= k1) t = -INFINITY;
+          bm = fmaxf(bm, t);
+        }
+      }
+      const float m_new = fmaxf(m, bm);
+      const float mu = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = ex2(m - mu);
+      m = m_new;
+      // pass 2: exp2, row sum, P
+      float ps = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t s[16];
+        tmem_ld16(tS + c * 16, s);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          float t = __uint_as_float(s[e]) * p.sc;
+          if (tail && kb + c * 16 + e >= k1) t = -INFINITY;
+          const float pv = ex2(t - mu);
+          ps += pv;
+          s[e] = __float_as_uint(pv);
+        }
+        if (c == 3) {                                     // the scores are no longer needed in tensor memory
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(s_free);
+        }
+        if (grp == 0) {
+          if (c == 0 && j >= 1) {                         // P is free once both parts of P_{j-1} . V_{j-1} are done
+            ok = mbar_wait(pvb_done, (uint32_t)((j - 1) & 1));
+            if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
+          }
+          uint32_t pk[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) pk[e] = pack_half2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1]));
+          tmem_st8(lane_base + kColP + c * 8, pk);
+        }
+      }
+      if (timed_out) break;
+      l = l * alpha + ps;
+#pragma unroll
+      for (int i = 0; i < 128; ++i) o[i] *= alpha;
+      if (grp == 0) {
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full);
+      }
+    }
+    if (!timed_out && nblk > 0 && !accumulate(nblk - 1)) timed_out = true;
+
+    // ---- emit -------------------------------------------------------------------------------------------
+    if (!timed_out) {
+      const int dv0 = half * 256 + grp * 128;
+      if (p.nsplit == 1) {
+        const float inv = 1.f / l;
+        __half* dst = p.out + ((size_t)b * kMH + head) * kDV + dv0;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          uint4 v;
+          v.x = pack_half2(o[8 * i] * inv, o[8 * i + 1] * inv);
+          v.y = pack_half2(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
+          v.z = pack_half2(o[8 * i + 4] * inv, o[8 * i + 5] * inv);
+          v.w = pack_half2(o[8 * i + 6] * inv, o[8 * i + 7] * inv);
+          reinterpret_cast<uint4*>(dst)[i] = v;
+        }
+      } else {
+        const size_t row = ((size_t)b * p.nsplit + split) * kMH + head;
+        float* dst = p.part_o + row * kDV + dv0;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          reinterpret_cast<float4*>(dst)[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+        if (half == 0 && grp == 0) {
+          p.part_ml[row * 2] = m;
+          p.part_ml[row * 2 + 1] = l;
+        }
+      }
+    }
+  }
+  if (timed_out) report(p.status, kStatusTimeout);
+
+  // common exit: every warp arrives, then the allocating warp frees the tensor memory
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_free(tmem_base, kMlaCols);
+  }
+}
+
+int mla_tc_launch(const MlaTcParams& p, cudaStream_t stream) {
+  static int configured_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (configured_dev != dev) {
+    cudaError_t e = cudaFuncSetAttribute(mla_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaTcSmem);
+    if (e != cudaSuccess) return check_launch(e);
+    configured_dev = dev;
+  }
+  mla_tc_kernel<<<dim3(p.nsplit, 2, p.B), kMlaThreads, kMlaTcSmem, stream>>>(p);
+  return check_launch(cudaGetLastError());
+}
+
+}  // namespace vmk

@@ -125,3 +125,9 @@ def set_indexer_variant(name):
     """Chooses the stage-1 implementation: "mma" (mma.sync, warp-level) or "tcgen05" (tensor memory)."""
     rc = _lib.lib().vmk_dsa_set_indexer_variant({"mma": 0, "tcgen05": 1}[name])
     _lib.check(rc, "vmk_dsa_set_indexer_variant")
+
+
+def set_attend_variant(name):
+    """Chooses the stage-3 implementation: "mma" (warp-level mma.sync) or "tcgen05" (tensor memory)."""
+    rc = _lib.lib().vmk_dsa_set_attend_variant({"mma": 0, "tcgen05": 1}[name])
+    _lib.check(rc, "vmk_dsa_set_attend_variant")
