@@ -8,14 +8,15 @@
 //     half of the output in REGISTERS: every 64-key block the product P.V is written to a 128-column
 //     scratch area of tensor memory, read back and added, first for value columns [0,128) of the half by
 //     softmax group A, then for [128,256) by group B.
-// One CTA = (key split, value half, request), 320 threads:
+// One CTA = (key split, value half, request), 384 threads:
 //   warps 0-3   softmax group A, warps 4-7 group B: one thread per head and group.  Both groups read the
 //               64 scores of their head from tensor memory (two passes: row max, then exp2 and row sum);
 //               group A also stores P (packed fp16) to tensor memory, the A operand of P.V
-//   warp 8      gathers the selected 576-wide rows by index (cp.async, 8 lanes per row) into a three-stage
+//   warps 8-10  gather the selected 576-wide rows by index (cp.async, 8 lanes per row, three of the nine
+//               128-byte column blocks per warp) into a three-stage
 //               ring laid out as nine [64 keys][128 B] blocks with the 128-byte swizzle, i.e. the K-major
 //               operand of Q.K^T and, for its first eight blocks, the MN-major operand of P.V
-//   warp 9      owns tensor memory and issues the MMAs: 36 x (M128 N64 K16, A from tensor memory) for
+//   warp 11     owns tensor memory and issues the MMAs: 36 x (M128 N64 K16, A from tensor memory) for
 //               S = Q.K^T, then 4 + 4 x (M128 N128 K16, A = P from tensor memory) for the two parts of P.V
 // Every mbarrier wait is bounded; a wait that runs out sets the status word and the CTA winds down
 // through the common exit, where tensor memory is freed.
@@ -29,14 +30,15 @@ constexpr int kBK = 64;                               // keys per block
 constexpr int kBlkBytes = kBK * 128;                  // one [64 keys][128 B] swizzled block
 constexpr int kKTile = 9 * kBlkBytes;                 // 72 KiB: 64 gathered rows of 576 fp16
 constexpr int kMlaStages = 3;
-constexpr int kMlaThreads = 320;
+constexpr int kMlaThreads = 384;
+constexpr int kMlaProducers = 3;                      // gather warps: one per ring slot
 constexpr int kColQ = 0;                              // 288 columns: Q as packed fp16 pairs
 constexpr int kColS = 288;                            // 64 columns: scores
 constexpr int kColT = 352;                            // 128 columns: P.V scratch
 constexpr int kColP = 480;                            // 32 columns: P as packed fp16 pairs
 constexpr int kMlaCols = 512;
-constexpr int kMlaBars = 2 * kMlaStages + 8;
-constexpr int kMlaTcSmem = kMlaStages * kKTile + kMlaBars * 8 + 16 + 1024;
+constexpr int kMlaBars = 2 * kMlaStages + 12;
+constexpr int kMlaTcSmem = kMlaStages * kKTile + kMlaBars * 8 + 16 + 6 * 128 * 4 + 1024;
 
 struct MlaTcParams {
   const __half* q;
@@ -50,6 +52,14 @@ struct MlaTcParams {
   float sc;
   int32_t* status;
 };
+
+#ifdef VMK_MLA_TIMING
+// Debug build only: cycles the MMA thread of CTA (0,0,0) spends per phase.
+__device__ long long g_mla_timing[16];
+#define MLA_T(slot) do { if (blockIdx.x + blockIdx.y + blockIdx.z == 0) { long long _t1 = clock64(); g_mla_timing[slot] += _t1 - _t0; _t0 = _t1; } } while (0)
+#else
+#define MLA_T(slot) do {} while (0)
+#endif
 
 // D[tmem] (+)= A[tmem] * B[smem descriptor]
 __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
@@ -80,12 +90,15 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
   uint64_t* q_full = empty + kMlaStages;                // Q stored to tensor memory            (4 warps)
   uint64_t* s_full = q_full + 1;                        // scores ready                         (MMA commit)
   uint64_t* s_free = s_full + 1;                        // scores consumed                      (8 warps)
-  uint64_t* p_full = s_free + 1;                        // P stored to tensor memory            (4 warps)
+  uint64_t* p_full = s_free + 1;                        // P stored to tensor memory            (8 warps)
   uint64_t* pva_done = p_full + 1;                      // first half of P.V in the scratch     (MMA commit)
   uint64_t* pvb_done = pva_done + 1;                    // second half                          (MMA commit)
   uint64_t* ta_free = pvb_done + 1;                     // group A has read the scratch         (4 warps)
   uint64_t* tb_free = ta_free + 1;                      // group B has read the scratch         (4 warps)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tb_free + 1);
+  uint64_t* xch = tb_free + 1;                          // [4] pair of warps that share 32 heads exchanged values
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xch + 4);
+  float* smax = reinterpret_cast<float*>(tmem_slot + 4);    // [2 parities][2 groups][128 heads] block maxima
+  float* ssum = smax + 4 * 128;                             // [2 groups][128 heads] row sums
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int split = blockIdx.x, half = blockIdx.y, b = blockIdx.z;
@@ -102,35 +115,39 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
     mbar_init(q_full, 4);
     mbar_init(s_full, 1);
     mbar_init(s_free, 8);
-    mbar_init(p_full, 4);
+    mbar_init(p_full, 8);
     mbar_init(pva_done, 1);
     mbar_init(pvb_done, 1);
     mbar_init(ta_free, 4);
     mbar_init(tb_free, 4);
+    for (int q = 0; q < 4; ++q) mbar_init(&xch[q], 2);
     fence_mbar_init();
   }
-  if (warp == 9) tmem_alloc(tmem_slot, kMlaCols);
+  if (warp == 11) tmem_alloc(tmem_slot, kMlaCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   bool timed_out = false;
-  if (warp == 8) {
-    // ------------------------------------------------------------------------------ gather producer
+  if (warp >= 8 && warp < 8 + kMlaProducers) {
+    // ------------------------------------------------------------------------------ gather producers
+    // Warp w owns ring slot w: it gathers blocks w, w + 3, ... whole (64 rows x 1152 B) and publishes each as
+    // soon as it has landed, so three blocks are in flight and no warp's wait holds up another's copies.
+    const int s = warp - 8;
     const __half* kvb = p.kv + (size_t)b * p.L * kDK;
     const int32_t* idxb = p.idx + (size_t)b * kMlaTopK;
     const int rsub = lane >> 3, c8 = lane & 7;          // 4 rows per instruction, 8 lanes (128 B) per row
-    for (int j = 0; j < nblk; ++j) {
-      const int s = j % kMlaStages;
+    uint8_t* st = sK + s * kKTile;
+    for (int j = s; j < nblk; j += kMlaStages) {
+      // this lane's two candidate row indices of the block (rows lane and lane + 32), requested early so that
+      // their latency hides behind the wait below
+      const int ka = k0 + j * kBK + lane, kb2 = ka + 32;
+      int ia = ka < k1 ? idxb[ka] : -1, ib = kb2 < k1 ? idxb[kb2] : -1;
       if (j >= kMlaStages) {
         const bool ok = mbar_wait(&empty[s], (uint32_t)(((j / kMlaStages) - 1) & 1));
         if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
       }
-      uint8_t* st = sK + s * kKTile;
-      // this lane's two candidate row indices of the block: rows lane and lane + 32
-      const int ka = k0 + j * kBK + lane, kb2 = ka + 32;
-      int ia = ka < k1 ? idxb[ka] : -1, ib = kb2 < k1 ? idxb[kb2] : -1;
       if (ia >= p.L || ib >= p.L) {
         report(p.status, kStatusBadIndex);
         ia = ia >= p.L ? 0 : ia;
@@ -147,18 +164,11 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
         for (int blk = 0; blk < 9; ++blk) cp_async16(dst + blk * kBlkBytes, src + blk * 128, valid ? 16 : 0);
       }
       cp_async_commit();
-      if (j >= 1) {                                     // block j-1 has landed: publish it to the async proxy
-        cp_async_wait<1>();
-        fence_proxy_async();
-        mbar_arrive(&full[(j - 1) % kMlaStages]);
-      }
-    }
-    if (nblk > 0 && !timed_out) {
       cp_async_wait<0>();
       fence_proxy_async();
-      mbar_arrive(&full[(nblk - 1) % kMlaStages]);
+      mbar_arrive(&full[s]);
     }
-  } else if (warp == 9) {
+  } else if (warp == 11) {
     // ------------------------------------------------------------------------------ MMA issuer
     if (lane == 0 && nblk > 0) {
       constexpr uint32_t idesc_qk = umma_idesc_f16(128, kBK, 0);
@@ -168,47 +178,75 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
       const uint32_t lo_k0 = (uint32_t)umma_desc_sw128(0), lo_v0 = (uint32_t)umma_desc_sw128_mn(0, kBlkBytes, 1024);
       const uint32_t k_lo = lo_k0 + (smem_u32(sK) >> 4), v_lo = lo_v0 + (smem_u32(sK) >> 4);
       const uint32_t tQ = tmem_base + kColQ, tS = tmem_base + kColS, tT = tmem_base + kColT, tP = tmem_base + kColP;
-      // both 128-column parts of P_i . V_i, through the scratch; releases the tile
-      auto issue_pv = [&](int i) -> bool {
-        const uint32_t vb = v_lo + (i % kMlaStages) * (kKTile >> 4) + (half * 4) * (kBlkBytes >> 4);
-        if (!mbar_wait(p_full, (uint32_t)(i & 1))) return false;
-        if (i >= 1 && !mbar_wait(tb_free, (uint32_t)((i - 1) & 1))) return false;
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          umma_f16_ts(tT, tP + k * 8, vb + k * (2048 >> 4), hi_v, idesc_pv, k > 0 ? 1u : 0u);
-        umma_commit(pva_done);
-        if (!mbar_wait(ta_free, (uint32_t)(i & 1))) return false;
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          umma_f16_ts(tT, tP + k * 8, vb + 2 * (kBlkBytes >> 4) + k * (2048 >> 4), hi_v, idesc_pv, k > 0 ? 1u : 0u);
-        umma_commit(pvb_done);
-        umma_commit(&empty[i % kMlaStages]);
-        return true;
-      };
-      if (!mbar_wait(q_full, 0)) timed_out = true;
-      for (int j = 0; j < nblk && !timed_out; ++j) {
-        if (!mbar_wait(&full[j % kMlaStages], (uint32_t)((j / kMlaStages) & 1))) { timed_out = true; break; }
-        if (j >= 1 && !mbar_wait(s_free, (uint32_t)((j - 1) & 1))) { timed_out = true; break; }
-        tc_fence_after();
+#ifdef VMK_MLA_TIMING
+      long long _t0 = clock64();
+#endif
+      // Half of the 36 K steps of S_j = Q . K_j^T (first half starts the accumulator afresh).
+      auto issue_qk_half = [&](int j, int part) {
         const uint32_t kb_lo = k_lo + (j % kMlaStages) * (kKTile >> 4);
-#pragma unroll 4
-        for (int kk = 0; kk < kDK / 16; ++kk)
+#pragma unroll 6
+        for (int kk = part * 18; kk < part * 18 + 18; ++kk)
           umma_f16_ts(tS, tQ + kk * 8, kb_lo + (kk >> 2) * (kBlkBytes >> 4) + (kk & 3) * 2, hi_k, idesc_qk,
                       kk > 0 ? 1u : 0u);
+      };
+      // One 128-column part of P_i . V_i into the scratch.
+      auto issue_pv_part = [&](int i, int part) {
+        const uint32_t vb = v_lo + (i % kMlaStages) * (kKTile >> 4) + (half * 4 + part * 2) * (kBlkBytes >> 4);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_f16_ts(tT, tP + k * 8, vb + k * (2048 >> 4), hi_v, idesc_pv, k > 0 ? 1u : 0u);
+      };
+      // Schedule per block j:  Q.K^T(j+1) first half | P.V(j) part A | Q.K^T(j+1) second half | P.V(j) part B
+      // so that each hand-over of the scratch to a softmax group is covered by half a Q.K^T on the tensor pipe.
+      if (!mbar_wait(q_full, 0) || !mbar_wait(&full[0], 0)) timed_out = true;
+      if (!timed_out) {
+        tc_fence_after();
+        issue_qk_half(0, 0);
+        issue_qk_half(0, 1);
         umma_commit(s_full);
-        if (j >= 1 && !issue_pv(j - 1)) { timed_out = true; break; }
       }
-      if (!timed_out && !issue_pv(nblk - 1)) timed_out = true;
+      for (int j = 0; j < nblk && !timed_out; ++j) {
+        const bool next = j + 1 < nblk;
+        if (next) {
+          if (!mbar_wait(&full[(j + 1) % kMlaStages], (uint32_t)(((j + 1) / kMlaStages) & 1))) { timed_out = true; break; }
+          MLA_T(0);
+          if (!mbar_wait(s_free, (uint32_t)(j & 1))) { timed_out = true; break; }
+          MLA_T(1);
+          tc_fence_after();
+          issue_qk_half(j + 1, 0);
+          MLA_T(2);
+        }
+        if (!mbar_wait(p_full, (uint32_t)(j & 1))) { timed_out = true; break; }
+        MLA_T(3);
+        if (j >= 1 && !mbar_wait(tb_free, (uint32_t)((j - 1) & 1))) { timed_out = true; break; }
+        MLA_T(4);
+        tc_fence_after();
+        issue_pv_part(j, 0);
+        umma_commit(pva_done);
+        MLA_T(5);
+        if (next) {
+          issue_qk_half(j + 1, 1);
+          umma_commit(s_full);
+          MLA_T(2);
+        }
+        if (!mbar_wait(ta_free, (uint32_t)(j & 1))) { timed_out = true; break; }
+        MLA_T(6);
+        tc_fence_after();
+        issue_pv_part(j, 1);
+        umma_commit(pvb_done);
+        umma_commit(&empty[j % kMlaStages]);
+        MLA_T(7);
+      }
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------------------------ softmax groups
-    const int grp = warp >> 2;                            // 0: A (also writes P), 1: B
+    // Group A owns keys [0,32) of every block and value columns [0,128) of this CTA's half; group B keys
+    // [32,64) and value columns [128,256).  The two threads of a head exchange their block maxima through
+    // shared memory, so both follow the same running maximum.
+    const int grp = warp >> 2;
     const int quarter = warp & 3;
     const int head = quarter * 32 + lane;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    const uint32_t tS = lane_base + kColS, tT = lane_base + kColT;
+    const uint32_t tS = lane_base + kColS + grp * 32, tT = lane_base + kColT, tPw = lane_base + kColP + grp * 16;
     uint64_t* my_done = grp == 0 ? pva_done : pvb_done;
     uint64_t* my_free = grp == 0 ? ta_free : tb_free;
 
@@ -216,14 +254,14 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
       // this head's query row -> tensor memory, two fp16 per 32-bit column
       const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)b * kMH + head) * kDK);
 #pragma unroll 1
-      for (int c = 0; c < 9; ++c) {
-        uint32_t r[32];
+      for (int c = 0; c < 18; ++c) {
+        uint32_t r[16];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const uint4 v = src[c * 8 + i];
+        for (int i = 0; i < 4; ++i) {
+          const uint4 v = src[c * 4 + i];
           r[4 * i] = v.x; r[4 * i + 1] = v.y; r[4 * i + 2] = v.z; r[4 * i + 3] = v.w;
         }
-        tmem_st32(lane_base + kColQ + c * 32, r);
+        tmem_st16(lane_base + kColQ + c * 16, r);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -236,8 +274,8 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
 #pragma unroll
     for (int i = 0; i < 128; ++i) o[i] = 0.f;
 
-    // adds the scratch (this group's 128 value columns of P_i . V_i) into the register accumulator
-    auto accumulate = [&](int i) -> bool {
+    // o = (o + scratch) * scale: adds this group's 128 value columns of P_i . V_i, then hands the scratch back
+    auto accumulate = [&](int i, float scale) -> bool {
       const bool ok = mbar_wait(my_done, (uint32_t)(i & 1));
       if (!__all_sync(0xffffffffu, ok)) return false;
       tc_fence_after();
@@ -247,7 +285,7 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
         tmem_ld16(tT + c * 16, t);
         tmem_ld_wait();
 #pragma unroll
-        for (int e = 0; e < 16; ++e) o[c * 16 + e] += __uint_as_float(t[e]);
+        for (int e = 0; e < 16; ++e) o[c * 16 + e] = (o[c * 16 + e] + __uint_as_float(t[e])) * scale;
       }
       tc_fence_before();
       __syncwarp();
@@ -256,73 +294,79 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
     };
 
     for (int j = 0; j < nblk; ++j) {
-      if (j >= 1 && !accumulate(j - 1)) { timed_out = true; break; }
       bool ok = mbar_wait(s_full, (uint32_t)(j & 1));
       if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
       tc_fence_after();
-      const int kb = k0 + j * kBK;
-      const bool tail = kb + kBK > k1;
-      // pass 1: row maximum
+      uint32_t s[32];
+      tmem_ld32(tS, s);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_free);                  // the scores live in registers from here on
+      const int kb = k0 + j * kBK + grp * 32;
+      const bool tail = kb + 32 > k1;
       float bm = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[16];
-        tmem_ld16(tS + c * 16, s);
-        tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          float t = __uint_as_float(s[e]) * p.sc;
-          if (tail && kb + c * 16 + e >= k1) t = -INFINITY;
-          bm = fmaxf(bm, t);
-        }
+      for (int e = 0; e < 32; ++e) {
+        float t = __uint_as_float(s[e]) * p.sc;
+        if (tail && kb + e >= k1) t = -INFINITY;
+        s[e] = __float_as_uint(t);
+        bm = fmaxf(bm, t);
       }
+      smax[((j & 1) * 2 + grp) * 128 + head] = bm;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&xch[quarter]);
+      ok = mbar_wait(&xch[quarter], (uint32_t)(j & 1));
+      if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
+      bm = fmaxf(bm, smax[((j & 1) * 2 + (grp ^ 1)) * 128 + head]);
       const float m_new = fmaxf(m, bm);
       const float mu = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = ex2(m - mu);
       m = m_new;
-      // pass 2: exp2, row sum, P
       float ps = 0.f;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[16];
-        tmem_ld16(tS + c * 16, s);
-        tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          float t = __uint_as_float(s[e]) * p.sc;
-          if (tail && kb + c * 16 + e >= k1) t = -INFINITY;
-          const float pv = ex2(t - mu);
-          ps += pv;
-          s[e] = __float_as_uint(pv);
-        }
-        if (c == 3) {                                     // the scores are no longer needed in tensor memory
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(s_free);
-        }
-        if (grp == 0) {
-          if (c == 0 && j >= 1) {                         // P is free once both parts of P_{j-1} . V_{j-1} are done
-            ok = mbar_wait(pvb_done, (uint32_t)((j - 1) & 1));
-            if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
-          }
-          uint32_t pk[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) pk[e] = pack_half2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1]));
-          tmem_st8(lane_base + kColP + c * 8, pk);
-        }
+      for (int e = 0; e < 32; ++e) {
+        const float pv = ex2(__uint_as_float(s[e]) - mu);
+        ps += pv;
+        s[e] = __float_as_uint(pv);
       }
-      if (timed_out) break;
       l = l * alpha + ps;
+      if (j >= 1) {                                        // P is free once both parts of P_{j-1} . V_{j-1} are done
+        ok = mbar_wait(pvb_done, (uint32_t)((j - 1) & 1));
+        if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
+      }
+      {
+        uint32_t pk[16];
 #pragma unroll
-      for (int i = 0; i < 128; ++i) o[i] *= alpha;
-      if (grp == 0) {
+        for (int e = 0; e < 16; ++e) pk[e] = pack_half2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1]));
+        tmem_st16(tPw, pk);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(p_full);
       }
+      if (grp == 0) {
+        // A: rescale now, then add part A of P_j . V_j as soon as it is there (the MMA warp needs the scratch back)
+#pragma unroll
+        for (int i = 0; i < 128; ++i) o[i] *= alpha;
+        if (!accumulate(j, 1.f)) { timed_out = true; break; }
+      } else {
+        // B: part B of the PREVIOUS block is added here, after this block's P is on its way, and rescaled with it
+        if (j >= 1) {
+          if (!accumulate(j - 1, alpha)) { timed_out = true; break; }
+        }
+      }
     }
-    if (!timed_out && nblk > 0 && !accumulate(nblk - 1)) timed_out = true;
+    if (!timed_out && nblk > 0 && grp == 1 && !accumulate(nblk - 1, 1.f)) timed_out = true;
+    // row sums of the two key halves
+    if (!timed_out) {
+      ssum[grp * 128 + head] = l;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&xch[quarter]);
+      const bool ok = mbar_wait(&xch[quarter], (uint32_t)(nblk & 1));
+      if (!__all_sync(0xffffffffu, ok)) timed_out = true;
+      l += ssum[(grp ^ 1) * 128 + head];
+    }
 
     // ---- emit -------------------------------------------------------------------------------------------
     if (!timed_out) {
@@ -357,11 +401,21 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
   // common exit: every warp arrives, then the allocating warp frees the tensor memory
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == 11) {
     tc_fence_after();
     tmem_free(tmem_base, kMlaCols);
   }
 }
+
+#ifdef VMK_MLA_TIMING
+extern "C" VMK_API int vmk_debug_mla_timing(long long* out, int reset) {
+  long long zero[16] = {0};
+  cudaDeviceSynchronize();
+  if (out) cudaMemcpyFromSymbol(out, g_mla_timing, sizeof(zero));
+  if (reset) cudaMemcpyToSymbol(g_mla_timing, zero, sizeof(zero));
+  return 0;
+}
+#endif
 
 int mla_tc_launch(const MlaTcParams& p, cudaStream_t stream) {
   static int configured_dev = -1;
