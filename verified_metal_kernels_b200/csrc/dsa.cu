@@ -21,11 +21,12 @@ struct MlaTcParams {
   __half* out;
   float* part_o;
   float* part_ml;
-  int B, L, nsplit, split_len;
+  int B, L, ncta;
   float sc;
   int32_t* status;
 };
-int mla_tc_launch(const MlaTcParams& p, cudaStream_t stream);   // dsa_mla_tc.cu
+int mla_tc_launch(const MlaTcParams& p, float* workspace, cudaStream_t stream);   // dsa_mla_tc.cu
+size_t mla_tc_workspace(int B);
 int select_launch(const float* scores, const uint32_t* hist, const int32_t* lens, int32_t* idx, int32_t* cnt, int B,
                   int L, cudaStream_t stream);
 
@@ -436,26 +437,8 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 static int g_attend_variant = 1;    // 0 = warp-level mma.sync kernel, 1 = tcgen05 kernel (default)
 
-// Key splits of the tcgen05 kernel: 2 CTAs (value halves) per request and split, one CTA per SM.  Minimises
-// waves x (blocks per split + a fixed cost of about four blocks for loading Q and draining), and avoids
-// splitting large batches, whose fp32 partials would cost more traffic than the rows themselves.
-static int mla_tc_splits(int B) {
-  const int sms = sm_count();
-  const int blocks = kTopK / 64;
-  if (2 * B >= sms) return 1;
-  long long best_cost = -1;
-  int best = 1;
-  for (int ns = 1; ns <= 16; ++ns) {
-    const int per = cdiv(blocks, ns);
-    const int real = cdiv(blocks, per);
-    const long long cost = (long long)cdiv(2 * B * real, sms) * (per + 4);
-    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = real; }
-  }
-  return best;
-}
-
+// Key splits of the warp-level kernel.
 static int mla_splits(int B) {
-  if (g_attend_variant == 1) return mla_tc_splits(B);
   int s = sm_count() / (B * (kMH / kMlaHeads));
   if (s < 1) s = 1;
   if (s > kTopK / (2 * kMlaBK)) s = kTopK / (2 * kMlaBK);   // at least two blocks per split
@@ -466,10 +449,14 @@ struct DsaPlan {
   size_t off_scores, off_idx, off_cnt, off_hist, off_attend, ws_bytes;
 };
 
+// Stage-3 scratch: the larger of what the two implementations need, so a size queried under one test hook
+// setting is valid under the other.
 static size_t attend_ws(int B) {
   const int ns = mla_splits(B);
-  if (ns == 1) return 256;
-  return align_up((size_t)B * ns * kMH * kDV * 4, 256) + align_up((size_t)B * ns * kMH * 2 * 4, 256);
+  const size_t warp_level =
+      ns == 1 ? 256 : align_up((size_t)B * ns * kMH * kDV * 4, 256) + align_up((size_t)B * ns * kMH * 2 * 4, 256);
+  const size_t tc = mla_tc_workspace(B);
+  return warp_level > tc ? warp_level : tc;
 }
 
 static DsaPlan plan_dsa(int B, int L) {
@@ -536,7 +523,7 @@ static int attend_impl(const void* q, const void* kv, const int32_t* idx, const 
   if (!q || !kv || !idx || !cnt || !out || B <= 0 || L <= 0) return VMK_E_BADARG;
   if (!aligned16(q) || !aligned16(kv) || !aligned16(out) || B > 65535) return VMK_E_BADARG;
   const int ns = mla_splits(B);
-  if (ns > 1 && (!ws || ws_bytes < attend_ws(B) || (reinterpret_cast<uintptr_t>(ws) & 255))) return VMK_E_WORKSPACE;
+  if (!ws || ws_bytes < attend_ws(B) || (reinterpret_cast<uintptr_t>(ws) & 255)) return VMK_E_WORKSPACE;
   MlaParams p;
   memset(&p, 0, sizeof(p));
   p.q = static_cast<const __half*>(q);
@@ -553,12 +540,9 @@ static int attend_impl(const void* q, const void* kv, const int32_t* idx, const 
   }
   if (g_attend_variant == 1) {
     MlaTcParams t;
-    t.q = p.q; t.kv = p.kv; t.idx = p.idx; t.cnt = p.cnt; t.out = p.out; t.part_o = p.part_o; t.part_ml = p.part_ml;
-    t.B = B; t.L = L; t.nsplit = ns; t.split_len = cdiv(cdiv(kTopK, ns), 64) * 64; t.sc = p.sc; t.status = status;
-    int rc = mla_tc_launch(t, stream);
-    if (rc || ns == 1) return rc;
-    mla_combine_kernel<<<dim3(kMH, B), 128, 0, stream>>>(p.part_o, p.part_ml, ns, p.out);
-    return check_launch(cudaGetLastError());
+    t.q = p.q; t.kv = p.kv; t.idx = p.idx; t.cnt = p.cnt; t.out = p.out; t.part_o = nullptr; t.part_ml = nullptr;
+    t.B = B; t.L = L; t.ncta = 0; t.sc = p.sc; t.status = status;
+    return mla_tc_launch(t, static_cast<float*>(ws), stream);
   }
   static int configured_dev = -1;
   int dev = 0;

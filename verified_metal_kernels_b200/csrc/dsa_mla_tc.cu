@@ -4,20 +4,26 @@
 // fp16 query tile is 147 KB of shared memory.  This kernel therefore
 //   * keeps Q in TENSOR MEMORY (288 columns of packed fp16 pairs) and feeds it to the MMA as the A operand
 //     straight from there, so shared memory only holds the gathered rows;
-//   * gives each CTA all 128 heads but only HALF of the value columns (grid.y = 2), and accumulates that
-//     half of the output in REGISTERS: every 64-key block the product P.V is written to a 128-column
+//   * works in UNITS of (request, value half): all 128 heads but 256 of the 512 value columns, whose
+//     output is accumulated in REGISTERS: every 64-key block the product P.V is written to a 128-column
 //     scratch area of tensor memory, read back and added, first for value columns [0,128) of the half by
-//     softmax group A, then for [128,256) by group B.
-// One CTA = (key split, value half, request), 384 threads:
-//   warps 0-3   softmax group A, warps 4-7 group B: one thread per head and group.  Both groups read the
-//               64 scores of their head from tensor memory (two passes: row max, then exp2 and row sum);
-//               group A also stores P (packed fp16) to tensor memory, the A operand of P.V
-//   warps 8-10  gather the selected 576-wide rows by index (cp.async, 8 lanes per row, three of the nine
-//               128-byte column blocks per warp) into a three-stage
-//               ring laid out as nine [64 keys][128 B] blocks with the 128-byte swizzle, i.e. the K-major
-//               operand of Q.K^T and, for its first eight blocks, the MN-major operand of P.V
-//   warp 11     owns tensor memory and issues the MMAs: 36 x (M128 N64 K16, A from tensor memory) for
-//               S = Q.K^T, then 4 + 4 x (M128 N128 K16, A = P from tensor memory) for the two parts of P.V
+//     softmax group A, then for [128,256) by group B;
+//   * is PERSISTENT: the 2 B units of 32 block slots each form one list, cut into equal contiguous ranges,
+//     one per CTA (at most one CTA per SM), so that no wave of CTAs is left part-filled.  A unit that lies
+//     inside one range is written out directly; a unit cut by a range boundary leaves (m, l, o) partials,
+//     at most two per CTA (its first and its last unit), merged by mla_tc_combine_kernel.
+// One CTA = 384 threads:
+//   warps 0-3   softmax group A, warps 4-7 group B: one thread per head and group.  A takes keys [0,32) of
+//               each block, B keys [32,64); the pair of a head exchanges block maxima through shared memory,
+//               both store their share of P (packed fp16) to tensor memory, the A operand of P.V
+//   warps 8-9   gather the selected 576-wide rows by index (cp.async, 8 lanes per row), alternate blocks
+//               each, into a three-slot ring laid out as nine [64 keys][128 B] blocks with the 128-byte
+//               swizzle, i.e. the K-major operand of Q.K^T and, for four of its first eight blocks, the
+//               MN-major operand of P.V
+//   warp 10     issues S = Q.K^T: 36 x (M128 N64 K16, A from tensor memory) per block
+//   warp 11     owns tensor memory and issues P.V: 4 + 4 x (M128 N128 K16, A = P from tensor memory)
+// Ring slots and barrier phases are indexed by the number of blocks the CTA has processed so far, so the
+// pipeline runs on across unit boundaries (the rows of the next unit are gathered while this one drains).
 // Every mbarrier wait is bounded; a wait that runs out sets the status word and the CTA winds down
 // through the common exit, where tensor memory is freed.
 #include "tcgen05.cuh"
@@ -38,7 +44,10 @@ constexpr int kColT = 352;                            // 128 columns: P.V scratc
 constexpr int kColP = 480;                            // 32 columns: P as packed fp16 pairs
 constexpr int kMlaCols = 512;
 constexpr int kMlaBars = 3 * kMlaStages + 12;
-constexpr int kMlaTcSmem = kMlaStages * kKTile + kMlaBars * 8 + 16 + 6 * 128 * 4 + 1024;
+constexpr int kMlaTcSmem = kMlaStages * kKTile + kMlaBars * 8 + 16 + 8 * 128 * 4 + 1024;
+
+constexpr int kUnitSlots = kMlaTopK / kBK;           // 32 block slots per unit
+constexpr int kMinSlotsPerCta = 2;
 
 struct MlaTcParams {
   const __half* q;
@@ -46,20 +55,47 @@ struct MlaTcParams {
   const int32_t* idx;
   const int32_t* cnt;
   __half* out;
-  float* part_o;       // ((b * nsplit + split) * 128 + head) * 512
-  float* part_ml;      // ((b * nsplit + split) * 128 + head) * 2
-  int B, L, nsplit, split_len;
+  float* part_o;       // (((cta * 2 + k) * 64 + column / 4) * 128 + head) * 4: k = 0 the CTA's first unit, 1 its last
+  float* part_ml;      // ((cta * 2 + k) * 128 + head) * 2
+  int B, L, ncta;
   float sc;
   int32_t* status;
 };
 
+// First block slot of CTA c when `total` slots are cut into `ncta` ranges.
+__host__ __device__ __forceinline__ int range_start(int c, int total, int ncta) {
+  return (int)(((long long)c * total) / ncta);
+}
+
+// One unit's share of a CTA's range.
+struct UnitWork {
+  int b, half, k0, k1, nblk;
+  bool whole;
+};
+__device__ __forceinline__ UnitWork unit_work(const MlaTcParams& p, int u, int slot0, int slot1) {
+  UnitWork w;
+  w.b = u >> 1;
+  w.half = u & 1;
+  const int ja = max(slot0 - u * kUnitSlots, 0), jb = min(slot1 - u * kUnitSlots, kUnitSlots);
+  const int nb = max(0, min(p.cnt[w.b], kMlaTopK));
+  w.k0 = ja * kBK;
+  w.k1 = min(nb, jb * kBK);
+  w.nblk = w.k1 > w.k0 ? (w.k1 - w.k0 + kBK - 1) / kBK : 0;
+  w.whole = ja == 0 && jb == kUnitSlots;
+  return w;
+}
+
 #ifdef VMK_MLA_TIMING
 // Debug build only.  Time stamps of blocks 8..15 of CTA (0,0,0): [role][block - 8][event]
 __device__ long long g_mla_trace[4 * 8 * 16];
-#define MLA_E(role, j, ev) do { if (blockIdx.x + blockIdx.y + blockIdx.z == 0 && (j) >= 8 && (j) < 16 && lane == 0) \
+#define MLA_E(role, j, ev) do { if (blockIdx.x == 0 && (j) >= 8 && (j) < 16 && lane == 0) \
     g_mla_trace[((role) * 8 + (j) - 8) * 16 + (ev)] = clock64(); } while (0)
+// CTA-level marks of CTA 0: [mark]
+__device__ long long g_mla_marks[16];
+#define MLA_M(k) do { if (blockIdx.x == 0 && lane == 0) g_mla_marks[k] = clock64(); } while (0)
 #else
 #define MLA_E(role, j, ev) do {} while (0)
+#define MLA_M(k) do {} while (0)
 #endif
 
 // D[tmem] (+)= A[tmem] * B[smem descriptor]
@@ -100,14 +136,12 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
   uint64_t* xch = tb_free + 1;                          // [4] pair of warps that share 32 heads exchanged values
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xch + 4);
   float* smax = reinterpret_cast<float*>(tmem_slot + 4);    // [2 parities][2 groups][128 heads] block maxima
-  float* ssum = smax + 4 * 128;                             // [2 groups][128 heads] row sums
+  float* ssum = smax + 4 * 128;                             // [2 parities][2 groups][128 heads] row sums
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int split = blockIdx.x, half = blockIdx.y, b = blockIdx.z;
-  const int nb = max(0, min(p.cnt[b], kMlaTopK));
-  const int k0 = split * p.split_len;
-  const int k1 = min(nb, k0 + p.split_len);
-  const int nblk = k1 > k0 ? (k1 - k0 + kBK - 1) / kBK : 0;
+  const int total_slots = 2 * p.B * kUnitSlots;
+  const int slot0 = range_start(blockIdx.x, total_slots, p.ncta), slot1 = range_start(blockIdx.x + 1, total_slots, p.ncta);
+  const int u_first = slot0 / kUnitSlots, u_last = (slot1 - 1) / kUnitSlots;
 
   if (tid == 0) {
     for (int s = 0; s < kMlaStages; ++s) {
@@ -133,119 +167,148 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
   const uint32_t tmem_base = *tmem_slot;
 
   bool timed_out = false;
+  if (warp == 0) MLA_M(0);
   if (warp >= 8 && warp < 8 + kMlaProducers) {
     // ------------------------------------------------------------------------------ gather producers
     // The two warps take alternate blocks (64 rows x 1152 B each) and publish each as soon as it has landed, so
     // two blocks are in flight and neither warp's wait holds up the other's copies.
-    const __half* kvb = p.kv + (size_t)b * p.L * kDK;
-    const int32_t* idxb = p.idx + (size_t)b * kMlaTopK;
     const int rsub = lane >> 3, c8 = lane & 7;          // 4 rows per instruction, 8 lanes (128 B) per row
-    for (int j = warp - 8; j < nblk; j += kMlaProducers) {
-      const int s = j % kMlaStages;
-      uint8_t* st = sK + s * kKTile;
-      // this lane's two candidate row indices of the block (rows lane and lane + 32), requested early so that
-      // their latency hides behind the wait below
-      const int ka = k0 + j * kBK + lane, kb2 = ka + 32;
-      int ia = ka < k1 ? idxb[ka] : -1, ib = kb2 < k1 ? idxb[kb2] : -1;
-      if (ia >= p.L || ib >= p.L) {
-        report(p.status, kStatusBadIndex);
-        ia = ia >= p.L ? 0 : ia;
-        ib = ib >= p.L ? 0 : ib;
+    int base = 0;                                       // blocks of the units before this one
+    for (int u = u_first; u <= u_last && !timed_out; ++u) {
+      const UnitWork w = unit_work(p, u, slot0, slot1);
+      const __half* kvb = p.kv + (size_t)w.b * p.L * kDK;
+      const int32_t* idxb = p.idx + (size_t)w.b * kMlaTopK;
+      const int own = w.half * 4, other = 4 - own;
+      if (warp == 9 && u + 1 <= u_last && ((u + 1) >> 1) != w.b) {
+        // the next request's query rows (147 KB) towards L2, long before the softmax threads ask for them
+        const uint8_t* nq = reinterpret_cast<const uint8_t*>(p.q + (size_t)((u + 1) >> 1) * kMH * kDK);
+        for (int i = lane; i < kMH * kDK * 2 / 128; i += 32)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(nq + (size_t)i * 128));
       }
-      // Two passes over the rows.  Pass 0 copies the five column blocks only Q.K^T reads (the other CTA's value
-      // half and the rope block): their part of the slot is free as soon as Q.K^T of block j - 3 is done, one
-      // block earlier than the four value blocks of pass 1, which P.V of block j - 3 still reads.
+      for (int j = (warp - 8 + base) & 1; j < w.nblk; j += kMlaProducers) {
+        const int g = base + j, s = g % kMlaStages;
+        uint8_t* st = sK + s * kKTile;
+        // this lane's two candidate row indices of the block (rows lane and lane + 32), requested early so
+        // that their latency hides behind the wait below
+        const int ka = w.k0 + j * kBK + lane, kb2 = ka + 32;
+        int ia = ka < w.k1 ? idxb[ka] : -1, ib = kb2 < w.k1 ? idxb[kb2] : -1;
+        if (ia >= p.L || ib >= p.L) {
+          report(p.status, kStatusBadIndex);
+          ia = ia >= p.L ? 0 : ia;
+          ib = ib >= p.L ? 0 : ib;
+        }
+        // Two passes over the rows.  Pass 0 copies the five column blocks only Q.K^T reads (the other value
+        // half and the rope block): their part of the slot is free as soon as Q.K^T of block g - 3 is done, one
+        // block earlier than the four value blocks of pass 1, which P.V of block g - 3 still reads.  That only
+        // holds while block g - 3 belongs to this unit: another unit may have the other value half.
 #pragma unroll 1
-      for (int pass = 0; pass < 2; ++pass) {
-        if (j >= kMlaStages) {
-          const bool ok = mbar_wait(pass == 0 ? &empty_k[s] : &empty[s], (uint32_t)(((j / kMlaStages) - 1) & 1));
-          if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
-        }
-        MLA_E(1, j, pass * 2);
-        const int own = half * 4, other = 4 - own;
-#pragma unroll 4
-        for (int g = 0; g < 16; ++g) {
-          const int row = g * 4 + rsub;
-          const int ridx = (g < 8) ? __shfl_sync(0xffffffffu, ia, row & 31) : __shfl_sync(0xffffffffu, ib, row & 31);
-          const bool valid = ridx >= 0;
-          const uint8_t* src = reinterpret_cast<const uint8_t*>(kvb + (size_t)(valid ? ridx : 0) * kDK) + c8 * 16;
-          uint8_t* dst = st + row * 128 + ((c8 ^ (row & 7)) << 4);
+        for (int pass = 0; pass < 2; ++pass) {
+          if (g >= kMlaStages) {
+            const uint32_t par = (uint32_t)(((g / kMlaStages) - 1) & 1);
+            const bool ok = mbar_wait(pass == 0 && j >= kMlaStages ? &empty_k[s] : &empty[s], par);
+            if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
+          }
+          MLA_E(1, g, pass * 2);
           const int first = pass == 0 ? other : own;
+#pragma unroll 4
+          for (int r4 = 0; r4 < 16; ++r4) {
+            const int row = r4 * 4 + rsub;
+            const int ridx = (r4 < 8) ? __shfl_sync(0xffffffffu, ia, row & 31) : __shfl_sync(0xffffffffu, ib, row & 31);
+            const bool valid = ridx >= 0;
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(kvb + (size_t)(valid ? ridx : 0) * kDK) + c8 * 16;
+            uint8_t* dst = st + row * 128 + ((c8 ^ (row & 7)) << 4);
 #pragma unroll
-          for (int blk = 0; blk < 4; ++blk)
-            cp_async16(dst + (first + blk) * kBlkBytes, src + (first + blk) * 128, valid ? 16 : 0);
-          if (pass == 0) cp_async16(dst + 8 * kBlkBytes, src + 8 * 128, valid ? 16 : 0);
+            for (int blk = 0; blk < 4; ++blk)
+              cp_async16(dst + (first + blk) * kBlkBytes, src + (first + blk) * 128, valid ? 16 : 0);
+            if (pass == 0) cp_async16(dst + 8 * kBlkBytes, src + 8 * 128, valid ? 16 : 0);
+          }
+          MLA_E(1, g, pass * 2 + 1);
         }
-        MLA_E(1, j, pass * 2 + 1);
+        if (timed_out) break;
+        cp_async_commit();
+        cp_async_wait<0>();
+        MLA_E(1, g, 4);
+        fence_proxy_async();
+        mbar_arrive(&full[s]);
       }
-      if (timed_out) break;
-      cp_async_commit();
-      cp_async_wait<0>();
-      MLA_E(1, j, 4);
-      fence_proxy_async();
-      mbar_arrive(&full[s]);
+      base += w.nblk;
     }
+    cp_async_wait<0>();                                 // also on the give-up path: no copy outlives the CTA
   } else if (warp == 10) {
     // ------------------------------------------------------------------------------ Q.K^T issuer
     // The tensor pipe buffers only an instruction or two, so every wait of an issuing thread drains it.  Two
-    // issuers (this warp for S_j = Q . K_j^T, the next for P_j . V_j) keep it fed: while one waits for a
-    // hand-over, the other's instructions run.
-    if (lane == 0 && nblk > 0) {
+    // issuers (this warp for S = Q . K^T, the next for P . V) keep it fed: while one waits for a hand-over,
+    // the other's instructions run.
+    if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc_f16(128, kBK, 0);
       const uint32_t hi_k = (uint32_t)(umma_desc_sw128(0) >> 32);
       const uint32_t k_lo = (uint32_t)umma_desc_sw128(0) + (smem_u32(sK) >> 4);
       const uint32_t tQ = tmem_base + kColQ, tS = tmem_base + kColS;
-      if (!mbar_wait(q_full, 0)) timed_out = true;
-      for (int j = 0; j < nblk && !timed_out; ++j) {
-        if (!mbar_wait(&full[j % kMlaStages], (uint32_t)((j / kMlaStages) & 1))) { timed_out = true; break; }
-        MLA_E(0, j, 0);
-        if (j >= 1 && !mbar_wait(s_free, (uint32_t)((j - 1) & 1))) { timed_out = true; break; }
-        MLA_E(0, j, 1);
-        tc_fence_after();
-        const uint32_t kb_lo = k_lo + (j % kMlaStages) * (kKTile >> 4);
+      int base = 0, units = 0;                          // blocks / non-empty units before this one
+      for (int u = u_first; u <= u_last && !timed_out; ++u) {
+        const UnitWork w = unit_work(p, u, slot0, slot1);
+        if (w.nblk == 0) continue;
+        if (!mbar_wait(q_full, (uint32_t)(units & 1))) { timed_out = true; break; }
+        for (int j = 0; j < w.nblk; ++j) {
+          const int g = base + j;
+          if (!mbar_wait(&full[g % kMlaStages], (uint32_t)((g / kMlaStages) & 1))) { timed_out = true; break; }
+          MLA_E(0, g, 0);
+          if (g >= 1 && !mbar_wait(s_free, (uint32_t)((g - 1) & 1))) { timed_out = true; break; }
+          MLA_E(0, g, 1);
+          tc_fence_after();
+          const uint32_t kb_lo = k_lo + (g % kMlaStages) * (kKTile >> 4);
 #pragma unroll 12
-        for (int kk = 0; kk < 36; ++kk)
-          umma_f16_ts(tS, tQ + kk * 8, kb_lo + (kk >> 2) * (kBlkBytes >> 4) + (kk & 3) * 2, hi_k, idesc_qk,
-                      kk > 0 ? 1u : 0u);
-        umma_commit(s_full);
-        umma_commit(&empty_k[j % kMlaStages]);
-        MLA_E(0, j, 2);
+          for (int kk = 0; kk < 36; ++kk)
+            umma_f16_ts(tS, tQ + kk * 8, kb_lo + (kk >> 2) * (kBlkBytes >> 4) + (kk & 3) * 2, hi_k, idesc_qk,
+                        kk > 0 ? 1u : 0u);
+          umma_commit(s_full);
+          umma_commit(&empty_k[g % kMlaStages]);
+          MLA_E(0, g, 2);
+        }
+        base += w.nblk;
+        ++units;
       }
     }
   } else if (warp == 11) {
     // ------------------------------------------------------------------------------ P.V issuer
-    if (lane == 0 && nblk > 0) {
+    if (lane == 0) {
       constexpr uint32_t idesc_pv = umma_idesc_f16(128, 128, 1);
       const uint32_t hi_v = (uint32_t)(umma_desc_sw128_mn(0, kBlkBytes, 1024) >> 32);
       const uint32_t v_lo = (uint32_t)umma_desc_sw128_mn(0, kBlkBytes, 1024) + (smem_u32(sK) >> 4);
       const uint32_t tT = tmem_base + kColT, tP = tmem_base + kColP;
-      // One 128-column part of P_i . V_i into the scratch.
-      auto issue_pv_part = [&](int i, int part) {
-        const uint32_t vb = v_lo + (i % kMlaStages) * (kKTile >> 4) + (half * 4 + part * 2) * (kBlkBytes >> 4);
+      int base = 0;
+      for (int u = u_first; u <= u_last && !timed_out; ++u) {
+        const UnitWork w = unit_work(p, u, slot0, slot1);
+        // One 128-column part of P_g . V_g into the scratch.
+        auto issue_pv_part = [&](int g, int part) {
+          const uint32_t vb = v_lo + (g % kMlaStages) * (kKTile >> 4) + (w.half * 4 + part * 2) * (kBlkBytes >> 4);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) umma_f16_ts(tT, tP + k * 8, vb + k * (2048 >> 4), hi_v, idesc_pv, k > 0 ? 1u : 0u);
-      };
-      for (int j = 0; j < nblk; ++j) {
-        if (!mbar_wait(p_full, (uint32_t)(j & 1))) { timed_out = true; break; }
-        MLA_E(0, j, 3);
-        if (j >= 1 && !mbar_wait(tb_free, (uint32_t)((j - 1) & 1))) { timed_out = true; break; }
-        MLA_E(0, j, 4);
-        tc_fence_after();
-        issue_pv_part(j, 0);
-        umma_commit(pva_done);
-        MLA_E(0, j, 5);
-        if (!mbar_wait(ta_free, (uint32_t)(j & 1))) { timed_out = true; break; }
-        MLA_E(0, j, 7);
-        tc_fence_after();
-        issue_pv_part(j, 1);
-        umma_commit(pvb_done);
-        umma_commit(&empty[j % kMlaStages]);
-        MLA_E(0, j, 8);
+          for (int k = 0; k < 4; ++k) umma_f16_ts(tT, tP + k * 8, vb + k * (2048 >> 4), hi_v, idesc_pv, k > 0 ? 1u : 0u);
+        };
+        for (int j = 0; j < w.nblk; ++j) {
+          const int g = base + j;
+          if (!mbar_wait(p_full, (uint32_t)(g & 1))) { timed_out = true; break; }
+          MLA_E(0, g, 3);
+          if (g >= 1 && !mbar_wait(tb_free, (uint32_t)((g - 1) & 1))) { timed_out = true; break; }
+          MLA_E(0, g, 4);
+          tc_fence_after();
+          issue_pv_part(g, 0);
+          umma_commit(pva_done);
+          MLA_E(0, g, 5);
+          if (!mbar_wait(ta_free, (uint32_t)(g & 1))) { timed_out = true; break; }
+          MLA_E(0, g, 7);
+          tc_fence_after();
+          issue_pv_part(g, 1);
+          umma_commit(pvb_done);
+          umma_commit(&empty[g % kMlaStages]);
+          MLA_E(0, g, 8);
+        }
+        base += w.nblk;
       }
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------------------------ softmax groups
-    // Group A owns keys [0,32) of every block and value columns [0,128) of this CTA's half; group B keys
+    // Group A owns keys [0,32) of every block and value columns [0,128) of the unit's half; group B keys
     // [32,64) and value columns [128,256).  The two threads of a head exchange their block maxima through
     // shared memory, so both follow the same running maximum.
     const int grp = warp >> 2;
@@ -255,36 +318,16 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
     const uint32_t tS = lane_base + kColS + grp * 32, tT = lane_base + kColT, tPw = lane_base + kColP + grp * 16;
     uint64_t* my_done = grp == 0 ? pva_done : pvb_done;
     uint64_t* my_free = grp == 0 ? ta_free : tb_free;
+    int base = 0;                                       // blocks of the units before this one
+    uint32_t nx = 0;                                    // exchanges through xch so far
+    int q_owner = -1;                                   // request whose query rows are in tensor memory
 
-    if (grp == 0) {
-      // this head's query row -> tensor memory, two fp16 per 32-bit column
-      const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)b * kMH + head) * kDK);
-#pragma unroll 1
-      for (int c = 0; c < 18; ++c) {
-        uint32_t r[16];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint4 v = src[c * 4 + i];
-          r[4 * i] = v.x; r[4 * i + 1] = v.y; r[4 * i + 2] = v.z; r[4 * i + 3] = v.w;
-        }
-        tmem_st16(lane_base + kColQ + c * 16, r);
-      }
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(q_full);
-    }
-
-    float m = -INFINITY, l = 0.f;
     float o[128];
-#pragma unroll
-    for (int i = 0; i < 128; ++i) o[i] = 0.f;
-
-    // o = (o + scratch) * scale: adds this group's 128 value columns of P_i . V_i, then hands the scratch back
-    auto accumulate = [&](int i, float scale) -> bool {
-      const bool ok = mbar_wait(my_done, (uint32_t)(i & 1));
+    // o = (o + scratch) * scale: adds this group's 128 value columns of P_g . V_g, then hands the scratch back
+    auto accumulate = [&](int g, float scale) -> bool {
+      const bool ok = mbar_wait(my_done, (uint32_t)(g & 1));
       if (!__all_sync(0xffffffffu, ok)) return false;
-      if (quarter == 0) MLA_E(2 + grp, i, 5);
+      if (quarter == 0) MLA_E(2 + grp, g, 5);
       tc_fence_after();
 #pragma unroll
       for (int c = 0; c < 8; ++c) {                       // 16 columns at a time keeps the live registers low
@@ -297,96 +340,139 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(my_free);
-      if (quarter == 0) MLA_E(2 + grp, i, 6);
+      if (quarter == 0) MLA_E(2 + grp, g, 6);
       return true;
     };
 
-    for (int j = 0; j < nblk; ++j) {
-      bool ok = mbar_wait(s_full, (uint32_t)(j & 1));
-      if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
-      if (quarter == 0) MLA_E(2 + grp, j, 0);
-      tc_fence_after();
-      uint32_t s[32];
-      tmem_ld32(tS, s);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_free);                  // the scores live in registers from here on
-      if (quarter == 0) MLA_E(2 + grp, j, 1);
-      const int kb = k0 + j * kBK + grp * 32;
-      const bool tail = kb + 32 > k1;
-      float bm = -INFINITY;
+    for (int u = u_first; u <= u_last && !timed_out; ++u) {
+      const UnitWork w = unit_work(p, u, slot0, slot1);
+      if (grp == 0 && w.nblk > 0) {
+        // This head's query row -> tensor memory, two fp16 per 32-bit column, unless the previous unit left the
+        // same request's rows there.  Every Q.K^T of the previous unit has completed: this thread has seen its
+        // last scores.  Six 16-column chunks are requested at a time so that their latencies overlap.
+        if (w.b != q_owner) {
+          const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)w.b * kMH + head) * kDK);
+#pragma unroll 1
+          for (int c0 = 0; c0 < 18; c0 += 6) {
+            uint4 v[24];
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        float t = __uint_as_float(s[e]) * p.sc;
-        if (tail && kb + e >= k1) t = -INFINITY;
-        s[e] = __float_as_uint(t);
-        bm = fmaxf(bm, t);
-      }
-      smax[((j & 1) * 2 + grp) * 128 + head] = bm;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&xch[quarter]);
-      ok = mbar_wait(&xch[quarter], (uint32_t)(j & 1));
-      if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
-      if (quarter == 0) MLA_E(2 + grp, j, 2);
-      bm = fmaxf(bm, smax[((j & 1) * 2 + (grp ^ 1)) * 128 + head]);
-      const float m_new = fmaxf(m, bm);
-      const float mu = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = ex2(m - mu);
-      m = m_new;
-      float ps = 0.f;
+            for (int i = 0; i < 24; ++i) v[i] = src[c0 * 4 + i];
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        const float pv = ex2(__uint_as_float(s[e]) - mu);
-        ps += pv;
-        s[e] = __float_as_uint(pv);
-      }
-      l = l * alpha + ps;
-      if (j >= 1) {                                        // P is free once both parts of P_{j-1} . V_{j-1} are done
-        ok = mbar_wait(pvb_done, (uint32_t)((j - 1) & 1));
-        if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
-      }
-      if (quarter == 0) MLA_E(2 + grp, j, 3);
-      {
-        uint32_t pk[16];
+            for (int c = 0; c < 6; ++c) {
+              uint32_t r[16];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) pk[e] = pack_half2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1]));
-        tmem_st16(tPw, pk);
-        tmem_st_wait();
+              for (int i = 0; i < 4; ++i) {
+                r[4 * i] = v[c * 4 + i].x; r[4 * i + 1] = v[c * 4 + i].y;
+                r[4 * i + 2] = v[c * 4 + i].z; r[4 * i + 3] = v[c * 4 + i].w;
+              }
+              tmem_st16(lane_base + kColQ + (c0 + c) * 16, r);
+            }
+          }
+          tmem_st_wait();
+          q_owner = w.b;
+        }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(p_full);
-        if (quarter == 0) MLA_E(2 + grp, j, 4);
+        if (lane == 0) mbar_arrive(q_full);
+        if (warp == 0 && u == u_first) MLA_M(1);
+        if (warp == 0 && u != u_first) MLA_M(5);
       }
-      if (grp == 0) {
-        // A: rescale now, then add part A of P_j . V_j as soon as it is there (the MMA warp needs the scratch back)
+
+      float m = -INFINITY, l = 0.f;
 #pragma unroll
-        for (int i = 0; i < 128; ++i) o[i] *= alpha;
-        if (!accumulate(j, 1.f)) { timed_out = true; break; }
-      } else {
-        // B: part B of the PREVIOUS block is added here, after this block's P is on its way, and rescaled with it
-        if (j >= 1) {
-          if (!accumulate(j - 1, alpha)) { timed_out = true; break; }
+      for (int i = 0; i < 128; ++i) o[i] = 0.f;
+
+      for (int j = 0; j < w.nblk; ++j) {
+        const int g = base + j;
+        bool ok = mbar_wait(s_full, (uint32_t)(g & 1));
+        if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
+        if (quarter == 0) MLA_E(2 + grp, g, 0);
+        if (warp == 0 && g == 0) MLA_M(2);
+        tc_fence_after();
+        uint32_t s[32];
+        tmem_ld32(tS, s);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free);                  // the scores live in registers from here on
+        if (quarter == 0) MLA_E(2 + grp, g, 1);
+        const int kb = w.k0 + j * kBK + grp * 32;
+        const bool tail = kb + 32 > w.k1;
+        float bm = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          float t = __uint_as_float(s[e]) * p.sc;
+          if (tail && kb + e >= w.k1) t = -INFINITY;
+          s[e] = __float_as_uint(t);
+          bm = fmaxf(bm, t);
+        }
+        smax[((g & 1) * 2 + grp) * 128 + head] = bm;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&xch[quarter]);
+        ok = mbar_wait(&xch[quarter], nx & 1);
+        ++nx;
+        if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
+        if (quarter == 0) MLA_E(2 + grp, g, 2);
+        bm = fmaxf(bm, smax[((g & 1) * 2 + (grp ^ 1)) * 128 + head]);
+        const float m_new = fmaxf(m, bm);
+        const float mu = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = ex2(m - mu);
+        m = m_new;
+        float ps = 0.f;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const float pv = ex2(__uint_as_float(s[e]) - mu);
+          ps += pv;
+          s[e] = __float_as_uint(pv);
+        }
+        l = l * alpha + ps;
+        if (g >= 1) {                                        // P is free once both parts of the previous P.V are done
+          ok = mbar_wait(pvb_done, (uint32_t)((g - 1) & 1));
+          if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
+        }
+        if (quarter == 0) MLA_E(2 + grp, g, 3);
+        {
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) pk[e] = pack_half2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1]));
+          tmem_st16(tPw, pk);
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(p_full);
+          if (quarter == 0) MLA_E(2 + grp, g, 4);
+        }
+        if (grp == 0) {
+          // A: rescale now, then add part A of this block's P.V as soon as it is there (the issuer needs the
+          // scratch back for part B)
+#pragma unroll
+          for (int i = 0; i < 128; ++i) o[i] *= alpha;
+          if (!accumulate(g, 1.f)) { timed_out = true; break; }
+        } else if (j >= 1) {
+          // B: part B of the PREVIOUS block is added here, after this block's P is on its way, and rescaled with it
+          if (!accumulate(g - 1, alpha)) { timed_out = true; break; }
         }
       }
-    }
-    if (!timed_out && nblk > 0 && grp == 1 && !accumulate(nblk - 1, 1.f)) timed_out = true;
-    // row sums of the two key halves
-    if (!timed_out) {
-      ssum[grp * 128 + head] = l;
+      if (!timed_out && w.nblk > 0 && grp == 1 && !accumulate(base + w.nblk - 1, 1.f)) timed_out = true;
+      if (timed_out) break;
+      base += w.nblk;
+      // row sums of the two key halves
+      ssum[((nx & 1) * 2 + grp) * 128 + head] = l;
       __syncwarp();
       if (lane == 0) mbar_arrive(&xch[quarter]);
-      const bool ok = mbar_wait(&xch[quarter], (uint32_t)(nblk & 1));
-      if (!__all_sync(0xffffffffu, ok)) timed_out = true;
-      l += ssum[(grp ^ 1) * 128 + head];
-    }
+      {
+        const bool ok = mbar_wait(&xch[quarter], nx & 1);
+        if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
+      }
+      l += ssum[((nx & 1) * 2 + (grp ^ 1)) * 128 + head];
+      ++nx;
 
-    // ---- emit -------------------------------------------------------------------------------------------
-    if (!timed_out) {
-      const int dv0 = half * 256 + grp * 128;
-      if (p.nsplit == 1) {
+      // ---- emit -----------------------------------------------------------------------------------------
+      if (warp == 0 && u == u_first) MLA_M(3);
+      const int dv0 = grp * 128;
+      if (w.whole) {
         const float inv = 1.f / l;
-        __half* dst = p.out + ((size_t)b * kMH + head) * kDV + dv0;
+        __half* dst = p.out + ((size_t)w.b * kMH + head) * kDV + w.half * 256 + dv0;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           uint4 v;
@@ -397,17 +483,19 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
           reinterpret_cast<uint4*>(dst)[i] = v;
         }
       } else {
-        const size_t row = ((size_t)b * p.nsplit + split) * kMH + head;
-        float* dst = p.part_o + row * kDV + dv0;
+        // partial record, stored [column group of 4][head][4] so that a warp writes 512 contiguous bytes
+        const size_t part = (size_t)blockIdx.x * 2 + (u == u_first ? 0 : 1);
+        float4* dst = reinterpret_cast<float4*>(p.part_o) + (part * 64 + grp * 32) * kMH + head;
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          reinterpret_cast<float4*>(dst)[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
-        if (half == 0 && grp == 0) {
-          p.part_ml[row * 2] = m;
-          p.part_ml[row * 2 + 1] = l;
+        for (int i = 0; i < 32; ++i) dst[(size_t)i * kMH] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+        if (grp == 0) {
+          p.part_ml[(part * kMH + head) * 2] = m;
+          p.part_ml[(part * kMH + head) * 2 + 1] = l;
         }
       }
+      if (warp == 0 && u == u_first) MLA_M(4);
     }
+    if (warp == 0) MLA_M(6);
   }
   if (timed_out) report(p.status, kStatusTimeout);
 
@@ -423,11 +511,92 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
 #ifdef VMK_MLA_TIMING
 extern "C" VMK_API int vmk_debug_mla_trace(long long* out) {
   cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out + 512, g_mla_marks, sizeof(long long) * 16);
   return (int)cudaMemcpyFromSymbol(out, g_mla_trace, sizeof(long long) * 512);
 }
 #endif
 
-int mla_tc_launch(const MlaTcParams& p, cudaStream_t stream) {
+// Merge of the units a range boundary cuts.  grid (ncta, 4): CTA (c, hq) looks at the boundary where range c
+// starts; if it lies inside a unit and is the first such boundary of that unit, it merges the unit's partials
+// (the last unit of range c - 1, then the first unit of ranges c, c + 1, ... while they start inside the unit)
+// for heads [32 hq, 32 hq + 32).  256 threads: lane = head, warp w = column groups [8w, 8w + 8).
+__global__ void __launch_bounds__(256) mla_tc_combine_kernel(const float* __restrict__ part_o,
+                                                             const float* __restrict__ part_ml, int B, int ncta,
+                                                             __half* __restrict__ out) {
+  const int c = blockIdx.x;
+  const int total = 2 * B * kUnitSlots;
+  const int s = range_start(c, total, ncta);
+  asm volatile("griddepcontrol.wait;" ::: "memory");    // launched as a programmatic dependent of mla_tc_kernel
+  if (c == 0 || s % kUnitSlots == 0) return;
+  const int u = s / kUnitSlots;
+  const int prev = range_start(c - 1, total, ncta);
+  if (prev > u * kUnitSlots) return;                    // an earlier boundary inside the unit does the merge
+  const int head = blockIdx.y * 32 + (threadIdx.x & 31), cg0 = (threadIdx.x >> 5) * 8;
+  const int unit_end = (u + 1) * kUnitSlots;
+  // range c - 1 holds this unit as its last unit (record 1) unless the unit is also its first
+  const size_t part_prev = (size_t)(c - 1) * 2 + (prev / kUnitSlots == u ? 0 : 1);
+  int c_end = c;
+  while (c_end < ncta && range_start(c_end, total, ncta) < unit_end) ++c_end;
+  float M = part_ml[(part_prev * kMH + head) * 2];
+  for (int cc = c; cc < c_end; ++cc) M = fmaxf(M, part_ml[((size_t)cc * 2 * kMH + head) * 2]);
+  float4 acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  float lsum = 0.f;
+  auto add = [&](size_t part) {
+    const float m = part_ml[(part * kMH + head) * 2];
+    const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
+    const float4* src = reinterpret_cast<const float4*>(part_o) + (part * 64 + cg0) * kMH + head;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float4 o = src[(size_t)i * kMH];
+      acc[i].x += w * o.x; acc[i].y += w * o.y; acc[i].z += w * o.z; acc[i].w += w * o.w;
+    }
+    lsum += w * part_ml[(part * kMH + head) * 2 + 1];
+  };
+  add(part_prev);
+  for (int cc = c; cc < c_end; ++cc) add((size_t)cc * 2);
+  const float inv = 1.f / lsum;
+  __half* dst = out + ((size_t)(u >> 1) * kMH + head) * kDV + (u & 1) * 256 + cg0 * 4;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 v;
+    v.x = pack_half2(acc[2 * i].x * inv, acc[2 * i].y * inv);
+    v.y = pack_half2(acc[2 * i].z * inv, acc[2 * i].w * inv);
+    v.z = pack_half2(acc[2 * i + 1].x * inv, acc[2 * i + 1].y * inv);
+    v.w = pack_half2(acc[2 * i + 1].z * inv, acc[2 * i + 1].w * inv);
+    reinterpret_cast<uint4*>(dst)[i] = v;
+  }
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Number of ranges (= CTAs).  With at least one unit per SM: one CTA per SM, ranges cut wherever they fall.
+// With fewer units the ranges may be aligned to the units instead (every unit cut into the same power-of-two
+// number of parts), which keeps most partial records away: parts per unit minimise
+// waves x (blocks per part + a fixed cost of about four blocks for loading Q and draining), and the aligned
+// cut is taken when that beats the free-running one.
+int mla_tc_ctas(int B) {
+  const int sms = sm_count();
+  if (2 * B >= sms) return sms;
+  long long best_cost = -1;
+  int best = 1;
+  for (int ns = 1; ns <= kUnitSlots / kMinSlotsPerCta; ns *= 2) {
+    const long long cost = (long long)cdiv(2 * B * ns, sms) * (kUnitSlots / ns + 4);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = ns; }
+  }
+  // free-running ranges pay about three more blocks for the partial records of nearly every unit
+  const long long free_cost = cdiv(2 * B * kUnitSlots, sms) + 4 + 3;
+  return free_cost < best_cost ? sms : 2 * B * best;
+}
+
+// Bytes of the partial (m, l, o) records: two per CTA.
+size_t mla_tc_workspace(int B) {
+  const size_t n = (size_t)mla_tc_ctas(B) * 2 * kMH;
+  return align_up(n * 256 * 4, 256) + align_up(n * 2 * 4, 256);
+}
+
+int mla_tc_launch(const MlaTcParams& p0, float* workspace, cudaStream_t stream) {
   static int configured_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -436,8 +605,26 @@ int mla_tc_launch(const MlaTcParams& p, cudaStream_t stream) {
     if (e != cudaSuccess) return check_launch(e);
     configured_dev = dev;
   }
-  mla_tc_kernel<<<dim3(p.nsplit, 2, p.B), kMlaThreads, kMlaTcSmem, stream>>>(p);
-  return check_launch(cudaGetLastError());
+  MlaTcParams p = p0;
+  p.ncta = mla_tc_ctas(p.B);
+  const size_t n = (size_t)p.ncta * 2 * kMH;
+  p.part_o = workspace;
+  p.part_ml = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + align_up(n * 256 * 4, 256));
+  mla_tc_kernel<<<p.ncta, kMlaThreads, kMlaTcSmem, stream>>>(p);
+  int rc = check_launch(cudaGetLastError());
+  if (rc || p.ncta == 1) return rc;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(p.ncta, 4);
+  cfg.blockDim = dim3(256);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return check_launch(cudaLaunchKernelEx(&cfg, mla_tc_combine_kernel, (const float*)p.part_o, (const float*)p.part_ml, p.B,
+                                         p.ncta, p.out));
 }
 
 }  // namespace vmk
