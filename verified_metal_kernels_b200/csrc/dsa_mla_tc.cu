@@ -74,8 +74,8 @@ struct UnitWork {
 };
 __device__ __forceinline__ UnitWork unit_work(const MlaTcParams& p, int u, int slot0, int slot1) {
   UnitWork w;
-  w.b = u >> 1;
-  w.half = u & 1;
+  w.b = u % p.B;
+  w.half = u / p.B;
   const int ja = max(slot0 - u * kUnitSlots, 0), jb = min(slot1 - u * kUnitSlots, kUnitSlots);
   const int nb = max(0, min(p.cnt[w.b], kMlaTopK));
   w.k0 = ja * kBK;
@@ -179,9 +179,9 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
       const __half* kvb = p.kv + (size_t)w.b * p.L * kDK;
       const int32_t* idxb = p.idx + (size_t)w.b * kMlaTopK;
       const int own = w.half * 4, other = 4 - own;
-      if (warp == 9 && u + 1 <= u_last && ((u + 1) >> 1) != w.b) {
+      if (warp == 9 && u + 1 <= u_last) {
         // the next request's query rows (147 KB) towards L2, long before the softmax threads ask for them
-        const uint8_t* nq = reinterpret_cast<const uint8_t*>(p.q + (size_t)((u + 1) >> 1) * kMH * kDK);
+        const uint8_t* nq = reinterpret_cast<const uint8_t*>(p.q + (size_t)((u + 1) % p.B) * kMH * kDK);
         for (int i = lane; i < kMH * kDK * 2 / 128; i += 32)
           asm volatile("prefetch.global.L2 [%0];" ::"l"(nq + (size_t)i * 128));
       }
@@ -557,7 +557,7 @@ __global__ void __launch_bounds__(256) mla_tc_combine_kernel(const float* __rest
   add(part_prev);
   for (int cc = c; cc < c_end; ++cc) add((size_t)cc * 2);
   const float inv = 1.f / lsum;
-  __half* dst = out + ((size_t)(u >> 1) * kMH + head) * kDV + (u & 1) * 256 + cg0 * 4;
+  __half* dst = out + ((size_t)(u % B) * kMH + head) * kDV + (u / B) * 256 + cg0 * 4;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     uint4 v;
