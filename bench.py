@@ -66,7 +66,7 @@ class ClockSampler:
     while the timed region runs; falls back to polling nvidia-smi when NVML cannot be loaded."""
     REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
-    def __init__(self, index, period=0.005):
+    def __init__(self, index, period=0.002):
         self.index, self.period, self.rows, self.stop_flag, self.thread = index, period, [], False, None
         self.max_mhz, self.err = None, None
 
@@ -107,9 +107,14 @@ class ClockSampler:
             self.err = repr(e)
             self._loop_smi()
 
-    def start(self):
+    def start(self, ready_timeout=10.0):
+        """Starts the sampling thread and waits for its first sample (NVML start-up can take longer than a
+        short timed region)."""
         self.thread = threading.Thread(target=self._loop, daemon=True)
         self.thread.start()
+        t_end = time.perf_counter() + ready_timeout
+        while not self.rows and self.thread.is_alive() and time.perf_counter() < t_end:
+            time.sleep(0.001)
 
     def mark(self):
         return time.perf_counter()
@@ -451,10 +456,11 @@ def main():
         del host
 
     launches = 3 + (1 if _lib.lib().vmk_dsa_attend_workspace_bytes(max(Bl, 1)) > 256 else 0)
-    line = dict(metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=a.steps, warmup=a.warmup,
+    metric = METRIC if (B, L) == (DSA["B"], DSA["L"]) else f"dsa decode rows/s (batch {B}, cache {L})"
+    line = dict(metric=metric, value=value, unit=UNIT, n_gpus=world, steps=a.steps, warmup=a.warmup,
                 ms_per_step=sec * 1e3 / a.steps, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f16",
                 data="synthetic",
-                config=dict(workload=f"dsa B={B} L={L} (8-GPU sweep configuration)", parallelism=f"batch-sharded x{world}",
+                config=dict(workload=f"dsa B={B} L={L}" + (" (8-GPU sweep configuration)" if (B, L) == (DSA["B"], DSA["L"]) else ""), parallelism=f"batch-sharded x{world}",
                             per_rank_batch=Bl, l2="inputs (GBs per rank) far larger than the 126 MB L2; no flush"),
                 clocks=clocks, e2e=e2e, gpu_launches=launches * a.steps, device_status=status)
 
