@@ -4,14 +4,15 @@
 //
 // One CTA = one (key group, 256-row tile, key split) and handles its rows as TWO 128-row tiles A and B
 // that share every K/V tile brought into shared memory (half the L2 traffic per flop, and two softmax
-// warpgroups to keep the tensor pipe fed).  352 threads, warp-specialised:
+// warpgroups to keep the tensor pipe fed).  384 threads, warp-specialised:
 //   warp 0      TMA producer of K tiles (64 keys x 128, two 64-wide swizzled boxes), 3-stage ring released
 //               as soon as both Q.K^T products have consumed a tile, so K runs ahead of the softmax
 //   warp 10     TMA producer of V tiles, ring of its own, released after both P.V products
-//   warp 1      owns tensor memory (512 columns: S_A[2], S_B[2], O_A, O_B) and issues the MMAs
+//   warp 1      owns tensor memory (512 columns: S_A[2], S_B[2], O_A, O_B) and issues
 //                 S_t[j & 1] (128 x 64 fp32)  = Q_t . K_j^T      8 x tcgen05.mma M128 N64 K16, K-major operands
-//                 O_t        (128 x 128 fp32) += P_t . V_j        4 x tcgen05.mma M128 N128 K16, V MN-major
 //               S is double buffered so the Q.K^T of block j+1 runs under the softmax of block j
+//   warp 11     issues
+//                 O_t        (128 x 128 fp32) += P_t . V_j        4 x tcgen05.mma M128 N128 K16, V MN-major
 //   warps 2-5   softmax of tile A, warps 6-9 softmax of tile B, one thread per row: two passes over the
 //               64 scores in tensor memory (row max, then exp2 / row sum / fp16 P into a swizzled
 //               shared-memory operand tile), LAZY rescaling of O (only when the row max grew by more than
@@ -32,7 +33,7 @@ constexpr int kKvHalf = kTcBK * 128;             // [64 keys][128 B] swizzled bo
 constexpr int kKvTile = 2 * kKvHalf;             // 16 KiB
 constexpr int kPTile = 128 * kTcBK * 2;          // 16 KiB: [128 rows][64 keys] fp16, one swizzled box
 constexpr int kTcStages = 3;
-constexpr int kTcThreads = 352;
+constexpr int kTcThreads = 384;
 constexpr int kTcCols = 512;
 constexpr int kColS = 0;                         // S_A[0], S_A[1], S_B[0], S_B[1]: 4 x 64 columns
 constexpr int kColO = 256;                       // O_A, O_B: 2 x 128 columns
@@ -139,23 +140,27 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------------------------ Q.K^T issuer
+    // The tensor pipe buffers only an instruction or two, so an issuing thread that waits lets it drain: the
+    // two products are issued by two warps, and one's instructions run while the other waits.
     if (lane == 0 && nblk > 0) {
       constexpr uint32_t idesc_qk = umma_idesc_f16(128, kTcBK, 0);
-      constexpr uint32_t idesc_pv = umma_idesc_f16(128, 128, 1);
       const int ntile = has_b ? 2 : 1;
       // Descriptor words.  High words are constants of the layout; low words are (address >> 4) plus a
       // constant per K step: +2 per 32-byte step inside a 128-byte swizzled row, + half-tile / 16 for the
-      // second 64-wide half, +128 per 16-key step of an MN-major V tile.
+      // second 64-wide half.
       const uint32_t hi_k = (uint32_t)(umma_desc_sw128(0) >> 32);
-      const uint32_t hi_v = (uint32_t)(umma_desc_sw128_mn(0, kKvHalf, 1024) >> 32);
-      const uint32_t lo_k0 = (uint32_t)umma_desc_sw128(0), lo_v0 = (uint32_t)umma_desc_sw128_mn(0, kKvHalf, 1024);
-      const uint32_t q_lo = lo_k0 + (smem_u32(sQ) >> 4), p_lo = lo_k0 + (smem_u32(sP) >> 4);
-      const uint32_t k_lo = lo_k0 + (smem_u32(sK) >> 4), v_lo = lo_v0 + (smem_u32(sV) >> 4);
-      // S_t[j & 1] = Q_t . K_j^T for both tiles; releases the K stage
-      auto issue_qk = [&](int j) {
+      const uint32_t lo_k0 = (uint32_t)umma_desc_sw128(0);
+      const uint32_t q_lo = lo_k0 + (smem_u32(sQ) >> 4), k_lo = lo_k0 + (smem_u32(sK) >> 4);
+      for (int t = 0; t < ntile; ++t)
+        if (!mbar_wait(&q_full[t], 0)) timed_out = true;
+      for (int j = 0; j < nblk && !timed_out; ++j) {
+        if (!mbar_wait(&k_full[j % kTcStages], (uint32_t)((j / kTcStages) & 1))) { timed_out = true; break; }
         const uint32_t kb_lo = k_lo + (j % kTcStages) * (kKvTile >> 4);
+        // S_t[j & 1] = Q_t . K_j^T for both tiles; releases the K stage
         for (int t = 0; t < ntile; ++t) {
+          if (j >= 2 && !mbar_wait(&s_empty[t * 2 + (j & 1)], (uint32_t)(((j >> 1) - 1) & 1))) { timed_out = true; break; }
+          tc_fence_after();
           const uint32_t d = tmem_base + kColS + (t * 2 + (j & 1)) * kTcBK;
           const uint32_t qa_lo = q_lo + t * (kQTile >> 4);
 #pragma unroll
@@ -165,38 +170,25 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
           }
           umma_commit(&s_full[t * 2 + (j & 1)]);
         }
+        if (timed_out) break;
         umma_commit(&k_empty[j % kTcStages]);
-      };
-      auto wait_qk_inputs = [&](int j) -> bool {
-        if (!mbar_wait(&k_full[j % kTcStages], (uint32_t)((j / kTcStages) & 1))) return false;
-        if (j >= 2) {
-          for (int t = 0; t < ntile; ++t)
-            if (!mbar_wait(&s_empty[t * 2 + (j & 1)], (uint32_t)(((j >> 1) - 1) & 1))) return false;
-        }
-        return true;
-      };
-      for (int t = 0; t < ntile; ++t)
-        if (!mbar_wait(&q_full[t], 0)) timed_out = true;
-      if (!timed_out && !wait_qk_inputs(0)) timed_out = true;
-      if (!timed_out) {
-        tc_fence_after();
-        issue_qk(0);
       }
-      TC_T0();
+    }
+  } else if (warp == 11) {
+    // ------------------------------------------------------------------------------ P.V issuer
+    if (lane == 0 && nblk > 0) {
+      constexpr uint32_t idesc_pv = umma_idesc_f16(128, 128, 1);
+      const int ntile = has_b ? 2 : 1;
+      // +128 per 16-key step of an MN-major V tile
+      const uint32_t hi_k = (uint32_t)(umma_desc_sw128(0) >> 32);
+      const uint32_t hi_v = (uint32_t)(umma_desc_sw128_mn(0, kKvHalf, 1024) >> 32);
+      const uint32_t p_lo = (uint32_t)umma_desc_sw128(0) + (smem_u32(sP) >> 4);
+      const uint32_t v_lo = (uint32_t)umma_desc_sw128_mn(0, kKvHalf, 1024) + (smem_u32(sV) >> 4);
       for (int j = 0; j < nblk && !timed_out; ++j) {
-        if (j + 1 < nblk) {
-          if (!wait_qk_inputs(j + 1)) { timed_out = true; break; }
-          TC_ACC(8);
-          tc_fence_after();
-          issue_qk(j + 1);
-          TC_ACC(9);
-        }
         if (!mbar_wait(&v_full[j % kTcStages], (uint32_t)((j / kTcStages) & 1))) { timed_out = true; break; }
-        TC_ACC(10);
         const uint32_t vb_lo = v_lo + (j % kTcStages) * (kKvTile >> 4);
         for (int t = 0; t < ntile; ++t) {
           if (!mbar_wait(&p_full[t], (uint32_t)(j & 1))) { timed_out = true; break; }
-          TC_ACC(11 + t);
           tc_fence_after();
 #pragma unroll
           for (int k = 0; k < kTcBK / 16; ++k) {
@@ -207,7 +199,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
                        idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&pv_done[t]);
-          TC_ACC(13);
         }
         if (timed_out) break;
         umma_commit(&v_empty[j % kTcStages]);
