@@ -164,12 +164,13 @@ static int tc_split_cap(int units) {
 // waves x (blocks per CTA + a fixed per-CTA overhead of about six blocks), which avoids a mostly empty
 // last wave.
 static void plan_role_tc(RolePlan* r, int groups, int rows, int keys) {
+  constexpr int kTcBlock = 128;      // keys per block of the tensor-memory kernel
   r->tc = true;
   r->rt = 8; r->ks = 1;
   r->row_tiles = cdiv(rows, 256);
   r->MP = rows;                      // partial rows are indexed by the real row, no padding needed
   const int units = groups * r->row_tiles;
-  const int blocks = cdiv(keys > 0 ? keys : 1, kBK);
+  const int blocks = cdiv(keys > 0 ? keys : 1, kTcBlock);
   const int sms = sm_count();
   const int cap = tc_split_cap(units);
   long long best_cost = -1;
@@ -177,11 +178,11 @@ static void plan_role_tc(RolePlan* r, int groups, int rows, int keys) {
   for (int ns = 1; ns <= cap && ns <= blocks; ++ns) {
     const int per = cdiv(blocks, ns);
     const int real = cdiv(blocks, per);
-    const long long cost = (long long)cdiv(units * real, sms) * (per + 6);
+    const long long cost = (long long)cdiv(units * real, sms) * (per + 3);
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = real; }
   }
-  r->split_len = cdiv(blocks, best) * kBK;
-  r->nsplit = cdiv(blocks * kBK, r->split_len);
+  r->split_len = cdiv(blocks, best) * kTcBlock;
+  r->nsplit = cdiv(blocks * kTcBlock, r->split_len);
   r->n_cta = units * r->nsplit;
 }
 

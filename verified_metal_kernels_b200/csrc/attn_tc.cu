@@ -2,21 +2,25 @@
 // requests sharing a prefix, or a wide speculative tree): the regime where the op is bound by the
 // tensor pipe rather than by HBM.
 //
+// One tcgen05.mma costs about 96 cycles whatever its width up to N = 128 (107 with A in shared memory), so
+// the kernel works on 128-key blocks: S = Q.K^T is 8 instructions of M128 N128 K16 per block and tile, and
+// P.V is 8 of M128 N128 K16 with P read from TENSOR MEMORY.
+//
 // One CTA = one (key group, 256-row tile, key split) and handles its rows as TWO 128-row tiles A and B
-// that share every K/V tile brought into shared memory (half the L2 traffic per flop, and two softmax
-// warpgroups to keep the tensor pipe fed).  384 threads, warp-specialised:
-//   warp 0      TMA producer of K tiles (64 keys x 128, two 64-wide swizzled boxes), 3-stage ring released
-//               as soon as both Q.K^T products have consumed a tile, so K runs ahead of the softmax
-//   warp 10     TMA producer of V tiles, ring of its own, released after both P.V products
-//   warp 1      owns tensor memory (512 columns: S_A[2], S_B[2], O_A, O_B) and issues
-//                 S_t[j & 1] (128 x 64 fp32)  = Q_t . K_j^T      8 x tcgen05.mma M128 N64 K16, K-major operands
-//               S is double buffered so the Q.K^T of block j+1 runs under the softmax of block j
-//   warp 11     issues
-//                 O_t        (128 x 128 fp32) += P_t . V_j        4 x tcgen05.mma M128 N128 K16, V MN-major
+// that share every K/V tile brought into shared memory and alternate on the tensor pipe: while the softmax
+// warps of one tile work, the products of the other run.  Tensor memory (512 columns): S_A, S_B, O_A, O_B,
+// 128 columns each.  P (fp16 pairs, 64 columns) is written IN PLACE over the scores it came from, so S_t
+// is rewritten by the next Q.K^T only after P_t.V has completed.  352 threads, warp-specialised:
+//   warp 0      TMA producer: K_0, V_0, K_1, V_1, ... (128 keys x 128, four 64x64 swizzled boxes each) into
+//               one ring of five 32 KiB slots; the products release the slots in the same order
+//   warp 1      owns tensor memory and issues  S_t = Q_t . K_j^T        (A, B from shared memory, K-major)
+//   warp 10     issues                          O_t += P_t . V_j          (A = P_t in tensor memory, V MN-major)
+//               two issuing warps, because the tensor pipe buffers only an instruction or two and an
+//               issuing thread that waits lets it drain
 //   warps 2-5   softmax of tile A, warps 6-9 softmax of tile B, one thread per row: two passes over the
-//               64 scores in tensor memory (row max, then exp2 / row sum / fp16 P into a swizzled
-//               shared-memory operand tile), LAZY rescaling of O (only when the row max grew by more than
-//               2^8, so P stays below 256 and the result exact)
+//               128 scores in tensor memory (row max; then exp2 / row sum / fp16 P back to tensor memory),
+//               LAZY rescaling of O (only when the row max grew by more than 2^8, so P stays below 256
+//               and the result exact)
 // Partials (m, l, o) per row are emitted exactly as by the warp-level kernel, so the combine pass and
 // the multi-GPU merge are shared.  Every mbarrier wait is bounded; a wait that runs out sets the status
 // word and the CTA winds down through the common exit, where tensor memory is freed.
@@ -25,31 +29,20 @@
 
 namespace vmk {
 
-constexpr int kTcBK = 64;                        // keys per block
+constexpr int kTcBK = 128;                       // keys per block
 constexpr int kTcRows = 256;                     // rows per CTA (two tiles of 128)
-constexpr int kQHalf = 128 * 128;                // [128 rows][128 B] swizzled box
+constexpr int kQHalf = 128 * 128;                // [128 rows][128 B] swizzled: one 64-wide half of the head dim
 constexpr int kQTile = 2 * kQHalf;               // 32 KiB per 128-row query tile
-constexpr int kKvHalf = kTcBK * 128;             // [64 keys][128 B] swizzled box
-constexpr int kKvTile = 2 * kKvHalf;             // 16 KiB
-constexpr int kPTile = 128 * kTcBK * 2;          // 16 KiB: [128 rows][64 keys] fp16, one swizzled box
-constexpr int kTcStages = 3;
-constexpr int kTcThreads = 384;
+constexpr int kKvHalf = kTcBK * 128;             // [128 keys][128 B] swizzled (two 64-key TMA boxes)
+constexpr int kKvTile = 2 * kKvHalf;             // 32 KiB
+constexpr int kTcSlots = 5;                      // ring slots: K_j -> slot 2j % 5, V_j -> slot (2j + 1) % 5
+constexpr int kTcThreads = 352;
 constexpr int kTcCols = 512;
-constexpr int kColS = 0;                         // S_A[0], S_A[1], S_B[0], S_B[1]: 4 x 64 columns
+constexpr int kColS = 0;                         // S_A, S_B: 2 x 128 columns (P_t over the first 64 of S_t)
 constexpr int kColO = 256;                       // O_A, O_B: 2 x 128 columns
 constexpr float kLazyRescale = 8.f;              // log2 units
-constexpr int kTcBars = 4 * kTcStages + 4 + 4 + 2 + 2 + 2;
-constexpr int kAttnTcSmem = 2 * kQTile + 2 * kTcStages * kKvTile + 2 * kPTile + kTcBars * 8 + 16 + 1024;
-
-#ifdef VMK_TC_TIMING
-// Debug build only: cycles spent per phase by CTA 0 (softmax warp 2 lane 0: slots 0-7, MMA thread: 8-15).
-__device__ long long g_tc_timing[16];
-#define TC_T0() long long _t0 = clock64()
-#define TC_ACC(slot) do { if (blockIdx.x == 0) { long long _t1 = clock64(); g_tc_timing[slot] += _t1 - _t0; _t0 = _t1; } } while (0)
-#else
-#define TC_T0() do {} while (0)
-#define TC_ACC(slot) do {} while (0)
-#endif
+constexpr int kTcBars = 2 * kTcSlots + 2 + 2 + 2 + 2;
+constexpr int kAttnTcSmem = 2 * kQTile + kTcSlots * kKvTile + kTcBars * 8 + 16 + 1024;
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -57,23 +50,32 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// D[tmem] (+)= A[tmem] * B[smem descriptor given as (low, high) words]
+__device__ __forceinline__ void umma_f16_ts_w(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 db;\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "mov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n"
+      "}\n" ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_constant__ AttnParams p) {
   const AttnRole& R = p.a;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;                                   // [2 tiles][32 KiB]
-  uint8_t* sK = sQ + 2 * kQTile;                        // [stages][16 KiB]
-  uint8_t* sV = sK + kTcStages * kKvTile;               // [stages][16 KiB]
-  uint8_t* sP = sV + kTcStages * kKvTile;               // [2 tiles][16 KiB]
-  uint64_t* k_full = reinterpret_cast<uint64_t*>(sP + 2 * kPTile);
-  uint64_t* k_empty = k_full + kTcStages;
-  uint64_t* v_full = k_empty + kTcStages;
-  uint64_t* v_empty = v_full + kTcStages;
-  uint64_t* s_full = v_empty + kTcStages;               // [tile][buffer]
-  uint64_t* s_empty = s_full + 4;                       // [tile][buffer]
-  uint64_t* p_full = s_empty + 4;                       // [tile]
-  uint64_t* pv_done = p_full + 2;                       // [tile]
-  uint64_t* q_full = pv_done + 2;                       // [tile]
+  uint8_t* sKV = sQ + 2 * kQTile;                       // [slots][32 KiB]
+  uint64_t* full = reinterpret_cast<uint64_t*>(sKV + kTcSlots * kKvTile);   // tile landed (TMA bytes)
+  uint64_t* empty = full + kTcSlots;                    // tile consumed by both row tiles' product (MMA commit)
+  uint64_t* s_full = empty + kTcSlots;                  // [tile] scores ready               (MMA commit)
+  uint64_t* p_full = s_full + 2;                        // [tile] P stored to tensor memory  (4 warps)
+  uint64_t* pv_done = p_full + 2;                       // [tile] P.V done: S_t and O_t free (MMA commit)
+  uint64_t* q_full = pv_done + 2;                       // [tile] Q tile in shared memory    (4 warps)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -94,17 +96,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
   const int nblk = kend > kbeg ? (kend - kbeg + kTcBK - 1) / kTcBK : 0;
 
   if (tid == 0) {
-    for (int s = 0; s < kTcStages; ++s) {
-      mbar_init(&k_full[s], 1);
-      mbar_init(&k_empty[s], 1);
-      mbar_init(&v_full[s], 1);
-      mbar_init(&v_empty[s], 1);
-    }
-    for (int s = 0; s < 4; ++s) {
-      mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 4);
+    for (int s = 0; s < kTcSlots; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
     }
     for (int t = 0; t < 2; ++t) {
+      mbar_init(&s_full[t], 1);
       mbar_init(&p_full[t], 4);
       mbar_init(&pv_done[t], 1);
       mbar_init(&q_full[t], 4);
@@ -118,31 +115,28 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
   const uint32_t tmem_base = *tmem_slot;
 
   bool timed_out = false;
-  if (warp == 0 || warp == 10) {
-    // ------------------------------------------------------------------------------ TMA producers
+  if (warp == 0) {
+    // ------------------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      const bool is_k = warp == 0;
-      uint64_t* full = is_k ? k_full : v_full;
-      uint64_t* empty = is_k ? k_empty : v_empty;
-      uint8_t* ring = is_k ? sK : sV;
-      const CUtensorMap* tm = is_k ? &R.tmK : &R.tmV;
-      for (int j = 0; j < nblk; ++j) {
-        const int s = j % kTcStages;
-        if (j >= kTcStages && !mbar_wait(&empty[s], (uint32_t)(((j / kTcStages) - 1) & 1))) {
+      for (int i = 0; i < 2 * nblk; ++i) {
+        const int s = i % kTcSlots;
+        if (i >= kTcSlots && !mbar_wait(&empty[s], (uint32_t)(((i / kTcSlots) - 1) & 1))) {
           timed_out = true;
           break;
         }
-        const int kb = kbeg + j * kTcBK;
-        uint8_t* dst = ring + s * kKvTile;
+        const CUtensorMap* tm = (i & 1) ? &R.tmV : &R.tmK;
+        const int kb = kbeg + (i >> 1) * kTcBK;
+        uint8_t* dst = sKV + s * kKvTile;
         mbar_expect_tx(&full[s], kKvTile);
+        // the tensor maps have 64 x 64 boxes: two boxes stacked along the keys make one [128][128 B] half
         tma_load_3d(dst, tm, 0, kb, z, &full[s]);
+        tma_load_3d(dst + kKvHalf / 2, tm, 0, kb + 64, z, &full[s]);
         tma_load_3d(dst + kKvHalf, tm, 64, kb, z, &full[s]);
+        tma_load_3d(dst + kKvHalf + kKvHalf / 2, tm, 64, kb + 64, z, &full[s]);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------------------ Q.K^T issuer
-    // The tensor pipe buffers only an instruction or two, so an issuing thread that waits lets it drain: the
-    // two products are issued by two warps, and one's instructions run while the other waits.
     if (lane == 0 && nblk > 0) {
       constexpr uint32_t idesc_qk = umma_idesc_f16(128, kTcBK, 0);
       const int ntile = has_b ? 2 : 1;
@@ -151,57 +145,54 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
       // second 64-wide half.
       const uint32_t hi_k = (uint32_t)(umma_desc_sw128(0) >> 32);
       const uint32_t lo_k0 = (uint32_t)umma_desc_sw128(0);
-      const uint32_t q_lo = lo_k0 + (smem_u32(sQ) >> 4), k_lo = lo_k0 + (smem_u32(sK) >> 4);
+      const uint32_t q_lo = lo_k0 + (smem_u32(sQ) >> 4), kv_lo = lo_k0 + (smem_u32(sKV) >> 4);
       for (int t = 0; t < ntile; ++t)
         if (!mbar_wait(&q_full[t], 0)) timed_out = true;
       for (int j = 0; j < nblk && !timed_out; ++j) {
-        if (!mbar_wait(&k_full[j % kTcStages], (uint32_t)((j / kTcStages) & 1))) { timed_out = true; break; }
-        const uint32_t kb_lo = k_lo + (j % kTcStages) * (kKvTile >> 4);
-        // S_t[j & 1] = Q_t . K_j^T for both tiles; releases the K stage
+        const int i = 2 * j, s = i % kTcSlots;
+        if (!mbar_wait(&full[s], (uint32_t)((i / kTcSlots) & 1))) { timed_out = true; break; }
+        const uint32_t kb_lo = kv_lo + s * (kKvTile >> 4);
         for (int t = 0; t < ntile; ++t) {
-          if (j >= 2 && !mbar_wait(&s_empty[t * 2 + (j & 1)], (uint32_t)(((j >> 1) - 1) & 1))) { timed_out = true; break; }
+          // S_t (and the P_t inside it) is free once P_t . V_{j-1} has completed
+          if (j >= 1 && !mbar_wait(&pv_done[t], (uint32_t)((j - 1) & 1))) { timed_out = true; break; }
           tc_fence_after();
-          const uint32_t d = tmem_base + kColS + (t * 2 + (j & 1)) * kTcBK;
+          const uint32_t d = tmem_base + kColS + t * 128;
           const uint32_t qa_lo = q_lo + t * (kQTile >> 4);
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             umma_f16_w(d, qa_lo + (k >> 2) * (kQHalf >> 4) + (k & 3) * 2, hi_k,
                        kb_lo + (k >> 2) * (kKvHalf >> 4) + (k & 3) * 2, hi_k, idesc_qk, k > 0 ? 1u : 0u);
           }
-          umma_commit(&s_full[t * 2 + (j & 1)]);
+          umma_commit(&s_full[t]);
         }
         if (timed_out) break;
-        umma_commit(&k_empty[j % kTcStages]);
+        umma_commit(&empty[s]);
       }
     }
-  } else if (warp == 11) {
+  } else if (warp == 10) {
     // ------------------------------------------------------------------------------ P.V issuer
     if (lane == 0 && nblk > 0) {
       constexpr uint32_t idesc_pv = umma_idesc_f16(128, 128, 1);
       const int ntile = has_b ? 2 : 1;
-      // +128 per 16-key step of an MN-major V tile
-      const uint32_t hi_k = (uint32_t)(umma_desc_sw128(0) >> 32);
+      // V rows 16k .. 16k+16 (keys) x 128 d, MN-major: 8-key groups 1024 B apart (+128 per 16-key step), the
+      // two 64-wide d halves kKvHalf apart.  P_t[:, 16k .. 16k+16) = 8 columns of packed fp16 pairs.
       const uint32_t hi_v = (uint32_t)(umma_desc_sw128_mn(0, kKvHalf, 1024) >> 32);
-      const uint32_t p_lo = (uint32_t)umma_desc_sw128(0) + (smem_u32(sP) >> 4);
-      const uint32_t v_lo = (uint32_t)umma_desc_sw128_mn(0, kKvHalf, 1024) + (smem_u32(sV) >> 4);
+      const uint32_t v_lo = (uint32_t)umma_desc_sw128_mn(0, kKvHalf, 1024) + (smem_u32(sKV) >> 4);
       for (int j = 0; j < nblk && !timed_out; ++j) {
-        if (!mbar_wait(&v_full[j % kTcStages], (uint32_t)((j / kTcStages) & 1))) { timed_out = true; break; }
-        const uint32_t vb_lo = v_lo + (j % kTcStages) * (kKvTile >> 4);
+        const int i = 2 * j + 1, s = i % kTcSlots;
+        if (!mbar_wait(&full[s], (uint32_t)((i / kTcSlots) & 1))) { timed_out = true; break; }
+        const uint32_t vb_lo = v_lo + s * (kKvTile >> 4);
         for (int t = 0; t < ntile; ++t) {
           if (!mbar_wait(&p_full[t], (uint32_t)(j & 1))) { timed_out = true; break; }
           tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < kTcBK / 16; ++k) {
-            // A: P_t[:, 16k .. 16k+16) K-major (one 128-byte swizzled row per query row);
-            // B: V rows 16k .. 16k+16 (keys) x 128 d, MN-major: 8-key groups 1024 B apart, the two 64-wide
-            //    d halves kKvHalf apart.
-            umma_f16_w(tmem_base + kColO + t * 128, p_lo + t * (kPTile >> 4) + k * 2, hi_k, vb_lo + k * (2048 >> 4), hi_v,
-                       idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-          }
+          for (int k = 0; k < kTcBK / 16; ++k)
+            umma_f16_ts_w(tmem_base + kColO + t * 128, tmem_base + kColS + t * 128 + k * 8, vb_lo + k * (2048 >> 4), hi_v,
+                          idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
           umma_commit(&pv_done[t]);
         }
         if (timed_out) break;
-        umma_commit(&v_empty[j % kTcStages]);
+        umma_commit(&empty[s]);
       }
     }
   } else if (warp >= 2 && warp <= 9) {
@@ -213,11 +204,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
     const bool valid_row = grow < rows;
     const bool tile_on = t == 0 || has_b;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    const uint32_t tS = lane_base + kColS + t * 2 * kTcBK;
+    const uint32_t tS = lane_base + kColS + t * 128;
     const uint32_t tO = lane_base + kColO + t * 128;
     const size_t outer = (size_t)zg * R.rows_outer + (valid_row ? grow / R.G : 0);
     const int head = h * R.G + (valid_row ? grow % R.G : 0);
-    uint8_t* myP = sP + t * kPTile;
 
     if (tile_on) {
       // this thread's query row -> swizzled K-major operand tile
@@ -237,75 +227,60 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
       mw[w] = 0xffffffffu;
       if (R.bits != nullptr && valid_row && w < R.bits_words) mw[w] = R.bits[outer * R.bits_words + w];
     }
+    // scaled score of key (kb + c * 32 + i), or -inf if the key is past the end or hidden from this draft row
+    auto visible = [&](int key, int kend_) -> bool {
+      bool vis = key < kend_;
+      if (vis && key >= R.mask_start) {
+        const int jb = key - R.mask_start;
+        uint32_t word = mw[0];
+#pragma unroll
+        for (int w = 1; w < kMaxMaskWords; ++w) word = ((jb >> 5) == w) ? mw[w] : word;
+        vis = (word >> (jb & 31)) & 1u;
+      }
+      return vis;
+    };
 
     float m = -INFINITY, l = 0.f;
     const int nloop = tile_on ? nblk : 0;
-#ifdef VMK_TC_TIMING
-    const bool tc_probe = warp == 2 && lane == 0;
-    long long _t0 = clock64();
-#define SM_ACC(slot) do { if (tc_probe && blockIdx.x == 0) { long long _t1 = clock64(); g_tc_timing[slot] += _t1 - _t0; _t0 = _t1; } } while (0)
-#else
-#define SM_ACC(slot) do {} while (0)
-#endif
     for (int j = 0; j < nloop; ++j) {
-      const int sb = j & 1;
-      bool ok = mbar_wait(&s_full[t * 2 + sb], (uint32_t)((j >> 1) & 1));
+      bool ok = mbar_wait(&s_full[t], (uint32_t)(j & 1));
       if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
-      SM_ACC(0);
       tc_fence_after();
       const int kb = kbeg + j * kTcBK;
       const bool tail = kb + kTcBK > kend;
       const bool edge = tail || (kb + kTcBK > R.mask_start);
-      // pass 1: row maximum of the 64 scores
-      uint32_t s0[32], s1[32];
-      tmem_ld32(tS + sb * kTcBK, s0);
-      tmem_ld32(tS + sb * kTcBK + 32, s1);
+      // the 128 scores of this row -> registers (one wait for the four loads)
+      uint32_t s0[32], s1[32], s2[32], s3[32];
+      tmem_ld32(tS, s0);
+      tmem_ld32(tS + 32, s1);
+      tmem_ld32(tS + 64, s2);
+      tmem_ld32(tS + 96, s3);
       tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[t * 2 + sb]);    // the scores now live in registers
-      SM_ACC(1);
       float bm = -INFINITY;
       if (!edge) {
-        // interior block: every key visible.  Kept free of per-element branches so the hot loop is a
-        // short straight-line sequence.
-        float bm1 = -INFINITY;
+        // interior block: every key visible.  Kept free of per-element branches.
+        float b0 = -INFINITY, b1 = -INFINITY, b2 = -INFINITY, b3 = -INFINITY;
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float a = __uint_as_float(s0[i]) * p.sc, b = __uint_as_float(s1[i]) * p.sc;
-          s0[i] = __float_as_uint(a);
-          s1[i] = __float_as_uint(b);
-          bm = fmaxf(bm, a);
-          bm1 = fmaxf(bm1, b);
+          b0 = fmaxf(b0, __uint_as_float(s0[i]));
+          b1 = fmaxf(b1, __uint_as_float(s1[i]));
+          b2 = fmaxf(b2, __uint_as_float(s2[i]));
+          b3 = fmaxf(b3, __uint_as_float(s3[i]));
         }
-        bm = fmaxf(bm, bm1);
+        bm = fmaxf(fmaxf(b0, b1), fmaxf(b2, b3));
       } else {
-        // block touching the end of the key range or the draft positions: per-key visibility
-#pragma unroll 1
-        for (int half = 0; half < 2; ++half) {
+        // block touching the end of the key range or the draft positions: hidden keys become -inf
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int key = kb + half * 32 + i;
-            bool vis = key < kend;
-            if (vis && key >= R.mask_start) {
-              const int jb = key - R.mask_start;
-              uint32_t word = mw[0];
-#pragma unroll
-              for (int w = 1; w < kMaxMaskWords; ++w) word = ((jb >> 5) == w) ? mw[w] : word;
-              vis = (word >> (jb & 31)) & 1u;
-            }
-            if (half == 0) {
-              const float a = vis ? __uint_as_float(s0[i]) * p.sc : -INFINITY;
-              s0[i] = __float_as_uint(a);
-              bm = fmaxf(bm, a);
-            } else {
-              const float a = vis ? __uint_as_float(s1[i]) * p.sc : -INFINITY;
-              s1[i] = __float_as_uint(a);
-              bm = fmaxf(bm, a);
-            }
-          }
+        for (int i = 0; i < 32; ++i) {
+          if (!visible(kb + i, kend)) s0[i] = 0xff800000u;
+          if (!visible(kb + 32 + i, kend)) s1[i] = 0xff800000u;
+          if (!visible(kb + 64 + i, kend)) s2[i] = 0xff800000u;
+          if (!visible(kb + 96 + i, kend)) s3[i] = 0xff800000u;
+          bm = fmaxf(bm, fmaxf(fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])),
+                               fmaxf(__uint_as_float(s2[i]), __uint_as_float(s3[i]))));
         }
       }
+      bm *= p.sc;                                      // the scale is positive: max commutes with it
       const float m_new = fmaxf(m, bm);
       float alpha = 1.f;
       bool rescale = false;
@@ -318,66 +293,56 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
       }
       l *= alpha;
       const float mu = (m == -INFINITY) ? 0.f : m;
-      float ps0 = 0.f, ps1 = 0.f;
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float a = fast_exp2(__uint_as_float(s0[i]) - mu), b = fast_exp2(__uint_as_float(s1[i]) - mu);
-        ps0 += a;
-        ps1 += b;
-        s0[i] = __float_as_uint(a);
-        s1[i] = __float_as_uint(b);
-      }
-      l += ps0 + ps1;
-      SM_ACC(2);
-
-      // O_t and the P tile are free once P_{j-1} . V_{j-1} has completed
-      if (j >= 1) {
-        ok = mbar_wait(&pv_done[t], (uint32_t)((j - 1) & 1));
-        if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
-        tc_fence_after();
-      }
-      SM_ACC(3);
+      // O_t is at rest here: Q.K^T of this block was only issued after P.V of the previous one had completed
       if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t o[32];
-          tmem_ld32(tO + c * 32, o);
+        for (int c = 0; c < 8; ++c) {
+          uint32_t o[16];
+          tmem_ld16(tO + c * 16, o);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st32(tO + c * 32, o);
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st16(tO + c * 16, o);
         }
-        tmem_st_wait();
       }
+      // P = exp2(score * scale - m) (exactly 0 for a hidden key: fma(-inf) = -inf), row sum, fp16 pairs written
+      // over the first 64 columns of the scores
+      float ps0 = 0.f, ps1 = 0.f;
+      auto to_p = [&](uint32_t (&sc32)[32], int c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float a = fast_exp2(fmaf(__uint_as_float(sc32[i]), p.sc, -mu));
+          const float b = fast_exp2(fmaf(__uint_as_float(sc32[i + 1]), p.sc, -mu));
+          ps0 += a;
+          ps1 += b;
+          pk[i >> 1] = pack_half2(a, b);
+        }
+        tmem_st16(tS + c * 16, pk);
+      };
+      to_p(s0, 0);
+      to_p(s1, 1);
+      to_p(s2, 2);
+      to_p(s3, 3);
+      l += ps0 + ps1;
       if (tail && kend < R.klen && t == 0) {
         // keys past kend exist in memory: their V rows must not reach the MMA (0 * Inf would poison the
         // row).  Tile A's warps clear them; tile B's P.V is issued after tile A's p_full.
-        ok = mbar_wait(&v_full[j % kTcStages], (uint32_t)((j / kTcStages) & 1));
+        const int i = 2 * j + 1, s = i % kTcSlots;
+        ok = mbar_wait(&full[s], (uint32_t)((i / kTcSlots) & 1));
         if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
-        uint8_t* v = sV + (j % kTcStages) * kKvTile;
+        uint8_t* v = sKV + s * kKvTile;
         const int r0 = kend - kb;
-        for (int i = row; i < (kTcBK - r0) * 16; i += 128) {
-          const int r = r0 + (i >> 4), c = i & 15;
+        for (int e = row; e < (kTcBK - r0) * 16; e += 128) {
+          const int r = r0 + (e >> 4), c = e & 15;
           *reinterpret_cast<uint4*>(v + (c >> 3) * kKvHalf + swz128(r, c & 7)) = make_uint4(0u, 0u, 0u, 0u);
         }
+        fence_proxy_async();
       }
-      SM_ACC(4);
-      // P (fp16) -> swizzled K-major operand tile: 64 keys = 8 chunks of 16 bytes per row
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const uint32_t* s8 = (c < 4) ? &s0[c * 8] : &s1[(c - 4) * 8];
-        uint4 v;
-        v.x = pack_half2(__uint_as_float(s8[0]), __uint_as_float(s8[1]));
-        v.y = pack_half2(__uint_as_float(s8[2]), __uint_as_float(s8[3]));
-        v.z = pack_half2(__uint_as_float(s8[4]), __uint_as_float(s8[5]));
-        v.w = pack_half2(__uint_as_float(s8[6]), __uint_as_float(s8[7]));
-        *reinterpret_cast<uint4*>(myP + swz128(row, c)) = v;
-      }
-      fence_proxy_async();
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[t]);
-      SM_ACC(5);
     }
 
     // ---- emit this row's partial (or final) result ------------------------------------------------
@@ -435,16 +400,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
     tmem_free(tmem_base, kTcCols);
   }
 }
-
-#ifdef VMK_TC_TIMING
-extern "C" VMK_API int vmk_debug_tc_timing(long long* out, int reset) {
-  long long zero[16] = {0};
-  cudaDeviceSynchronize();
-  if (out) cudaMemcpyFromSymbol(out, g_tc_timing, sizeof(zero));
-  if (reset) cudaMemcpyToSymbol(g_tc_timing, zero, sizeof(zero));
-  return 0;
-}
-#endif
 
 int launch_attn_tc(const AttnParams& p, int n_cta, cudaStream_t stream) {
   static int configured_dev = -1;
