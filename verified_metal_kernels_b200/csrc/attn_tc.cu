@@ -44,6 +44,15 @@ constexpr float kLazyRescale = 8.f;              // log2 units
 constexpr int kTcBars = 2 * kTcSlots + 2 + 2 + 2 + 2;
 constexpr int kAttnTcSmem = 2 * kQTile + kTcSlots * kKvTile + kTcBars * 8 + 16 + 1024;
 
+#ifdef VMK_TC_TIMING
+// Debug build only.  Time stamps of blocks 8..15 of CTA 0: [role][block - 8][event]
+__device__ long long g_tc_trace[5 * 8 * 8];
+#define TC_E(role, j, ev) do { if (blockIdx.x == 0 && (j) >= 8 && (j) < 16 && lane == 0) \
+    g_tc_trace[((role) * 8 + (j) - 8) * 8 + (ev)] = clock64(); } while (0)
+#else
+#define TC_E(role, j, ev) do {} while (0)
+#endif
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -127,6 +136,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
         const CUtensorMap* tm = (i & 1) ? &R.tmV : &R.tmK;
         const int kb = kbeg + (i >> 1) * kTcBK;
         uint8_t* dst = sKV + s * kKvTile;
+        TC_E(4, i >> 1, (i & 1) * 2);
         mbar_expect_tx(&full[s], kKvTile);
         // the tensor maps have 64 x 64 boxes: two boxes stacked along the keys make one [128][128 B] half
         tma_load_3d(dst, tm, 0, kb, z, &full[s]);
@@ -152,9 +162,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
         const int i = 2 * j, s = i % kTcSlots;
         if (!mbar_wait(&full[s], (uint32_t)((i / kTcSlots) & 1))) { timed_out = true; break; }
         const uint32_t kb_lo = kv_lo + s * (kKvTile >> 4);
+        TC_E(0, j, 0);
         for (int t = 0; t < ntile; ++t) {
           // S_t (and the P_t inside it) is free once P_t . V_{j-1} has completed
           if (j >= 1 && !mbar_wait(&pv_done[t], (uint32_t)((j - 1) & 1))) { timed_out = true; break; }
+          TC_E(0, j, 1 + 2 * t);
           tc_fence_after();
           const uint32_t d = tmem_base + kColS + t * 128;
           const uint32_t qa_lo = q_lo + t * (kQTile >> 4);
@@ -164,6 +176,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
                        kb_lo + (k >> 2) * (kKvHalf >> 4) + (k & 3) * 2, hi_k, idesc_qk, k > 0 ? 1u : 0u);
           }
           umma_commit(&s_full[t]);
+          TC_E(0, j, 2 + 2 * t);
         }
         if (timed_out) break;
         umma_commit(&empty[s]);
@@ -182,14 +195,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
         const int i = 2 * j + 1, s = i % kTcSlots;
         if (!mbar_wait(&full[s], (uint32_t)((i / kTcSlots) & 1))) { timed_out = true; break; }
         const uint32_t vb_lo = v_lo + s * (kKvTile >> 4);
+        TC_E(1, j, 0);
         for (int t = 0; t < ntile; ++t) {
           if (!mbar_wait(&p_full[t], (uint32_t)(j & 1))) { timed_out = true; break; }
+          TC_E(1, j, 1 + 2 * t);
           tc_fence_after();
 #pragma unroll
           for (int k = 0; k < kTcBK / 16; ++k)
             umma_f16_ts_w(tmem_base + kColO + t * 128, tmem_base + kColS + t * 128 + k * 8, vb_lo + k * (2048 >> 4), hi_v,
                           idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
           umma_commit(&pv_done[t]);
+          TC_E(1, j, 2 + 2 * t);
         }
         if (timed_out) break;
         umma_commit(&empty[s]);
@@ -245,6 +261,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
     for (int j = 0; j < nloop; ++j) {
       bool ok = mbar_wait(&s_full[t], (uint32_t)(j & 1));
       if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
+      if (quarter == 2) TC_E(2 + t, j, 0);
       tc_fence_after();
       const int kb = kbeg + j * kTcBK;
       const bool tail = kb + kTcBK > kend;
@@ -256,6 +273,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
       tmem_ld32(tS + 64, s2);
       tmem_ld32(tS + 96, s3);
       tmem_ld_wait();
+      if (quarter == 2) TC_E(2 + t, j, 1);
       float bm = -INFINITY;
       if (!edge) {
         // interior block: every key visible.  Kept free of per-element branches.
@@ -293,6 +311,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
       }
       l *= alpha;
       const float mu = (m == -INFINITY) ? 0.f : m;
+      if (quarter == 2) TC_E(2 + t, j, 2);
       // O_t is at rest here: Q.K^T of this block was only issued after P.V of the previous one had completed
       if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
@@ -307,6 +326,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
       }
       // P = exp2(score * scale - m) (exactly 0 for a hidden key: fma(-inf) = -inf), row sum, fp16 pairs written
       // over the first 64 columns of the scores
+      if (quarter == 2) TC_E(2 + t, j, 3);
       float ps0 = 0.f, ps1 = 0.f;
       auto to_p = [&](uint32_t (&sc32)[32], int c) {
         uint32_t pk[16];
@@ -325,6 +345,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
       to_p(s2, 2);
       to_p(s3, 3);
       l += ps0 + ps1;
+      if (quarter == 2) TC_E(2 + t, j, 4);
       if (tail && kend < R.klen && t == 0) {
         // keys past kend exist in memory: their V rows must not reach the MMA (0 * Inf would poison the
         // row).  Tile A's warps clear them; tile B's P.V is issued after tile A's p_full.
@@ -343,6 +364,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[t]);
+      if (quarter == 2) TC_E(2 + t, j, 5);
     }
 
     // ---- emit this row's partial (or final) result ------------------------------------------------
@@ -400,6 +422,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
     tmem_free(tmem_base, kTcCols);
   }
 }
+
+#ifdef VMK_TC_TIMING
+extern "C" VMK_API int vmk_debug_tc_trace(long long* out) {
+  cudaDeviceSynchronize();
+  return (int)cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(g_tc_trace));
+}
+#endif
 
 int launch_attn_tc(const AttnParams& p, int n_cta, cudaStream_t stream) {
   static int configured_dev = -1;
