@@ -74,3 +74,17 @@ def test_kernel_modules_refuse_cpu_only_use():
     inp = ops.load_op("spec").make_inputs(dict(B=1, L=16, k=2), seed=0)
     with pytest.raises((RuntimeError, ValueError, AssertionError)):
         load_kernel("spec")(**ops.to_torch(inp, "cpu"))
+
+
+def test_build_is_keyed_by_content_not_by_file_times(monkeypatch):
+    """A copy of the tree to another machine does not keep file times, and one rank per GPU may call the build
+    at the same moment: the library is rebuilt only when the hash of its sources and flags differs from the
+    stamp written beside it, under a file lock."""
+    from verified_metal_kernels_b200 import build
+    build.build()
+    assert os.path.exists(build.LIB + ".stamp")
+    assert not build.needs_build()
+    os.utime(build.deps()[0])                                  # a newer source file alone is not a reason
+    assert not build.needs_build()
+    monkeypatch.setenv("VMK_EXTRA_NVCC_FLAGS", "-DVMK_SOME_FLAG")
+    assert build.needs_build()                                 # other flags are
