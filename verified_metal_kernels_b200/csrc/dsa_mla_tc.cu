@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
   uint64_t* full = reinterpret_cast<uint64_t*>(sK + kMlaStages * kKTile);   // gathered tile landed (32 producer lanes)
   uint64_t* empty = full + kMlaStages;                  // tile consumed by Q.K^T and P.V       (MMA commit)
   uint64_t* empty_k = empty + kMlaStages;               // tile consumed by Q.K^T               (MMA commit)
-  uint64_t* q_full = empty_k + kMlaStages;                // Q stored to tensor memory            (4 warps)
+  uint64_t* q_full = empty_k + kMlaStages;              // Q stored to tensor memory            (8 warps)
   uint64_t* s_full = q_full + 1;                        // scores ready                         (MMA commit)
   uint64_t* s_free = s_full + 1;                        // scores consumed                      (8 warps)
   uint64_t* p_full = s_free + 1;                        // P stored to tensor memory            (8 warps)
@@ -149,7 +149,7 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
       mbar_init(&empty[s], 1);
       mbar_init(&empty_k[s], 1);
     }
-    mbar_init(q_full, 4);
+    mbar_init(q_full, 8);
     mbar_init(s_full, 1);
     mbar_init(s_free, 8);
     mbar_init(p_full, 8);
@@ -346,26 +346,27 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
 
     for (int u = u_first; u <= u_last && !timed_out; ++u) {
       const UnitWork w = unit_work(p, u, slot0, slot1);
-      if (grp == 0 && w.nblk > 0) {
-        // This head's query row -> tensor memory, two fp16 per 32-bit column, unless the previous unit left the
-        // same request's rows there.  Every Q.K^T of the previous unit has completed: this thread has seen its
-        // last scores.  Six 16-column chunks are requested at a time so that their latencies overlap.
+      if (w.nblk > 0) {
+        // This head's query row -> tensor memory, two fp16 per 32-bit column (group A the first 144 columns,
+        // group B the other 144), unless the previous unit left the same request's rows there.  Every Q.K^T of
+        // the previous unit has completed: this thread has seen its last scores.  Three 16-column chunks are
+        // requested at a time so that their latencies overlap.
         if (w.b != q_owner) {
-          const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)w.b * kMH + head) * kDK);
+          const uint4* src = reinterpret_cast<const uint4*>(p.q + ((size_t)w.b * kMH + head) * kDK) + grp * 36;
 #pragma unroll 1
-          for (int c0 = 0; c0 < 18; c0 += 6) {
-            uint4 v[24];
+          for (int c0 = 0; c0 < 9; c0 += 3) {
+            uint4 v[12];
 #pragma unroll
-            for (int i = 0; i < 24; ++i) v[i] = src[c0 * 4 + i];
+            for (int i = 0; i < 12; ++i) v[i] = src[c0 * 4 + i];
 #pragma unroll
-            for (int c = 0; c < 6; ++c) {
+            for (int c = 0; c < 3; ++c) {
               uint32_t r[16];
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
                 r[4 * i] = v[c * 4 + i].x; r[4 * i + 1] = v[c * 4 + i].y;
                 r[4 * i + 2] = v[c * 4 + i].z; r[4 * i + 3] = v[c * 4 + i].w;
               }
-              tmem_st16(lane_base + kColQ + (c0 + c) * 16, r);
+              tmem_st16(lane_base + kColQ + (grp * 9 + c0 + c) * 16, r);
             }
           }
           tmem_st_wait();
