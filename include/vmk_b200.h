@@ -126,6 +126,14 @@ VMK_API int vmk_dsa_indexer_hist(const void* iq, const void* ik, const float* w,
                                  float* scores, uint32_t* hist, int B, int L, int32_t* status, void* stream);
 VMK_API int vmk_dsa_select_hist(const float* scores, const uint32_t* hist, const int32_t* lens, int32_t* idx,
                                 int32_t* cnt, int B, int L, void* stream);
+/* Compaction of the selected rows (the reference's dsa_gather_v7, kernels/dsa_opus55_v7.py:537-550, 744-746,
+ * 853): kv_sel (B,2048,576) fp16 receives row idx[b][j] of request b at position j for j < cnt[b]; idx_sel
+ * (B,2048) receives j, so that vmk_dsa_attend(q, kv_sel, idx_sel, cnt, out, B, 2048, ...) equals
+ * vmk_dsa_attend(q, kv, idx, cnt, out, B, L, ...) bit for bit.  kv only has to be readable from the device: it
+ * may be page-locked host memory, and a host-resident cache then sends 2048 rows per request over the link
+ * instead of L.  kv_sel and idx_sel are device memory; rows at or beyond cnt[b] are left untouched. */
+VMK_API int vmk_dsa_gather(const void* kv, const int32_t* idx, const int32_t* cnt, void* kv_sel, int32_t* idx_sel,
+                           int B, int L, int32_t* status, void* stream);
 /* Stage 3 (kernels/dsa_opus55_v7.py:839-871): absorbed-MLA attention over the selected rows. */
 VMK_API size_t vmk_dsa_attend_workspace_bytes(int B);
 VMK_API int vmk_dsa_attend(const void* q, const void* kv, const int32_t* idx, const int32_t* cnt, void* out,

@@ -200,3 +200,44 @@ def test_argument_errors():
                           d["w"].data_ptr(), None, d["q"].data_ptr(), None, None, 1, 64, d["kv"].data_ptr(), 64, None,
                           None)
     assert rc == -3
+
+
+def test_gather_compacts_selected_rows_from_device_and_from_pinned_host_memory():
+    """vmk_dsa_gather: kv_sel[b, j] = kv[b, idx[b, j]] for j < cnt[b] and idx_sel = 0..cnt-1, whether the
+    cache is a device tensor or page-locked host memory read in place."""
+    B, L = 3, 5000
+    g = torch.Generator().manual_seed(5)
+    kv = torch.randn(B, L, 576, generator=g).to(torch.float16)
+    cnt = torch.tensor([2048, 1, 777], dtype=torch.int32)
+    idx = torch.zeros(B, 2048, dtype=torch.int32)
+    for b in range(B):
+        idx[b, :cnt[b]] = torch.sort(torch.randperm(L, generator=g)[:cnt[b]]).values.to(torch.int32)
+    for src in (kv.cuda(), kv.pin_memory()):
+        kv_sel, idx_sel = dsa_b200.gather(src, idx.cuda(), cnt.cuda())
+        torch.cuda.synchronize()
+        for b in range(B):
+            n = int(cnt[b])
+            assert torch.equal(kv_sel[b, :n].cpu(), kv[b, idx[b, :n].long()])
+            assert torch.equal(idx_sel[b, :n].cpu(), torch.arange(n, dtype=torch.int32))
+    _verify.assert_clean_status()
+
+
+@pytest.mark.parametrize("dist", ["randn", "ragged"])
+def test_host_resident_cache_gives_the_same_bits_as_the_device_call(dist):
+    """kernel(...) with page-locked host tensors leaves the latent cache on the host and reads only the
+    selected rows; output and selection must equal the all-on-device call bit for bit."""
+    inp = op.make_inputs(dict(B=3, L=9000), seed=21, dist=dist)
+    d = _verify.device_inputs("dsa", inp)
+    out_d, idx_d, cnt_d = dsa_b200.kernel(**d, return_selection=True)
+    host = {k: (None if v is None else v.cpu().pin_memory()) for k, v in d.items()}
+    out_h, idx_h, cnt_h = dsa_b200.kernel(**host, return_selection=True)
+    torch.cuda.synchronize()
+    assert not out_h.is_cuda
+    assert torch.equal(out_h, out_d.cpu())
+    assert torch.equal(cnt_h, cnt_d)
+    for b in range(3):
+        assert torch.equal(idx_h[b, :cnt_h[b]], idx_d[b, :cnt_d[b]])
+    # an unpinned cache is copied whole and must agree too
+    host["kv"] = d["kv"].cpu()
+    assert torch.equal(dsa_b200.kernel(**host), out_d.cpu())
+    _verify.assert_clean_status()

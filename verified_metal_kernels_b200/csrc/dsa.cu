@@ -429,6 +429,38 @@ __global__ void __launch_bounds__(128) mla_combine_kernel(const float* __restric
   dst[1] = __floats2half2_rn(acc.z / lsum, acc.w / lsum);
 }
 
+// Compaction of the selected rows: kv_sel[b][j] = kv[b][idx[b][j]] for j < cnt[b], idx_sel[b][j] = j.  One warp
+// per row (1152 B = 72 x 16 B).  `kv` only has to be readable from the device, so it may be page-locked HOST
+// memory: a caller whose latent cache lives on the host then moves 2048 rows per request over the link instead
+// of the whole cache.  grid (64, B), 256 threads: 32 rows per CTA.
+__global__ void __launch_bounds__(256) gather_rows_kernel(const __half* __restrict__ kv, const int32_t* __restrict__ idx,
+                                                          const int32_t* __restrict__ cnt, __half* __restrict__ kv_sel,
+                                                          int32_t* __restrict__ idx_sel, int L, int32_t* status) {
+  const int b = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = max(0, min(cnt[b], kTopK));
+  const uint4* src_b = reinterpret_cast<const uint4*>(kv + (size_t)b * L * kDK);
+  uint4* dst_b = reinterpret_cast<uint4*>(kv_sel + (size_t)b * kTopK * kDK);
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int j = blockIdx.x * 32 + warp * 4 + r;
+    if (j >= n) break;
+    int row = idx[(size_t)b * kTopK + j];
+    if (row < 0 || row >= L) {
+      report(status, kStatusBadIndex);
+      row = 0;
+    }
+    const uint4* src = src_b + (size_t)row * (kDK / 8);
+    uint4* dst = dst_b + (size_t)j * (kDK / 8);
+    const uint4 v0 = src[lane], v1 = src[lane + 32];
+    uint4 v2 = make_uint4(0u, 0u, 0u, 0u);
+    if (lane < 8) v2 = src[lane + 64];
+    dst[lane] = v0;
+    dst[lane + 32] = v1;
+    if (lane < 8) dst[lane + 64] = v2;
+    if (lane == 0) idx_sel[(size_t)b * kTopK + j] = j;
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------------
@@ -604,6 +636,15 @@ extern "C" size_t vmk_dsa_attend_workspace_bytes(int B) { return B > 0 ? attend_
 extern "C" int vmk_dsa_attend(const void* q, const void* kv, const int32_t* idx, const int32_t* cnt, void* out, int B,
                               int L, void* ws, size_t ws_bytes, int32_t* status, void* stream) {
   return attend_impl(q, kv, idx, cnt, out, B, L, ws, ws_bytes, status, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int vmk_dsa_gather(const void* kv, const int32_t* idx, const int32_t* cnt, void* kv_sel, int32_t* idx_sel,
+                              int B, int L, int32_t* status, void* stream) {
+  if (!kv || !idx || !cnt || !kv_sel || !idx_sel || B <= 0 || L <= 0 || B > 65535) return VMK_E_BADARG;
+  if (!aligned16(kv) || !aligned16(kv_sel)) return VMK_E_BADARG;
+  gather_rows_kernel<<<dim3(kTopK / 32, B), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(kv), idx, cnt, static_cast<__half*>(kv_sel), idx_sel, L, status);
+  return check_launch(cudaGetLastError());
 }
 
 extern "C" size_t vmk_dsa_workspace_bytes(int B, int L) { return (B > 0 && L > 0) ? plan_dsa(B, L).ws_bytes : 0; }

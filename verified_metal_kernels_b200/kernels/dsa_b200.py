@@ -10,6 +10,10 @@ from ._common import need, stage_in
 
 H, DK, DC, HI, DI, TOPK = 128, 576, 512, 64, 128, 2048
 
+# A page-locked host `kv` is read in place by stage 3's gather (only the selected rows cross the link).  False
+# makes kernel() copy it to the device whole, like every other host input.
+HOST_CACHE_IN_PLACE = True
+
 
 def _check(q, kv, iq, ik, w, lens):
     need(q, "q", torch.float16, dims=3)
@@ -30,7 +34,14 @@ def kernel(q, kv, iq, ik, w, lens=None, return_selection=False):
     """q (B,128,576), kv (B,L,576), iq (B,64,128), ik (B,L,128) fp16, w (B,64) fp32, lens (B,) int32 or
     None -> (B,128,512) fp16.  With return_selection=True also returns (idx (B,2048) int32 ascending,
     cnt (B,) int32), the integer stage's result.  Inputs are not modified; host tensors are copied in
-    and the result is returned on the host."""
+    and the result is returned on the host.
+
+    A page-locked host `kv` is NOT copied whole: the index keys go to the device, stages 1 and 2 run there,
+    and stage 3 is fed by `gather`, which reads only the selected rows out of host memory (2048 of L rows per
+    request over the link).  The result is bit-identical to the all-on-device call."""
+    if (HOST_CACHE_IN_PLACE and isinstance(kv, torch.Tensor) and not kv.is_cuda and kv.is_pinned() and kv.dim() == 3 and kv.shape[1] > TOPK
+            and kv.dtype == torch.float16 and kv.is_contiguous()):
+        return _kernel_host_cache(q, kv, iq, ik, w, lens, return_selection)
     (q, kv, iq, ik, w, lens), host = stage_in([q, kv, iq, ik, w, lens])
     B, L = _check(q, kv, iq, ik, w, lens)
     lib = _lib.lib()
@@ -49,6 +60,42 @@ def kernel(q, kv, iq, ik, w, lens=None, return_selection=False):
     if host:
         out = out.cpu()
     return (out, idx, cnt) if return_selection else out
+
+
+def _kernel_host_cache(q, kv, iq, ik, w, lens, return_selection):
+    """The op with the latent cache left in page-locked host memory (see kernel)."""
+    (q, iq, ik, w, lens), _ = stage_in([q, iq, ik, w, lens])
+    B, L = kv.shape[0], kv.shape[1]
+    if tuple(kv.shape) != (B, L, DK):
+        raise ValueError(f"kv: expected shape {(B, L, DK)}, got {tuple(kv.shape)}")
+    need(q, "q", torch.float16, shape=(B, H, DK))
+    scores, hist = indexer_hist(iq, ik, w, lens)
+    idx, cnt = select(scores, lens, hist)
+    kv_sel, idx_sel = gather(kv, idx, cnt)
+    out = attend(q, kv_sel, idx_sel, cnt).cpu()
+    return (out, idx, cnt) if return_selection else out
+
+
+def gather(kv, idx, cnt):
+    """Compaction of the selected rows: (kv_sel (B,2048,576) fp16, idx_sel (B,2048) int32 = 0..cnt-1) on the
+    device of `idx`.  `kv` (B,L,576) fp16 is a device tensor or a page-locked host tensor, which the kernel
+    reads in place."""
+    if not isinstance(kv, torch.Tensor) or kv.dtype != torch.float16 or kv.dim() != 3 or kv.shape[2] != DK:
+        raise TypeError("kv: expected a (B,L,576) fp16 tensor")
+    if not kv.is_contiguous() or not (kv.is_cuda or kv.is_pinned()):
+        raise ValueError("kv: expected a C-contiguous device tensor or page-locked host tensor")
+    B, L = kv.shape[0], kv.shape[1]
+    need(idx, "idx", torch.int32, shape=(B, TOPK))
+    need(cnt, "cnt", torch.int32, shape=(B,))
+    lib = _lib.lib()
+    dev = idx.device
+    with torch.cuda.device(dev):
+        kv_sel = torch.empty(B, TOPK, DK, dtype=torch.float16, device=dev)
+        idx_sel = torch.empty(B, TOPK, dtype=torch.int32, device=dev)
+        rc = lib.vmk_dsa_gather(kv.data_ptr(), _lib.ptr(idx), _lib.ptr(cnt), _lib.ptr(kv_sel), _lib.ptr(idx_sel), B, L,
+                                _lib.ptr(_lib.status_word(dev)), torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "vmk_dsa_gather")
+    return kv_sel, idx_sel
 
 
 def indexer(iq, ik, w, lens=None):
