@@ -2,12 +2,16 @@
 
     python bench.py                                   # 1 GPU, dsa B=128 L=131072 (+ prefix / spec side lines)
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port P \
-        bench.py --gpus 8 --steps 20 --warmup 3       # the same total workload sharded by request
+        bench.py --gpus 8 --steps 20 --warmup 3       # every rank its own batch of 128 requests (weak scaling)
+    ... bench.py --gpus 8 --scaling strong            # ONE batch of 128 requests cut over the ranks
     python bench.py --impl reference                  # the float64 NumPy truth timed on the host cores
 
 A step is one pass of the op over the whole batch.  The headline op is `dsa` on the sweep configuration
-(batch 128, cache 131072): rows/s where a row is one request's complete output.  The batch is sharded
-by request across ranks with no collective on the data path (strong scaling: the total batch is fixed).
+(batch 128, cache 131072): rows/s where a row is one request's complete output.  Requests are independent
+units: they are spread over the ranks with no collective on the data path.  By default every rank holds
+the configuration's 128 requests (weak scaling: the global batch is 128 x N); `--scaling strong` cuts one
+batch of 128 over the ranks instead (16 per GPU at N=8, where the fixed latencies of the three stages weigh
+more).
 Inputs are synthetic (seeded N(0,1) rounded to fp16, head weights N(0,1)/sqrt(64*128), as the op's
 generator draws them) and far larger than the 126 MB L2, so no flush is needed between steps.
 
@@ -376,7 +380,7 @@ def reference_arm(a):
     sec = sum(t) / len(t)
     v = 1.0 / sec
     line = dict(metric=METRIC, value=v, unit=UNIT, impl="reference", n_gpus=a.gpus, steps=a.steps, warmup=min(a.warmup, 1),
-                ms_per_step=sec * 1e3, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f64",
+                ms_per_step=sec * 1e3, higher_is_better=True, scaling=a.scaling, vs_baseline=None, dtype="f64",
                 data="synthetic", config=dict(workload="dsa B=128 L=131072 (sample: 1 request per step)"),
                 cpu_baseline=dict(value=v, unit=UNIT, cores=host_cores(), kind="port",
                                   sample="1 of 128 requests (B=1, L=131072) per step, NumPy float64, BLAS threads"),
@@ -394,6 +398,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=DSA["B"], help="total dsa batch (default: the sweep's 128)")
     ap.add_argument("--cache", type=int, default=DSA["L"], help="dsa cache length (default: the sweep's 131072)")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="N>1: weak = --batch requests per rank (default), strong = --batch requests in total")
     ap.add_argument("--no-side", action="store_true", help="skip the prefix / spec side lines")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
@@ -421,15 +427,18 @@ def main():
     fn = load_kernel("dsa")
     op = ops.load_op("dsa")
     B, L = a.batch, a.cache
-    lo, hi = shard.unit_range(B, rank, world)
-    Bl = hi - lo
+    if a.scaling == "weak":
+        Bl, B_total = B, B * world                       # this rank's own requests; global batch grows with N
+    else:
+        lo, hi = shard.unit_range(B, rank, world)
+        Bl, B_total = hi - lo, B
     inp = dsa_inputs(max(Bl, 1), L, "cuda", seed=1000 + rank)
     run = (lambda: fn(**inp)) if Bl > 0 else (lambda: None)
 
     sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
     sec, per, clocks = timed_steps(run, a.steps, a.warmup, dist, torch, sampler)
     status = _lib.read_status(torch.device("cuda", torch.cuda.current_device()))
-    value = B * a.steps / sec
+    value = B_total * a.steps / sec
 
     # end to end: pinned host tensors in, host tensor out, through the public kernel(...) call
     e2e = None
@@ -473,10 +482,10 @@ def main():
     launches = 3 + (1 if _lib.lib().vmk_dsa_attend_workspace_bytes(max(Bl, 1)) > 256 else 0)
     metric = METRIC if (B, L) == (DSA["B"], DSA["L"]) else f"dsa decode rows/s (batch {B}, cache {L})"
     line = dict(metric=metric, value=value, unit=UNIT, n_gpus=world, steps=a.steps, warmup=a.warmup,
-                ms_per_step=sec * 1e3 / a.steps, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f16",
+                ms_per_step=sec * 1e3 / a.steps, higher_is_better=True, scaling=a.scaling, vs_baseline=None, dtype="f16",
                 data="synthetic",
                 config=dict(workload=f"dsa B={B} L={L}" + (" (8-GPU sweep configuration)" if (B, L) == (DSA["B"], DSA["L"]) else ""), parallelism=f"batch-sharded x{world}",
-                            per_rank_batch=Bl, l2="inputs (GBs per rank) far larger than the 126 MB L2; no flush"),
+                            global_batch=B_total, per_rank_batch=Bl, l2="inputs (GBs per rank) far larger than the 126 MB L2; no flush"),
                 clocks=clocks, e2e=e2e, gpu_launches=launches * a.steps, device_status=status)
 
     if rank == 0:

@@ -59,20 +59,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-// D[tmem] (+)= A[tmem] * B[smem descriptor given as (low, high) words]
-__device__ __forceinline__ void umma_f16_ts_w(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
-                                              uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      ".reg .b64 db;\n"
-      "setp.ne.b32 p, %5, 0;\n"
-      "mov.b64 db, {%2, %3};\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n"
-      "}\n" ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
 __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_constant__ AttnParams p) {
   const AttnRole& R = p.a;
   extern __shared__ uint8_t smem_raw[];
@@ -202,7 +188,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
           tc_fence_after();
 #pragma unroll
           for (int k = 0; k < kTcBK / 16; ++k)
-            umma_f16_ts_w(tmem_base + kColO + t * 128, tmem_base + kColS + t * 128 + k * 8, vb_lo + k * (2048 >> 4), hi_v,
+            umma_f16_ts(tmem_base + kColO + t * 128, tmem_base + kColS + t * 128 + k * 8, vb_lo + k * (2048 >> 4), hi_v,
                           idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
           umma_commit(&pv_done[t]);
           TC_E(1, j, 2 + 2 * t);

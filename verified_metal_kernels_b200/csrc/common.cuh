@@ -89,22 +89,6 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* tm, in
       : "memory");
 }
 
-// L2 eviction policies for streaming loads: data read once should not push reusable data out of L2.
-__device__ __forceinline__ uint64_t l2_policy_evict_first() {
-  uint64_t pol;
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-  return pol;
-}
-
-__device__ __forceinline__ void tma_load_3d_hint(void* dst, const CUtensorMap* tm, int x, int y, int z, uint64_t* bar,
-                                                 uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, "
-      "%5}], [%2], %6;" ::"r"(smem_u32(dst)),
-      "l"(tm), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "l"(policy)
-      : "memory");
-}
-
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* tm, int x, int y, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
