@@ -73,6 +73,19 @@ VMK_API int vmk_spec_verify(const void* q, const void* k, const void* v, const u
                     void* out, int B, int kd, int Hq, int Hkv, int D, int L, void* ws, size_t ws_bytes,
                     int32_t* status, void* stream);
 
+/* vmk_spec_verify over a PAGED cache, the layout serving stacks keep (the reference names the paged variant as
+ * the one it left out, README.md:141-142; its contiguous launch path is kernels/spec_opus55_v7.py:467-521).
+ *   k_pages, v_pages (pages, Hkv, page_size, D) fp16: one pool for all requests; page_size a multiple of 64.
+ *   page_table (B, table_stride) int32: keys [i*page_size, (i+1)*page_size) of request b live in page
+ *   page_table[b][i]; table_stride * page_size >= L.  Entries beyond ceil(L / page_size) are not read; a page id
+ *   outside [0, pages) reads as zeros.  Rows of the last page beyond L may hold anything (NaN included).
+ * Everything else as vmk_spec_verify, same workspace size; the result equals vmk_spec_verify on the
+ * de-paged cache bit for bit. */
+VMK_API int vmk_spec_verify_paged(const void* q, const void* k_pages, const void* v_pages, const int32_t* page_table,
+                                  int pages, int page_size, int table_stride, const uint32_t* bits, int bits_words,
+                                  void* out, int B, int kd, int Hq, int Hkv, int D, int L, void* ws,
+                                  size_t ws_bytes, int32_t* status, void* stream);
+
 /* vmk_spec_verify without any caller-provided scratch.  This entry point has no counterpart in the
  * reference; it exists for hosts that may not allocate device memory around the call: a serving runtime
  * that hands every byte of HBM to its own pools at start-up and loads this library as a plug-in with no

@@ -371,9 +371,17 @@ static int prefix_impl(const void* q, const void* kp, const void* vp, const void
   return launch_combine(c, N * Hq, stream);
 }
 
+// Pages of a paged cache: pool (pages, Hkv, page_size, D) addressed through table (B, table_stride); pages == 0
+// means k, v are contiguous (B, Hkv, L, D).
+struct PageArgs {
+  const int32_t* table;
+  int pages, page_size, table_stride;
+};
+
 static int spec_impl(const void* q, const void* k, const void* v, const uint32_t* bits, int bits_words, void* out,
                      int B, int kd, int Hq, int Hkv, int D, int L, int key_lo, int key_hi, float* pm, float* plv,
-                     float* po, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream) {
+                     float* po, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream,
+                     PageArgs pg = PageArgs{nullptr, 0, 0, 0}) {
   if (B <= 0 || kd <= 0 || Hq <= 0 || Hkv <= 0 || L <= 0 || bits_words <= 0) return VMK_E_BADARG;
   if (D != kHD || Hq % Hkv != 0 || Hq / Hkv > 16) return VMK_E_UNSUPPORTED;
   if (kd > L || kd > VMK_SPEC_MAX_DRAFTS || kd > 32 * bits_words || bits_words > kMaxMaskWords) return VMK_E_UNSUPPORTED;
@@ -390,10 +398,25 @@ static int spec_impl(const void* q, const void* k, const void* v, const uint32_t
   memset(&p, 0, sizeof(p));
   p.sc = kLog2e / sqrtf((float)D);
   p.status = status;
-  int rc = make_tmap_3d(&p.a.tmK, k, D, L, (uint64_t)B * Hkv, 64, kBK);
-  if (rc) return rc;
-  rc = make_tmap_3d(&p.a.tmV, v, D, L, (uint64_t)B * Hkv, 64, kBK);
-  if (rc) return rc;
+  int rc;
+  if (pg.pages > 0) {
+    if (!pg.table || pg.page_size < kBK || pg.page_size % kBK != 0 || pg.table_stride <= 0 ||
+        (long long)pg.table_stride * pg.page_size < L)
+      return VMK_E_BADARG;
+    rc = make_tmap_3d(&p.a.tmK, k, D, pg.page_size, (uint64_t)pg.pages * Hkv, 64, kBK);
+    if (rc) return rc;
+    rc = make_tmap_3d(&p.a.tmV, v, D, pg.page_size, (uint64_t)pg.pages * Hkv, 64, kBK);
+    if (rc) return rc;
+    p.a.page_table = pg.table;
+    p.a.page_size = pg.page_size;
+    p.a.table_stride = pg.table_stride;
+    p.a.page_groups = pg.pages * Hkv;
+  } else {
+    rc = make_tmap_3d(&p.a.tmK, k, D, L, (uint64_t)B * Hkv, 64, kBK);
+    if (rc) return rc;
+    rc = make_tmap_3d(&p.a.tmV, v, D, L, (uint64_t)B * Hkv, 64, kBK);
+    if (rc) return rc;
+  }
   p.a.q = static_cast<const __half*>(q);
   p.a.out = static_cast<__half*>(out);
   p.a.bits = bits;
@@ -462,6 +485,15 @@ extern "C" int vmk_spec_verify(const void* q, const void* k, const void* v, cons
   if (!out) return VMK_E_BADARG;
   return spec_impl(q, k, v, bits, bits_words, out, B, kd, Hq, Hkv, D, L, 0, L, nullptr, nullptr, nullptr, ws,
                    ws_bytes, status, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int vmk_spec_verify_paged(const void* q, const void* k_pages, const void* v_pages, const int32_t* page_table,
+                                     int pages, int page_size, int table_stride, const uint32_t* bits, int bits_words,
+                                     void* out, int B, int kd, int Hq, int Hkv, int D, int L, void* ws, size_t ws_bytes,
+                                     int32_t* status, void* stream) {
+  if (!out || pages <= 0) return VMK_E_BADARG;
+  return spec_impl(q, k_pages, v_pages, bits, bits_words, out, B, kd, Hq, Hkv, D, L, 0, L, nullptr, nullptr, nullptr, ws,
+                   ws_bytes, status, static_cast<cudaStream_t>(stream), PageArgs{page_table, pages, page_size, table_stride});
 }
 
 extern "C" int vmk_spec_partial(const void* q, const void* k, const void* v, const uint32_t* bits, int bits_words,

@@ -34,6 +34,10 @@ struct AttnRole {
   __half* out;              // same layout as q; written only when `direct`
   const uint32_t* bits;     // draft visibility words, row (outer) at outer * bits_words; null = no mask
   const int32_t* klens;     // valid key count per outer group (ragged suffixes); null = klen
+  const int32_t* page_table;  // paged cache: page of keys [i * page_size, (i+1) * page_size) of outer group zg at
+                              // page_table[zg * table_stride + i]; the tensor maps then describe
+                              // (128, page_size, pages * Hkv).  null = one contiguous cache per group
+  int page_size, table_stride, page_groups;   // page_groups = pages * Hkv: the first group index out of range
   float* part_o;            // ((z * nsplit + split) * MP + row) * 128
   float* part_ml;           // ((z * nsplit + split) * MP + row) * 2  -> (m, l)
   int n_groups, Hkv, G, Hq;
@@ -106,12 +110,20 @@ __device__ __forceinline__ void attn_core(const AttnRole& R, float sc, int32_t* 
   auto issue = [&](int j) {
     const int s = j % STAGES;
     uint8_t* st = stage0 + s * kStageBytes;
-    const int kb = kbeg + j * kBK;
+    int kb = kbeg + j * kBK, zz = z;
+    if (R.page_table != nullptr) {
+      // a 64-key tile lies inside one page (page_size is a multiple of 64); a page id outside the pool makes
+      // the TMA coordinate out of range, which reads zeros
+      const int pi = kb / R.page_size;
+      const int pg = pi < R.table_stride ? R.page_table[(size_t)zg * R.table_stride + pi] : -1;
+      zz = (pg >= 0 && pg * R.Hkv + h < R.page_groups) ? pg * R.Hkv + h : R.page_groups;
+      kb -= pi * R.page_size;
+    }
     mbar_expect_tx(&bars[s], kStageBytes);
-    tma_load_3d(st, &R.tmK, 0, kb, z, &bars[s]);
-    tma_load_3d(st + kHalfTile, &R.tmK, 64, kb, z, &bars[s]);
-    tma_load_3d(st + 2 * kHalfTile, &R.tmV, 0, kb, z, &bars[s]);
-    tma_load_3d(st + 3 * kHalfTile, &R.tmV, 64, kb, z, &bars[s]);
+    tma_load_3d(st, &R.tmK, 0, kb, zz, &bars[s]);
+    tma_load_3d(st + kHalfTile, &R.tmK, 64, kb, zz, &bars[s]);
+    tma_load_3d(st + 2 * kHalfTile, &R.tmV, 0, kb, zz, &bars[s]);
+    tma_load_3d(st + 3 * kHalfTile, &R.tmV, 64, kb, zz, &bars[s]);
   };
   if (tid == 0) {
     for (int j = 0; j < STAGES && j < nblk; ++j) issue(j);
@@ -177,9 +189,9 @@ __device__ __forceinline__ void attn_core(const AttnRole& R, float sc, int32_t* 
     uint8_t* st = stage0 + s * kStageBytes;
     const int kb = kbeg + j * kBK;
     const bool tail = kb + kBK > kend;
-    if (tail && kend < R.klen) {
-      // Keys past kend exist in memory (ragged length / split of another rank): their V rows must not
-      // reach the MMA, where 0 * Inf would poison the row.  Uniform across the CTA.
+    if (tail && (kend < R.klen || R.page_table != nullptr)) {
+      // Keys past kend exist in memory (ragged length / split of another rank / rest of a page): their V rows
+      // must not reach the MMA, where 0 * Inf would poison the row.  Uniform across the CTA.
       const int r0 = kend - kb;
       for (int i = tid; i < (kBK - r0) * 16; i += nthreads) {
         const int r = r0 + (i >> 4), c = i & 15;

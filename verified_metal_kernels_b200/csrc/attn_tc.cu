@@ -124,11 +124,22 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
         uint8_t* dst = sKV + s * kKvTile;
         TC_E(4, i >> 1, (i & 1) * 2);
         mbar_expect_tx(&full[s], kKvTile);
-        // the tensor maps have 64 x 64 boxes: two boxes stacked along the keys make one [128][128 B] half
-        tma_load_3d(dst, tm, 0, kb, z, &full[s]);
-        tma_load_3d(dst + kKvHalf / 2, tm, 0, kb + 64, z, &full[s]);
-        tma_load_3d(dst + kKvHalf, tm, 64, kb, z, &full[s]);
-        tma_load_3d(dst + kKvHalf + kKvHalf / 2, tm, 64, kb + 64, z, &full[s]);
+        // the tensor maps have 64 x 64 boxes: two boxes stacked along the keys make one [128][128 B] half.
+        // Paged cache: each 64-key box lies inside one page; a page id outside the pool reads zeros.
+        int y0 = kb, y1 = kb + 64, z0 = z, z1 = z;
+        if (R.page_table != nullptr) {
+          const int p0 = y0 / R.page_size, p1 = y1 / R.page_size;
+          const int g0 = p0 < R.table_stride ? R.page_table[(size_t)zg * R.table_stride + p0] : -1;
+          const int g1 = p1 < R.table_stride ? R.page_table[(size_t)zg * R.table_stride + p1] : -1;
+          z0 = (g0 >= 0 && g0 * R.Hkv + h < R.page_groups) ? g0 * R.Hkv + h : R.page_groups;
+          z1 = (g1 >= 0 && g1 * R.Hkv + h < R.page_groups) ? g1 * R.Hkv + h : R.page_groups;
+          y0 -= p0 * R.page_size;
+          y1 -= p1 * R.page_size;
+        }
+        tma_load_3d(dst, tm, 0, y0, z0, &full[s]);
+        tma_load_3d(dst + kKvHalf / 2, tm, 0, y1, z1, &full[s]);
+        tma_load_3d(dst + kKvHalf, tm, 64, y0, z0, &full[s]);
+        tma_load_3d(dst + kKvHalf + kKvHalf / 2, tm, 64, y1, z1, &full[s]);
       }
     }
   } else if (warp == 1) {
@@ -332,7 +343,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
       to_p(s3, 3);
       l += ps0 + ps1;
       if (quarter == 2) TC_E(2 + t, j, 4);
-      if (tail && kend < R.klen && t == 0) {
+      if (tail && (kend < R.klen || R.page_table != nullptr) && t == 0) {
         // keys past kend exist in memory: their V rows must not reach the MMA (0 * Inf would poison the
         // row).  Tile A's warps clear them; tile B's P.V is issued after tile A's p_full.
         const int i = 2 * j + 1, s = i % kTcSlots;

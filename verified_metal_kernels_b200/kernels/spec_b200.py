@@ -43,3 +43,39 @@ def kernel(q, k, v, bits):
                                stream.cuda_stream)
     _lib.check(rc, "vmk_spec_verify")
     return out.cpu() if host else out
+
+
+def kernel_paged(q, k_pages, v_pages, page_table, L, bits):
+    """`spec` over a paged cache: k_pages / v_pages (pages, Hkv, page_size, D) fp16 are one pool for every
+    request, page_table (B, T) int32 maps keys [i * page_size, (i + 1) * page_size) of request b to page
+    page_table[b, i]; L is the (common) cache length, T * page_size >= L, page_size a multiple of 64.
+    q, bits and the result as in kernel(); the result equals kernel() on the de-paged cache bit for bit."""
+    need(q, "q", torch.float16, dims=4)
+    B, kd, Hq, D = q.shape
+    need(k_pages, "k_pages", torch.float16, dims=4)
+    pages, Hkv, page_size = k_pages.shape[0], k_pages.shape[1], k_pages.shape[2]
+    need(k_pages, "k_pages", torch.float16, shape=(pages, Hkv, page_size, D))
+    need(v_pages, "v_pages", torch.float16, shape=(pages, Hkv, page_size, D))
+    need(page_table, "page_table", torch.int32, dims=2)
+    T = page_table.shape[1]
+    need(page_table, "page_table", torch.int32, shape=(B, T))
+    if page_size % 64 != 0 or T * page_size < L or L <= 0:
+        raise ValueError("page_size must be a multiple of 64 and the table must cover L keys")
+    if not isinstance(bits, torch.Tensor) or bits.dtype != torch.int32:
+        raise TypeError("bits: expected an int32 tensor")
+    words = 1 if bits.dim() == 2 else bits.shape[2]
+    need(bits, "bits", torch.int32, shape=(B, kd) if bits.dim() == 2 else (B, kd, words))
+    lib = _lib.lib()
+    dev = q.device
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream()
+        out = torch.empty_like(q)
+        nbytes = lib.vmk_spec_workspace_bytes(B, kd, Hq, Hkv, D, L)
+        if nbytes == 0:
+            raise _lib.VmkError(-2, "spec: unsupported shape")
+        ws = _lib.workspace(nbytes, dev, stream.cuda_stream)
+        rc = lib.vmk_spec_verify_paged(_lib.ptr(q), _lib.ptr(k_pages), _lib.ptr(v_pages), _lib.ptr(page_table), pages,
+                                       page_size, T, _lib.ptr(bits), words, _lib.ptr(out), B, kd, Hq, Hkv, D, L,
+                                       _lib.ptr(ws), ws.numel(), _lib.ptr(_lib.status_word(dev)), stream.cuda_stream)
+    _lib.check(rc, "vmk_spec_verify_paged")
+    return out

@@ -146,3 +146,23 @@ def algorithmic_bytes(shape):
     B, L, kd = shape["B"], shape["L"], shape["k"]
     Hq, Hkv, d = shape.get("Hq", HQ), shape.get("Hkv", HKV), shape.get("D", D)
     return 2 * B * Hkv * L * d * 2 + 2 * B * kd * Hq * d * 2 + 4 * B * kd * ((kd + 31) // 32)
+
+
+def to_pages(k, v, page_size, seed=0, spare=3, fill=np.nan):
+    """Extension beyond the reference (which stores one contiguous cache per request): scatters k, v
+    (B,Hkv,L,D) into a shuffled page pool.  Returns (k_pages, v_pages (pages,Hkv,page_size,D), page_table
+    (B,T) int32).  The pool holds `spare` unused pages, and the unused rows of every last page, filled with
+    `fill`: a kernel that read them would show it."""
+    B, Hkv, L, D = k.shape
+    T = -(-L // page_size)
+    pages = B * T + spare
+    rng = np.random.default_rng(seed)
+    perm = rng.permutation(pages)[:B * T].astype(np.int32).reshape(B, T)
+    kp = np.full((pages, Hkv, page_size, D), fill, dtype=k.dtype)
+    vp = np.full((pages, Hkv, page_size, D), fill, dtype=v.dtype)
+    for b in range(B):
+        for i in range(T):
+            n = min(page_size, L - i * page_size)
+            kp[perm[b, i], :, :n] = k[b, :, i * page_size:i * page_size + n]
+            vp[perm[b, i], :, :n] = v[b, :, i * page_size:i * page_size + n]
+    return kp, vp, perm
