@@ -231,7 +231,8 @@ def stage_times(inp, steps, torch):
 
 def side_line(config, torch, steps):
     """rows/s and HBM fraction of one named configuration on one GPU, L2 flushed between iterations.
-    Configurations: prefix_small, spec_chain, spec_tree, dsa_small (the single-GPU ones) and prefix_sweep."""
+    Configurations: prefix_small, spec_chain, spec_tree, spec_tree_paged, dsa_small (the single-GPU ones) and
+    prefix_sweep."""
     from verified_metal_kernels_b200 import load_kernel, ops
     g = torch.Generator(device="cuda")
     g.manual_seed(1)
@@ -250,7 +251,7 @@ def side_line(config, torch, steps):
         rows = N
         name = f"prefix N={N} P={P} " + (f"S~U[0,{S}]" if sl is not None else f"S={S}")
         flops = 4.0 * N * 32 * 128 * (P + (float(sl.mean()) if sl is not None else S))
-    elif config in ("spec_chain", "spec_tree"):
+    elif config in ("spec_chain", "spec_tree", "spec_tree_paged"):
         opname = "spec"
         op = ops.load_op(opname)
         shape = dict(B=1, L=8192, k=8) if config == "spec_chain" else SPEC
@@ -263,6 +264,14 @@ def side_line(config, torch, steps):
         rows = B * kd
         name = f"spec {'chain' if config == 'spec_chain' else 'tree depth<=8'} B={B} k={kd} L={L}"
         flops = 4.0 * B * kd * 32 * 128 * L
+        if config == "spec_tree_paged":
+            # the same cache as a shuffled pool of 64-key pages (the smallest page the kernels take)
+            page = 64
+            T = L // page
+            perm = torch.randperm(B * T + 7, generator=g, device="cuda")[:B * T].to(torch.int32).reshape(B, T)
+            inp = dict(q=inp["q"], k_pages=r16(B * T + 7, 8, page, 128), v_pages=r16(B * T + 7, 8, page, 128),
+                       page_table=perm.contiguous(), L=L, bits=inp["bits"])
+            name += f", paged cache (page {page})"
     else:
         opname = "dsa"
         op = ops.load_op(opname)
@@ -272,6 +281,9 @@ def side_line(config, torch, steps):
         rows, name = shape["B"], "dsa B=8 L=32768"
         flops = 2.0 * 64 * 128 * shape["L"] * shape["B"] + 2.0 * 128 * (576 + 512) * 2048 * shape["B"]
     fn = load_kernel(opname)
+    if config == "spec_tree_paged":
+        from verified_metal_kernels_b200.kernels import spec_b200
+        fn = spec_b200.kernel_paged
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     times = []
     for i in range(steps + 3):
@@ -308,7 +320,7 @@ def side_line(config, torch, steps):
 def chain_time(opname, fn, inp, flush, torch, rounds, layers=16):
     """Median time per layer of a `layers`-long chain over up to 8 distinct copies of the inputs (within
     1.5 GiB), replayed from a CUDA graph; the L2 is flushed before every replay."""
-    per_set = sum(v.numel() * v.element_size() for v in inp.values() if v is not None)
+    per_set = sum(v.numel() * v.element_size() for v in inp.values() if isinstance(v, torch.Tensor))
     n_distinct = int(max(1, min(8, (3 << 29) // max(per_set, 1))))
     g = torch.Generator(device="cuda")
     g.manual_seed(77)
@@ -316,7 +328,7 @@ def chain_time(opname, fn, inp, flush, torch, rounds, layers=16):
     for _ in range(1, n_distinct):
         cp = {}
         for k, v in inp.items():
-            if v is None or not v.is_floating_point() or k in ("w",):
+            if not isinstance(v, torch.Tensor) or not v.is_floating_point() or k in ("w",):
                 cp[k] = v
             else:
                 cp[k] = torch.randn(v.shape, generator=g, device="cuda", dtype=torch.float32).to(v.dtype)
@@ -505,7 +517,7 @@ def main():
             del inp
             torch.cuda.empty_cache()
             line["ops"] = {c: side_line(c, torch, 10)
-                           for c in ("prefix_small", "spec_chain", "spec_tree", "dsa_small", "prefix_sweep")}
+                           for c in ("prefix_small", "spec_chain", "spec_tree", "spec_tree_paged", "dsa_small", "prefix_sweep")}
         if not a.no_cpu and world == 1:
             n = 2
             t = cpu_sample(n, L)

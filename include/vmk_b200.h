@@ -61,6 +61,22 @@ VMK_API int vmk_prefix_decode(const void* q, const void* kp, const void* vp, con
                       const int32_t* slens, void* out, int N, int Hq, int Hkv, int D, int P, int S,
                       void* ws, size_t ws_bytes, int32_t* status, void* stream);
 
+/* vmk_prefix_decode over a PAGED cache (the variant the reference names and leaves out, README.md:141-142; its
+ * contiguous launch path is kernels/prefix_opus55_v8.py:282-355).
+ *   k_pages, v_pages (pages, Hkv, page_size, D) fp16: one pool for the shared prefix and every private suffix;
+ *   page_size a multiple of 64.
+ *   prefix_table (prefix_pages) int32: keys [i*page_size, (i+1)*page_size) of the shared prefix live in page
+ *   prefix_table[i]; prefix_pages * page_size >= P.
+ *   suffix_table (N, suffix_stride) int32, slens (N) int32: request n's private suffix is slens[n] <= S keys in
+ *   pages suffix_table[n][0..]; suffix_stride * page_size >= S.  Both may be null when S == 0.
+ * A page id outside [0, pages) reads as zeros; rows of a page beyond the end of its prefix or suffix may hold
+ * anything (NaN included).  Workspace: vmk_prefix_workspace_bytes(N, Hq, Hkv, D, P, S).  The result equals
+ * vmk_prefix_decode on the de-paged tensors bit for bit. */
+VMK_API int vmk_prefix_decode_paged(const void* q, const void* k_pages, const void* v_pages, int pages, int page_size,
+                                    const int32_t* prefix_table, int prefix_pages, const int32_t* suffix_table,
+                                    int suffix_stride, const int32_t* slens, void* out, int N, int Hq, int Hkv,
+                                    int D, int P, int S, void* ws, size_t ws_bytes, int32_t* status, void* stream);
+
 /* ---- spec: speculative chain / tree verification ----------------------------------------------
  * Replaces the reference's permute / partial / combine launches (kernels/spec_opus55_v7.py:467-521).
  *   q (B,kd,Hq,D)  k,v (B,Hkv,L,D)  out (B,kd,Hq,D) fp16.  The drafts are the last kd cache positions.

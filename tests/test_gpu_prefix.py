@@ -136,3 +136,27 @@ def test_argument_errors():
                              d["vs"].data_ptr(), None, d["q"].data_ptr(), 2, 32, 8, 64, 64, 8, d["q"].data_ptr(), 1 << 30,
                              None, None)
     assert rc == -2       # head dimension other than 128
+
+
+@pytest.mark.parametrize("shape,page_size,ragged", [
+    (dict(N=4, P=1000, S=77), 64, False),        # warp-level kernel for both roles
+    (dict(N=5, P=3000, S=300), 128, True),
+    (dict(N=40, P=2100, S=200), 64, True),       # 160 stacked rows per KV head: tcgen05 kernel on the prefix
+    (dict(N=40, P=2100, S=200), 256, False),
+], ids=lambda x: str(x))
+def test_paged_cache_equals_the_contiguous_call_bit_for_bit(shape, page_size, ragged):
+    """vmk_prefix_decode_paged on one shuffled page pool holding the shared prefix and every suffix (unused
+    pages and rows filled with NaN) against vmk_prefix_decode on contiguous tensors."""
+    from verified_metal_kernels_b200.kernels import prefix_b200
+    inp = op.make_inputs(dict(shape, ragged=True) if ragged else shape, seed=17)
+    d = _verify.device_inputs("prefix", inp)
+    N, S = shape["N"], shape["S"]
+    slens = inp.get("slens")
+    ref = prefix_b200.kernel(**d)
+    kpg, vpg, ptab, stab = op.to_pages(inp["kp"], inp["vp"], inp["ks"], inp["vs"], slens, page_size, seed=3)
+    sl = torch.from_numpy(np.full(N, S, dtype=np.int32) if slens is None else np.asarray(slens, dtype=np.int32)).cuda()
+    out = prefix_b200.kernel_paged(d["q"], torch.from_numpy(kpg).cuda(), torch.from_numpy(vpg).cuda(),
+                                   torch.from_numpy(ptab).cuda(), shape["P"], torch.from_numpy(stab).cuda(), sl)
+    torch.cuda.synchronize()
+    _verify.assert_clean_status()
+    assert torch.equal(out, ref)

@@ -302,10 +302,41 @@ static void fill_role(AttnRole* r, const RolePlan& pl, uint8_t* ws) {
   r->part_ml = reinterpret_cast<float*>(ws + pl.off_ml);
 }
 
+// Pages of a paged cache: pool (pages, Hkv, page_size, D) addressed through table (groups, table_stride);
+// pages == 0 means the caches are contiguous.
+struct PageArgs {
+  const int32_t* table;
+  int pages, page_size, table_stride;
+};
+
+// Describes the role's K/V to TMA: a contiguous (groups, keys, 128) tensor, or the page pool.
+static int role_tmaps(AttnRole* r, const void* k, const void* v, int keys, uint64_t groups, int Hkv, const PageArgs& pg) {
+  if (pg.pages > 0) {
+    if (!pg.table || pg.page_size < kBK || pg.page_size % kBK != 0 || pg.table_stride <= 0 ||
+        (long long)pg.table_stride * pg.page_size < keys)
+      return VMK_E_BADARG;
+    int rc = make_tmap_3d(&r->tmK, k, kHD, pg.page_size, (uint64_t)pg.pages * Hkv, 64, kBK);
+    if (rc) return rc;
+    rc = make_tmap_3d(&r->tmV, v, kHD, pg.page_size, (uint64_t)pg.pages * Hkv, 64, kBK);
+    if (rc) return rc;
+    r->page_table = pg.table;
+    r->page_size = pg.page_size;
+    r->table_stride = pg.table_stride;
+    r->page_groups = pg.pages * Hkv;
+    return VMK_OK;
+  }
+  int rc = make_tmap_3d(&r->tmK, k, kHD, keys, groups, 64, kBK);
+  if (rc) return rc;
+  return make_tmap_3d(&r->tmV, v, kHD, keys, groups, 64, kBK);
+}
+
+// pg_a / pg_b: page tables of the shared prefix (one row) and of the private suffixes (one row per request);
+// with pages > 0, kp/vp and ks/vs all point at the page pool.
 static int prefix_impl(const void* q, const void* kp, const void* vp, const void* ks, const void* vs,
                        const int32_t* slens, void* out, int N, int Hq, int Hkv, int D, int P, int S, int key_lo,
                        int key_hi, int with_suffix, float* pm, float* plv, float* po, void* ws, size_t ws_bytes,
-                       int32_t* status, cudaStream_t stream) {
+                       int32_t* status, cudaStream_t stream, PageArgs pg_a = PageArgs{nullptr, 0, 0, 0},
+                       PageArgs pg_b = PageArgs{nullptr, 0, 0, 0}) {
   if (N <= 0 || Hq <= 0 || Hkv <= 0 || P <= 0 || S < 0) return VMK_E_BADARG;
   if (D != kHD || Hq % Hkv != 0 || Hq / Hkv > 16) return VMK_E_UNSUPPORTED;
   if ((long long)N * (Hq / Hkv) > (1 << 24)) return VMK_E_UNSUPPORTED;
@@ -323,9 +354,7 @@ static int prefix_impl(const void* q, const void* kp, const void* vp, const void
   memset(&p, 0, sizeof(p));
   p.sc = kLog2e / sqrtf((float)D);
   p.status = status;
-  int rc = make_tmap_3d(&p.a.tmK, kp, D, P, Hkv, 64, kBK);
-  if (rc) return rc;
-  rc = make_tmap_3d(&p.a.tmV, vp, D, P, Hkv, 64, kBK);
+  int rc = role_tmaps(&p.a, kp, vp, P, Hkv, Hkv, pg_a);
   if (rc) return rc;
   p.a.q = static_cast<const __half*>(q);
   p.a.n_groups = Hkv; p.a.Hkv = Hkv; p.a.G = G; p.a.Hq = Hq;
@@ -334,9 +363,7 @@ static int prefix_impl(const void* q, const void* kp, const void* vp, const void
   p.a.mask_start = INT_MAX;
   fill_role(&p.a, pl.a, static_cast<uint8_t*>(ws));
   if (pl.has_b) {
-    rc = make_tmap_3d(&p.b.tmK, ks, D, S, (uint64_t)N * Hkv, 64, kBK);
-    if (rc) return rc;
-    rc = make_tmap_3d(&p.b.tmV, vs, D, S, (uint64_t)N * Hkv, 64, kBK);
+    rc = role_tmaps(&p.b, ks, vs, S, (uint64_t)N * Hkv, Hkv, pg_b);
     if (rc) return rc;
     p.b.q = static_cast<const __half*>(q);
     p.b.klens = slens;
@@ -371,13 +398,6 @@ static int prefix_impl(const void* q, const void* kp, const void* vp, const void
   return launch_combine(c, N * Hq, stream);
 }
 
-// Pages of a paged cache: pool (pages, Hkv, page_size, D) addressed through table (B, table_stride); pages == 0
-// means k, v are contiguous (B, Hkv, L, D).
-struct PageArgs {
-  const int32_t* table;
-  int pages, page_size, table_stride;
-};
-
 static int spec_impl(const void* q, const void* k, const void* v, const uint32_t* bits, int bits_words, void* out,
                      int B, int kd, int Hq, int Hkv, int D, int L, int key_lo, int key_hi, float* pm, float* plv,
                      float* po, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream,
@@ -398,25 +418,8 @@ static int spec_impl(const void* q, const void* k, const void* v, const uint32_t
   memset(&p, 0, sizeof(p));
   p.sc = kLog2e / sqrtf((float)D);
   p.status = status;
-  int rc;
-  if (pg.pages > 0) {
-    if (!pg.table || pg.page_size < kBK || pg.page_size % kBK != 0 || pg.table_stride <= 0 ||
-        (long long)pg.table_stride * pg.page_size < L)
-      return VMK_E_BADARG;
-    rc = make_tmap_3d(&p.a.tmK, k, D, pg.page_size, (uint64_t)pg.pages * Hkv, 64, kBK);
-    if (rc) return rc;
-    rc = make_tmap_3d(&p.a.tmV, v, D, pg.page_size, (uint64_t)pg.pages * Hkv, 64, kBK);
-    if (rc) return rc;
-    p.a.page_table = pg.table;
-    p.a.page_size = pg.page_size;
-    p.a.table_stride = pg.table_stride;
-    p.a.page_groups = pg.pages * Hkv;
-  } else {
-    rc = make_tmap_3d(&p.a.tmK, k, D, L, (uint64_t)B * Hkv, 64, kBK);
-    if (rc) return rc;
-    rc = make_tmap_3d(&p.a.tmV, v, D, L, (uint64_t)B * Hkv, 64, kBK);
-    if (rc) return rc;
-  }
+  int rc = role_tmaps(&p.a, k, v, L, (uint64_t)B * Hkv, Hkv, pg);
+  if (rc) return rc;
   p.a.q = static_cast<const __half*>(q);
   p.a.out = static_cast<__half*>(out);
   p.a.bits = bits;
@@ -463,6 +466,17 @@ extern "C" int vmk_prefix_decode(const void* q, const void* kp, const void* vp, 
   if (!out) return VMK_E_BADARG;
   return prefix_impl(q, kp, vp, ks, vs, slens, out, N, Hq, Hkv, D, P, S, 0, P, 1, nullptr, nullptr, nullptr, ws,
                      ws_bytes, status, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int vmk_prefix_decode_paged(const void* q, const void* k_pages, const void* v_pages, int pages, int page_size,
+                                       const int32_t* prefix_table, int prefix_pages, const int32_t* suffix_table,
+                                       int suffix_stride, const int32_t* slens, void* out, int N, int Hq, int Hkv, int D,
+                                       int P, int S, void* ws, size_t ws_bytes, int32_t* status, void* stream) {
+  if (!out || pages <= 0 || !prefix_table || (S > 0 && (!suffix_table || !slens))) return VMK_E_BADARG;
+  return prefix_impl(q, k_pages, v_pages, k_pages, v_pages, slens, out, N, Hq, Hkv, D, P, S, 0, P, 1, nullptr, nullptr,
+                     nullptr, ws, ws_bytes, status, static_cast<cudaStream_t>(stream),
+                     PageArgs{prefix_table, pages, page_size, prefix_pages},
+                     PageArgs{suffix_table, pages, page_size, suffix_stride});
 }
 
 extern "C" int vmk_prefix_partial(const void* q, const void* kp, const void* vp, const void* ks, const void* vs,

@@ -41,3 +41,42 @@ def kernel(q, kp, vp, ks, vs, slens=None):
                                  _lib.ptr(ws), ws.numel(), _lib.ptr(_lib.status_word(dev)), stream.cuda_stream)
     _lib.check(rc, "vmk_prefix_decode")
     return out.cpu() if host else out
+
+
+def kernel_paged(q, k_pages, v_pages, prefix_table, P, suffix_table=None, slens=None):
+    """`prefix` over a paged cache: k_pages / v_pages (pages, Hkv, page_size, D) fp16 are one pool; the shared
+    prefix is P keys in pages prefix_table (T_p,) int32; request n's private suffix is slens[n] keys in pages
+    suffix_table[n] ((N, T_s) int32).  page_size a multiple of 64.  Returns (N,Hq,D) fp16, equal to kernel() on
+    the de-paged tensors bit for bit."""
+    need(q, "q", torch.float16, dims=3)
+    N, Hq, D = q.shape
+    need(k_pages, "k_pages", torch.float16, dims=4)
+    pages, Hkv, page_size = k_pages.shape[0], k_pages.shape[1], k_pages.shape[2]
+    need(k_pages, "k_pages", torch.float16, shape=(pages, Hkv, page_size, D))
+    need(v_pages, "v_pages", torch.float16, shape=(pages, Hkv, page_size, D))
+    need(prefix_table, "prefix_table", torch.int32, dims=1)
+    Tp = prefix_table.shape[0]
+    if page_size % 64 != 0 or P <= 0 or Tp * page_size < P:
+        raise ValueError("page_size must be a multiple of 64 and prefix_table must cover P keys")
+    S, Ts = 0, 0
+    if suffix_table is not None:
+        need(suffix_table, "suffix_table", torch.int32, dims=2)
+        Ts = suffix_table.shape[1]
+        need(suffix_table, "suffix_table", torch.int32, shape=(N, Ts))
+        need(slens, "slens", torch.int32, shape=(N,))
+        S = Ts * page_size
+    lib = _lib.lib()
+    dev = q.device
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream()
+        out = torch.empty_like(q)
+        nbytes = lib.vmk_prefix_workspace_bytes(N, Hq, Hkv, D, P, S)
+        if nbytes == 0:
+            raise _lib.VmkError(-2, "prefix: unsupported shape")
+        ws = _lib.workspace(nbytes, dev, stream.cuda_stream)
+        rc = lib.vmk_prefix_decode_paged(_lib.ptr(q), _lib.ptr(k_pages), _lib.ptr(v_pages), pages, page_size,
+                                         _lib.ptr(prefix_table), Tp, _lib.ptr(suffix_table), Ts, _lib.ptr(slens),
+                                         _lib.ptr(out), N, Hq, Hkv, D, P, S, _lib.ptr(ws), ws.numel(),
+                                         _lib.ptr(_lib.status_word(dev)), stream.cuda_stream)
+    _lib.check(rc, "vmk_prefix_decode_paged")
+    return out

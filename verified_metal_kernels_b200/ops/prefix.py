@@ -115,3 +115,31 @@ def algorithmic_bytes(shape, slens=None):
     Hq, Hkv, d = shape.get("Hq", HQ), shape.get("Hkv", HKV), shape.get("D", D)
     suffix_tokens = int(np.sum(slens)) if slens is not None else N * S
     return 2 * Hkv * P * d * 2 + 2 * Hkv * d * 2 * suffix_tokens + 2 * N * Hq * d * 2
+
+
+def to_pages(kp, vp, ks, vs, slens, page_size, seed=0, spare=3, fill=np.nan):
+    """Extension beyond the reference (contiguous prefix and suffixes): scatters the shared prefix
+    kp, vp (Hkv,P,D) and the private suffixes ks, vs (N,Hkv,S,D) (first slens[n] keys of each) into one
+    shuffled page pool.  Returns (k_pages, v_pages (pages,Hkv,page_size,D), prefix_table (T_p,) int32,
+    suffix_table (N,T_s) int32).  Unused pages and the unused rows of last pages hold `fill`."""
+    Hkv, P, D = kp.shape
+    N, S = ks.shape[0], ks.shape[2]
+    slens = np.full(N, S, dtype=np.int32) if slens is None else np.asarray(slens)
+    Tp, Ts = -(-P // page_size), max(1, -(-S // page_size))
+    pages = Tp + N * Ts + spare
+    perm = np.random.default_rng(seed).permutation(pages).astype(np.int32)
+    ptab, stab = perm[:Tp].copy(), perm[Tp:Tp + N * Ts].reshape(N, Ts).copy()
+    kpg = np.full((pages, Hkv, page_size, D), fill, dtype=kp.dtype)
+    vpg = np.full((pages, Hkv, page_size, D), fill, dtype=vp.dtype)
+    for i in range(Tp):
+        n = min(page_size, P - i * page_size)
+        kpg[ptab[i], :, :n] = kp[:, i * page_size:i * page_size + n]
+        vpg[ptab[i], :, :n] = vp[:, i * page_size:i * page_size + n]
+    for r in range(N):
+        for i in range(Ts):
+            n = min(page_size, int(slens[r]) - i * page_size)
+            if n <= 0:
+                break
+            kpg[stab[r, i], :, :n] = ks[r, :, i * page_size:i * page_size + n]
+            vpg[stab[r, i], :, :n] = vs[r, :, i * page_size:i * page_size + n]
+    return kpg, vpg, ptab, stab
