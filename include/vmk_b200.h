@@ -168,6 +168,20 @@ VMK_API size_t vmk_dsa_attend_workspace_bytes(int B);
 VMK_API int vmk_dsa_attend(const void* q, const void* kv, const int32_t* idx, const int32_t* cnt, void* out,
                    int B, int L, void* ws, size_t ws_bytes, int32_t* status, void* stream);
 
+/* ---- dsa on bf16 tensors --------------------------------------------------------------------------
+ * The reference's kernels read fp16 only and produce invalid values on bf16 inputs (README.md:140); these are
+ * vmk_dsa_decode (kernels/dsa_opus55_v7.py:946-977), vmk_dsa_indexer_hist and vmk_dsa_attend with q, kv, iq,
+ * ik and out in bf16 (w stays fp32, scores fp32, indices int32; vmk_dsa_select_hist and vmk_dsa_gather do not
+ * depend on the 16-bit type).  Same shapes, workspaces and status word.  Products of bf16 values are exact in
+ * fp32 as those of fp16 values are; P is rounded to bf16 before P.V and the output to bf16. */
+VMK_API int vmk_dsa_decode_bf16(const void* q, const void* kv, const void* iq, const void* ik, const float* w,
+                                const int32_t* lens, void* out, int32_t* idx_out, int32_t* cnt_out, int B, int L,
+                                void* ws, size_t ws_bytes, int32_t* status, void* stream);
+VMK_API int vmk_dsa_indexer_hist_bf16(const void* iq, const void* ik, const float* w, const int32_t* lens,
+                                      float* scores, uint32_t* hist, int B, int L, int32_t* status, void* stream);
+VMK_API int vmk_dsa_attend_bf16(const void* q, const void* kv, const int32_t* idx, const int32_t* cnt, void* out,
+                                int B, int L, void* ws, size_t ws_bytes, int32_t* status, void* stream);
+
 /* ---- merge of split partials -------------------------------------------------------------------
  * Log-sum-exp merge used after a KV split across GPUs (the reference merges its in-GPU splits the
  * same way, kernels/prefix_opus55_v8.py:211-261).  m, l (parts,rows) and o (parts,rows,D) fp32 with m

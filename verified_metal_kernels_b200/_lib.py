@@ -24,12 +24,15 @@ SIGNATURES = {
     "vmk_spec_verify_noalloc": (_i, [_vp] * 4 + [_i] + [_vp] + [_i] * 6 + [_vp, _vp]),
     "vmk_dsa_workspace_bytes": (_sz, [_i] * 2),
     "vmk_dsa_decode": (_i, [_vp] * 9 + [_i] * 2 + [_vp, _sz, _vp, _vp]),
+    "vmk_dsa_decode_bf16": (_i, [_vp] * 9 + [_i] * 2 + [_vp, _sz, _vp, _vp]),
     "vmk_dsa_indexer": (_i, [_vp] * 5 + [_i] * 2 + [_vp, _vp]),
     "vmk_dsa_select": (_i, [_vp] * 4 + [_i] * 2 + [_vp]),
     "vmk_dsa_indexer_hist": (_i, [_vp] * 6 + [_i] * 2 + [_vp, _vp]),
+    "vmk_dsa_indexer_hist_bf16": (_i, [_vp] * 6 + [_i] * 2 + [_vp, _vp]),
     "vmk_dsa_select_hist": (_i, [_vp] * 5 + [_i] * 2 + [_vp]),
     "vmk_dsa_attend_workspace_bytes": (_sz, [_i]),
     "vmk_dsa_attend": (_i, [_vp] * 5 + [_i] * 2 + [_vp, _sz, _vp, _vp]),
+    "vmk_dsa_attend_bf16": (_i, [_vp] * 5 + [_i] * 2 + [_vp, _sz, _vp, _vp]),
     "vmk_dsa_gather": (_i, [_vp] * 5 + [_i] * 2 + [_vp, _vp]),
     "vmk_lse_merge": (_i, [_vp] * 3 + [_i] * 3 + [_vp, _vp]),
     "vmk_prefix_partial": (_i, [_vp] * 6 + [_i] * 9 + [_vp] * 3 + [_vp, _sz, _vp, _vp]),

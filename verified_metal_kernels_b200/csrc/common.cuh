@@ -133,6 +133,18 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// Two fp32 -> one 32-bit word of bf16 (round to nearest even), low element first.
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// The 16-bit type of a call's tensors: fp16 (the reference's) or bf16.
+__device__ __forceinline__ uint32_t pack2(float lo, float hi, int bf16) {
+  return bf16 ? pack_bf16x2(lo, hi) : pack_half2(lo, hi);
+}
+
 // Byte offset of the 16-byte chunk `chunk` (0..7) of row `row` inside a [rows][128 B] tile written by
 // TMA with CU_TENSOR_MAP_SWIZZLE_128B (tile base 1024-byte aligned): chunk index XOR (row mod 8).
 __device__ __forceinline__ uint32_t swz128(uint32_t row, uint32_t chunk) {

@@ -12,7 +12,7 @@ constexpr int kDK = 576;       // latent row: 512 latent + 64 rope
 constexpr int kDV = 512;       // value = first 512 columns of the row
 
 int indexer_tc_launch(const CUtensorMap& tmIK, const CUtensorMap& tmIQ, const float* w, const int32_t* lens,
-                      float* scores, uint32_t* hist, int B, int L, int32_t* status, cudaStream_t stream);
+                      float* scores, uint32_t* hist, int B, int L, int32_t* status, cudaStream_t stream, int bf16);
 struct MlaTcParams {
   const __half* q;
   const __half* kv;
@@ -24,6 +24,7 @@ struct MlaTcParams {
   int B, L, ncta;
   float sc;
   int32_t* status;
+  int bf16;
 };
 int mla_tc_launch(const MlaTcParams& p, float* workspace, cudaStream_t stream);   // dsa_mla_tc.cu
 size_t mla_tc_workspace(int B);
@@ -524,9 +525,11 @@ int indexer_chunks(int B, int tiles) {
   return best;
 }
 
+// bf16 = 1: the 16-bit tensors of the call are bf16 (only the tcgen05 implementations take them).
 static int indexer_impl(const void* iq, const void* ik, const float* w, const int32_t* lens, float* scores,
-                        uint32_t* hist, int B, int L, int32_t* status, cudaStream_t stream, int variant) {
+                        uint32_t* hist, int B, int L, int32_t* status, cudaStream_t stream, int variant, int bf16 = 0) {
   if (!iq || !ik || !w || !scores || B <= 0 || L <= 0) return VMK_E_BADARG;
+  if (bf16 && variant != 1) return VMK_E_UNSUPPORTED;
   if (!aligned16(iq) || !aligned16(ik) || B > 65535) return VMK_E_BADARG;
   if (L <= kTopK) return VMK_OK;                        // nothing to rank
   IndexerParams p;
@@ -535,7 +538,7 @@ static int indexer_impl(const void* iq, const void* ik, const float* w, const in
   if (rc) return rc;
   rc = make_tmap_3d(&p.tmIQ, iq, kDI, kHI, B, 64, kHI);
   if (rc) return rc;
-  if (variant == 1) return indexer_tc_launch(p.tmIK, p.tmIQ, w, lens, scores, hist, B, L, status, stream);
+  if (variant == 1) return indexer_tc_launch(p.tmIK, p.tmIQ, w, lens, scores, hist, B, L, status, stream, bf16);
   p.w = w; p.lens = lens; p.scores = scores; p.B = B; p.L = L; p.status = status;
   static int configured_dev = -1;
   int dev = 0;
@@ -551,8 +554,9 @@ static int indexer_impl(const void* iq, const void* ik, const float* w, const in
 }
 
 static int attend_impl(const void* q, const void* kv, const int32_t* idx, const int32_t* cnt, void* out, int B,
-                       int L, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream) {
+                       int L, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream, int bf16 = 0) {
   if (!q || !kv || !idx || !cnt || !out || B <= 0 || L <= 0) return VMK_E_BADARG;
+  if (bf16 && g_attend_variant != 1) return VMK_E_UNSUPPORTED;
   if (!aligned16(q) || !aligned16(kv) || !aligned16(out) || B > 65535) return VMK_E_BADARG;
   const int ns = mla_splits(B);
   if (!ws || ws_bytes < attend_ws(B) || (reinterpret_cast<uintptr_t>(ws) & 255)) return VMK_E_WORKSPACE;
@@ -573,7 +577,7 @@ static int attend_impl(const void* q, const void* kv, const int32_t* idx, const 
   if (g_attend_variant == 1) {
     MlaTcParams t;
     t.q = p.q; t.kv = p.kv; t.idx = p.idx; t.cnt = p.cnt; t.out = p.out; t.part_o = nullptr; t.part_ml = nullptr;
-    t.B = B; t.L = L; t.ncta = 0; t.sc = p.sc; t.status = status;
+    t.B = B; t.L = L; t.ncta = 0; t.sc = p.sc; t.status = status; t.bf16 = bf16;
     return mla_tc_launch(t, static_cast<float*>(ws), stream);
   }
   static int configured_dev = -1;
@@ -649,9 +653,9 @@ extern "C" int vmk_dsa_gather(const void* kv, const int32_t* idx, const int32_t*
 
 extern "C" size_t vmk_dsa_workspace_bytes(int B, int L) { return (B > 0 && L > 0) ? plan_dsa(B, L).ws_bytes : 0; }
 
-extern "C" int vmk_dsa_decode(const void* q, const void* kv, const void* iq, const void* ik, const float* w,
-                              const int32_t* lens, void* out, int32_t* idx_out, int32_t* cnt_out, int B, int L,
-                              void* ws, size_t ws_bytes, int32_t* status, void* stream) {
+static int decode_impl(const void* q, const void* kv, const void* iq, const void* ik, const float* w,
+                       const int32_t* lens, void* out, int32_t* idx_out, int32_t* cnt_out, int B, int L, void* ws,
+                       size_t ws_bytes, int32_t* status, void* stream, int bf16) {
   if (B <= 0 || L <= 0 || !ws || (reinterpret_cast<uintptr_t>(ws) & 255)) return VMK_E_BADARG;
   const DsaPlan pl = plan_dsa(B, L);
   if (ws_bytes < pl.ws_bytes) return VMK_E_WORKSPACE;
@@ -667,10 +671,36 @@ extern "C" int vmk_dsa_decode(const void* q, const void* kv, const void* iq, con
     hist = reinterpret_cast<uint32_t*>(base + pl.off_hist);
     if (cudaMemsetAsync(hist, 0, (size_t)B * kSelBins * 4, st) != cudaSuccess) return VMK_E_LAUNCH;
   }
-  int rc = indexer_impl(iq, ik, w, lens, scores, hist, B, L, status, st, g_indexer_variant);
+  int rc = indexer_impl(iq, ik, w, lens, scores, hist, B, L, status, st, g_indexer_variant, bf16);
   if (rc) return rc;
   if (!idx || !cnt) return VMK_E_BADARG;
   rc = select_launch(scores, hist, lens, idx, cnt, B, L, st);
   if (rc) return rc;
-  return vmk_dsa_attend(q, kv, idx, cnt, out, B, L, base + pl.off_attend, attend_ws(B), status, stream);
+  return attend_impl(q, kv, idx, cnt, out, B, L, base + pl.off_attend, attend_ws(B), status, st, bf16);
+}
+
+extern "C" int vmk_dsa_decode(const void* q, const void* kv, const void* iq, const void* ik, const float* w,
+                              const int32_t* lens, void* out, int32_t* idx_out, int32_t* cnt_out, int B, int L,
+                              void* ws, size_t ws_bytes, int32_t* status, void* stream) {
+  return decode_impl(q, kv, iq, ik, w, lens, out, idx_out, cnt_out, B, L, ws, ws_bytes, status, stream, 0);
+}
+
+// ---- the same op on bf16 tensors (q, kv, iq, ik and out; w stays fp32) ---------------------------------------
+extern "C" int vmk_dsa_decode_bf16(const void* q, const void* kv, const void* iq, const void* ik, const float* w,
+                                   const int32_t* lens, void* out, int32_t* idx_out, int32_t* cnt_out, int B, int L,
+                                   void* ws, size_t ws_bytes, int32_t* status, void* stream) {
+  return decode_impl(q, kv, iq, ik, w, lens, out, idx_out, cnt_out, B, L, ws, ws_bytes, status, stream, 1);
+}
+
+extern "C" int vmk_dsa_indexer_hist_bf16(const void* iq, const void* ik, const float* w, const int32_t* lens,
+                                         float* scores, uint32_t* hist, int B, int L, int32_t* status, void* stream) {
+  if (!hist || B <= 0) return VMK_E_BADARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(hist, 0, (size_t)B * kSelBins * 4, st) != cudaSuccess) return VMK_E_LAUNCH;
+  return indexer_impl(iq, ik, w, lens, scores, hist, B, L, status, st, 1, 1);
+}
+
+extern "C" int vmk_dsa_attend_bf16(const void* q, const void* kv, const int32_t* idx, const int32_t* cnt, void* out,
+                                   int B, int L, void* ws, size_t ws_bytes, int32_t* status, void* stream) {
+  return attend_impl(q, kv, idx, cnt, out, B, L, ws, ws_bytes, status, static_cast<cudaStream_t>(stream), 1);
 }

@@ -36,11 +36,9 @@ struct TcParams {
   float* scores;
   uint32_t* hist;        // (B, 2048) counts of the top 11 key bits, accumulated with atomics; nullable
   int B, L;
+  int bf16;              // the index queries and keys are bf16 instead of fp16
   int32_t* status;
 };
-
-// Instruction descriptor: fp16 A and B (both K-major), fp32 accumulate, M = 128, N = 64.
-constexpr uint32_t kIdesc = umma_idesc_f16(kTile, kHI, 0);
 
 __device__ __forceinline__ float relu_nan(float x) { return (x < 0.f) ? 0.f : x; }
 
@@ -114,6 +112,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
     if (lane == 0) {
       if (!mbar_wait(iq_full, 0)) timed_out = true;
       const uint32_t iq_addr = smem_u32(sIQ);
+      // Instruction descriptor: fp16 or bf16 A and B (both K-major), fp32 accumulate, M = 128, N = 64.
+      const uint32_t idesc = umma_idesc_16(kTile, kHI, 0, p.bf16);
       for (int j = 0; j < nt && !timed_out; ++j) {
         const int s = j % kStages, a = j % kAccs;
         if (j >= kAccs && !mbar_wait(&acc_empty[a], (uint32_t)(((j / kAccs) - 1) & 1))) {
@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
           // K step k: 64-element half (k / 4), 32-byte offset (k % 4) inside the 128-byte swizzled row
           const uint64_t da = umma_desc_sw128(a_addr + (k >> 2) * (kTileBytes / 2) + (k & 3) * 32);
           const uint64_t db = umma_desc_sw128(iq_addr + (k >> 2) * (kIqBytes / 2) + (k & 3) * 32);
-          umma_f16(d_tmem, da, db, kIdesc, k > 0 ? 1u : 0u);
+          umma_f16(d_tmem, da, db, idesc, k > 0 ? 1u : 0u);
         }
         umma_commit(&empty[s]);        // the ring slot may be refilled once these MMAs have read it
         umma_commit(&acc_full[a]);     // the accumulator is complete
@@ -192,12 +192,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
 int indexer_chunks(int B, int tiles);
 
 int indexer_tc_launch(const CUtensorMap& tmIK, const CUtensorMap& tmIQ, const float* w, const int32_t* lens,
-                      float* scores, uint32_t* hist, int B, int L, int32_t* status, cudaStream_t stream) {
+                      float* scores, uint32_t* hist, int B, int L, int32_t* status, cudaStream_t stream, int bf16) {
   TcParams p;
   memset(&p, 0, sizeof(p));
   p.tmIK = tmIK;
   p.tmIQ = tmIQ;
   p.w = w; p.lens = lens; p.scores = scores; p.hist = hist; p.B = B; p.L = L; p.status = status;
+  p.bf16 = bf16;
   static int configured_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);

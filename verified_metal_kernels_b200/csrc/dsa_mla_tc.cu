@@ -60,6 +60,7 @@ struct MlaTcParams {
   int B, L, ncta;
   float sc;
   int32_t* status;
+  int bf16;            // q, kv and out are bf16 instead of fp16
 };
 
 // First block slot of CTA c when `total` slots are cut into `ncta` ranges.
@@ -226,7 +227,7 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
     // issuers (this warp for S = Q . K^T, the next for P . V) keep it fed: while one waits for a hand-over,
     // the other's instructions run.
     if (lane == 0) {
-      constexpr uint32_t idesc_qk = umma_idesc_f16(128, kBK, 0);
+      const uint32_t idesc_qk = umma_idesc_16(128, kBK, 0, p.bf16);
       const uint32_t hi_k = (uint32_t)(umma_desc_sw128(0) >> 32);
       const uint32_t k_lo = (uint32_t)umma_desc_sw128(0) + (smem_u32(sK) >> 4);
       const uint32_t tQ = tmem_base + kColQ, tS = tmem_base + kColS;
@@ -258,7 +259,7 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
   } else if (warp == 11) {
     // ------------------------------------------------------------------------------ P.V issuer
     if (lane == 0) {
-      constexpr uint32_t idesc_pv = umma_idesc_f16(128, 128, 1);
+      const uint32_t idesc_pv = umma_idesc_16(128, 128, 1, p.bf16);
       const uint32_t hi_v = (uint32_t)(umma_desc_sw128_mn(0, kBlkBytes, 1024) >> 32);
       const uint32_t v_lo = (uint32_t)umma_desc_sw128_mn(0, kBlkBytes, 1024) + (smem_u32(sK) >> 4);
       const uint32_t tT = tmem_base + kColT, tP = tmem_base + kColP;
@@ -421,7 +422,7 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
         {
           uint32_t pk[16];
 #pragma unroll
-          for (int e = 0; e < 16; ++e) pk[e] = pack_half2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1]));
+          for (int e = 0; e < 16; ++e) pk[e] = pack2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1]), p.bf16);
           tmem_st16(tPw, pk);
           tmem_st_wait();
           tc_fence_before();
@@ -463,10 +464,10 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           uint4 v;
-          v.x = pack_half2(o[8 * i] * inv, o[8 * i + 1] * inv);
-          v.y = pack_half2(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
-          v.z = pack_half2(o[8 * i + 4] * inv, o[8 * i + 5] * inv);
-          v.w = pack_half2(o[8 * i + 6] * inv, o[8 * i + 7] * inv);
+          v.x = pack2(o[8 * i] * inv, o[8 * i + 1] * inv, p.bf16);
+          v.y = pack2(o[8 * i + 2] * inv, o[8 * i + 3] * inv, p.bf16);
+          v.z = pack2(o[8 * i + 4] * inv, o[8 * i + 5] * inv, p.bf16);
+          v.w = pack2(o[8 * i + 6] * inv, o[8 * i + 7] * inv, p.bf16);
           reinterpret_cast<uint4*>(dst)[i] = v;
         }
       } else {
@@ -509,7 +510,7 @@ extern "C" VMK_API int vmk_debug_mla_trace(long long* out) {
 // for heads [32 hq, 32 hq + 32).  256 threads: lane = head, warp w = column groups [8w, 8w + 8).
 __global__ void __launch_bounds__(256) mla_tc_combine_kernel(const float* __restrict__ part_o,
                                                              const float* __restrict__ part_ml, int B, int ncta,
-                                                             __half* __restrict__ out) {
+                                                             __half* __restrict__ out, int bf16) {
   const int c = blockIdx.x;
   const int total = 2 * B * kUnitSlots;
   const int s = range_start(c, total, ncta);
@@ -548,10 +549,10 @@ __global__ void __launch_bounds__(256) mla_tc_combine_kernel(const float* __rest
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     uint4 v;
-    v.x = pack_half2(acc[2 * i].x * inv, acc[2 * i].y * inv);
-    v.y = pack_half2(acc[2 * i].z * inv, acc[2 * i].w * inv);
-    v.z = pack_half2(acc[2 * i + 1].x * inv, acc[2 * i + 1].y * inv);
-    v.w = pack_half2(acc[2 * i + 1].z * inv, acc[2 * i + 1].w * inv);
+    v.x = pack2(acc[2 * i].x * inv, acc[2 * i].y * inv, bf16);
+    v.y = pack2(acc[2 * i].z * inv, acc[2 * i].w * inv, bf16);
+    v.z = pack2(acc[2 * i + 1].x * inv, acc[2 * i + 1].y * inv, bf16);
+    v.w = pack2(acc[2 * i + 1].z * inv, acc[2 * i + 1].w * inv, bf16);
     reinterpret_cast<uint4*>(dst)[i] = v;
   }
 }
@@ -611,7 +612,7 @@ int mla_tc_launch(const MlaTcParams& p0, float* workspace, cudaStream_t stream) 
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return check_launch(cudaLaunchKernelEx(&cfg, mla_tc_combine_kernel, (const float*)p.part_o, (const float*)p.part_ml, p.B,
-                                         p.ncta, p.out));
+                                         p.ncta, p.out, p.bf16));
 }
 
 }  // namespace vmk

@@ -115,6 +115,10 @@ __device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t smem_addr, uint3
 __host__ __device__ constexpr uint32_t umma_idesc_f16(int M, int N, int b_mn_major) {
   return (1u << 4) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
+// The same with bf16 operands (A and B format fields = 1) when `bf16` is set.
+__host__ __device__ constexpr uint32_t umma_idesc_16(int M, int N, int b_mn_major, int bf16) {
+  return umma_idesc_f16(M, N, b_mn_major) | (bf16 ? ((1u << 7) | (1u << 10)) : 0u);
+}
 
 // 32 lanes x 16 consecutive 32-bit columns <- 16 registers per thread
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {

@@ -15,15 +15,27 @@ H, DK, DC, HI, DI, TOPK = 128, 576, 512, 64, 128, 2048
 HOST_CACHE_IN_PLACE = True
 
 
+def _half(t, name="q"):
+    """The call's 16-bit type, taken from one of its tensors: fp16 (the reference's) or bf16."""
+    if not isinstance(t, torch.Tensor) or t.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError(f"{name}: expected a float16 or bfloat16 tensor")
+    return t.dtype
+
+
+def _sfx(dt):
+    return "_bf16" if dt == torch.bfloat16 else ""
+
+
 def _check(q, kv, iq, ik, w, lens):
-    need(q, "q", torch.float16, dims=3)
+    dt = _half(q)
+    need(q, "q", dt, dims=3)
     B = q.shape[0]
-    need(q, "q", torch.float16, shape=(B, H, DK))
-    need(kv, "kv", torch.float16, dims=3)
+    need(q, "q", dt, shape=(B, H, DK))
+    need(kv, "kv", dt, dims=3)
     L = kv.shape[1]
-    need(kv, "kv", torch.float16, shape=(B, L, DK))
-    need(iq, "iq", torch.float16, shape=(B, HI, DI))
-    need(ik, "ik", torch.float16, shape=(B, L, DI))
+    need(kv, "kv", dt, shape=(B, L, DK))
+    need(iq, "iq", dt, shape=(B, HI, DI))
+    need(ik, "ik", dt, shape=(B, L, DI))
     need(w, "w", torch.float32, shape=(B, HI))
     if lens is not None:
         need(lens, "lens", torch.int32, shape=(B,))
@@ -31,8 +43,8 @@ def _check(q, kv, iq, ik, w, lens):
 
 
 def kernel(q, kv, iq, ik, w, lens=None, return_selection=False):
-    """q (B,128,576), kv (B,L,576), iq (B,64,128), ik (B,L,128) fp16, w (B,64) fp32, lens (B,) int32 or
-    None -> (B,128,512) fp16.  With return_selection=True also returns (idx (B,2048) int32 ascending,
+    """q (B,128,576), kv (B,L,576), iq (B,64,128), ik (B,L,128) fp16 (or all four bf16), w (B,64) fp32, lens
+    (B,) int32 or None -> (B,128,512) of the same 16-bit type.  With return_selection=True also returns (idx (B,2048) int32 ascending,
     cnt (B,) int32), the integer stage's result.  Inputs are not modified; host tensors are copied in
     and the result is returned on the host.
 
@@ -40,7 +52,7 @@ def kernel(q, kv, iq, ik, w, lens=None, return_selection=False):
     and stage 3 is fed by `gather`, which reads only the selected rows out of host memory (2048 of L rows per
     request over the link).  The result is bit-identical to the all-on-device call."""
     if (HOST_CACHE_IN_PLACE and isinstance(kv, torch.Tensor) and not kv.is_cuda and kv.is_pinned() and kv.dim() == 3 and kv.shape[1] > TOPK
-            and kv.dtype == torch.float16 and kv.is_contiguous()):
+            and kv.dtype in (torch.float16, torch.bfloat16) and kv.is_contiguous()):
         return _kernel_host_cache(q, kv, iq, ik, w, lens, return_selection)
     (q, kv, iq, ik, w, lens), host = stage_in([q, kv, iq, ik, w, lens])
     B, L = _check(q, kv, iq, ik, w, lens)
@@ -48,12 +60,12 @@ def kernel(q, kv, iq, ik, w, lens=None, return_selection=False):
     dev = q.device
     with torch.cuda.device(dev):
         stream = torch.cuda.current_stream()
-        out = torch.empty(B, H, DC, dtype=torch.float16, device=dev)
+        out = torch.empty(B, H, DC, dtype=q.dtype, device=dev)
         idx = torch.empty(B, TOPK, dtype=torch.int32, device=dev) if return_selection else None
         cnt = torch.empty(B, dtype=torch.int32, device=dev) if return_selection else None
         nbytes = lib.vmk_dsa_workspace_bytes(B, L)
         ws = _lib.workspace(nbytes, dev, stream.cuda_stream)
-        rc = lib.vmk_dsa_decode(_lib.ptr(q), _lib.ptr(kv), _lib.ptr(iq), _lib.ptr(ik), _lib.ptr(w), _lib.ptr(lens),
+        rc = getattr(lib, "vmk_dsa_decode" + _sfx(q.dtype))(_lib.ptr(q), _lib.ptr(kv), _lib.ptr(iq), _lib.ptr(ik), _lib.ptr(w), _lib.ptr(lens),
                                 _lib.ptr(out), _lib.ptr(idx), _lib.ptr(cnt), B, L, _lib.ptr(ws), ws.numel(),
                                 _lib.ptr(_lib.status_word(dev)), stream.cuda_stream)
     _lib.check(rc, "vmk_dsa_decode")
@@ -68,7 +80,7 @@ def _kernel_host_cache(q, kv, iq, ik, w, lens, return_selection):
     B, L = kv.shape[0], kv.shape[1]
     if tuple(kv.shape) != (B, L, DK):
         raise ValueError(f"kv: expected shape {(B, L, DK)}, got {tuple(kv.shape)}")
-    need(q, "q", torch.float16, shape=(B, H, DK))
+    need(q, "q", kv.dtype, shape=(B, H, DK))
     scores, hist = indexer_hist(iq, ik, w, lens)
     idx, cnt = select(scores, lens, hist)
     kv_sel, idx_sel = gather(kv, idx, cnt)
@@ -80,8 +92,8 @@ def gather(kv, idx, cnt):
     """Compaction of the selected rows: (kv_sel (B,2048,576) fp16, idx_sel (B,2048) int32 = 0..cnt-1) on the
     device of `idx`.  `kv` (B,L,576) fp16 is a device tensor or a page-locked host tensor, which the kernel
     reads in place."""
-    if not isinstance(kv, torch.Tensor) or kv.dtype != torch.float16 or kv.dim() != 3 or kv.shape[2] != DK:
-        raise TypeError("kv: expected a (B,L,576) fp16 tensor")
+    if not isinstance(kv, torch.Tensor) or kv.dtype not in (torch.float16, torch.bfloat16) or kv.dim() != 3 or kv.shape[2] != DK:
+        raise TypeError("kv: expected a (B,L,576) fp16 or bf16 tensor")
     if not kv.is_contiguous() or not (kv.is_cuda or kv.is_pinned()):
         raise ValueError("kv: expected a C-contiguous device tensor or page-locked host tensor")
     B, L = kv.shape[0], kv.shape[1]
@@ -90,7 +102,7 @@ def gather(kv, idx, cnt):
     lib = _lib.lib()
     dev = idx.device
     with torch.cuda.device(dev):
-        kv_sel = torch.empty(B, TOPK, DK, dtype=torch.float16, device=dev)
+        kv_sel = torch.empty(B, TOPK, DK, dtype=kv.dtype, device=dev)
         idx_sel = torch.empty(B, TOPK, dtype=torch.int32, device=dev)
         rc = lib.vmk_dsa_gather(kv.data_ptr(), _lib.ptr(idx), _lib.ptr(cnt), _lib.ptr(kv_sel), _lib.ptr(idx_sel), B, L,
                                 _lib.ptr(_lib.status_word(dev)), torch.cuda.current_stream().cuda_stream)
@@ -117,14 +129,15 @@ def indexer(iq, ik, w, lens=None):
 def indexer_hist(iq, ik, w, lens=None):
     """Stage 1 with the fused first radix level: (scores (B,L) fp32, hist (B,2048) int32)."""
     B, L = ik.shape[0], ik.shape[1]
-    need(iq, "iq", torch.float16, shape=(B, HI, DI))
-    need(ik, "ik", torch.float16, shape=(B, L, DI))
+    dt = _half(ik, "ik")
+    need(iq, "iq", dt, shape=(B, HI, DI))
+    need(ik, "ik", dt, shape=(B, L, DI))
     need(w, "w", torch.float32, shape=(B, HI))
     lib = _lib.lib()
     with torch.cuda.device(ik.device):
         scores = torch.zeros(B, L, dtype=torch.float32, device=ik.device)
         hist = torch.empty(B, 2048, dtype=torch.int32, device=ik.device)
-        rc = lib.vmk_dsa_indexer_hist(_lib.ptr(iq), _lib.ptr(ik), _lib.ptr(w), _lib.ptr(lens), _lib.ptr(scores),
+        rc = getattr(lib, "vmk_dsa_indexer_hist" + _sfx(dt))(_lib.ptr(iq), _lib.ptr(ik), _lib.ptr(w), _lib.ptr(lens), _lib.ptr(scores),
                                       _lib.ptr(hist), B, L, _lib.ptr(_lib.status_word(ik.device)),
                                       torch.cuda.current_stream().cuda_stream)
     _lib.check(rc, "vmk_dsa_indexer_hist")
@@ -152,17 +165,18 @@ def select(scores, lens=None, hist=None):
 def attend(q, kv, idx, cnt):
     """Stage 3 alone: absorbed-MLA attention over given selections."""
     B, L = kv.shape[0], kv.shape[1]
-    need(q, "q", torch.float16, shape=(B, H, DK))
-    need(kv, "kv", torch.float16, shape=(B, L, DK))
+    dt = _half(q)
+    need(q, "q", dt, shape=(B, H, DK))
+    need(kv, "kv", dt, shape=(B, L, DK))
     need(idx, "idx", torch.int32, shape=(B, TOPK))
     need(cnt, "cnt", torch.int32, shape=(B,))
     lib = _lib.lib()
     dev = q.device
     with torch.cuda.device(dev):
         stream = torch.cuda.current_stream()
-        out = torch.empty(B, H, DC, dtype=torch.float16, device=dev)
+        out = torch.empty(B, H, DC, dtype=dt, device=dev)
         ws = _lib.workspace(lib.vmk_dsa_attend_workspace_bytes(B), dev, stream.cuda_stream)
-        rc = lib.vmk_dsa_attend(_lib.ptr(q), _lib.ptr(kv), _lib.ptr(idx), _lib.ptr(cnt), _lib.ptr(out), B, L,
+        rc = getattr(lib, "vmk_dsa_attend" + _sfx(dt))(_lib.ptr(q), _lib.ptr(kv), _lib.ptr(idx), _lib.ptr(cnt), _lib.ptr(out), B, L,
                                 _lib.ptr(ws), ws.numel(), _lib.ptr(_lib.status_word(dev)), stream.cuda_stream)
     _lib.check(rc, "vmk_dsa_attend")
     return out

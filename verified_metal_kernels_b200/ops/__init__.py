@@ -11,6 +11,31 @@ KEYS = {"prefix": ["q", "kp", "vp", "ks", "vs", "slens"],
         "dsa": ["q", "kv", "iq", "ik", "w", "lens"]}
 
 
+# The 16-bit tensors of each op (everything else keeps its type whatever the 16-bit type is).
+HALF_KEYS = {"prefix": ["q", "kp", "vp", "ks", "vs"], "spec": ["q", "k", "v"], "dsa": ["q", "kv", "iq", "ik"]}
+
+
+def round_bf16(a):
+    """float array -> float32 array of the nearest bf16 values (round to nearest even; NaN and Inf kept)."""
+    import numpy as np
+    x = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+    r = ((x + np.uint32(0x7FFF) + ((x >> np.uint32(16)) & np.uint32(1))) & np.uint32(0xFFFF0000))
+    nan = ((x & np.uint32(0x7F800000)) == np.uint32(0x7F800000)) & ((x & np.uint32(0x007FFFFF)) != 0)
+    r = np.where(nan, np.uint32(0x7FC00000) | (x & np.uint32(0x80000000)), r).astype(np.uint32)
+    return r.view(np.float32)
+
+
+def as_bf16(name, inputs):
+    """Extension beyond the reference (its kernels are fp16-only): the same seeded inputs with the 16-bit
+    tensors rounded to bf16 instead of fp16.  They are returned as float32 arrays holding bf16 values, which is
+    what the float64 oracle reads; to_torch(..., bf16=name) turns them into torch.bfloat16."""
+    out = dict(inputs)
+    for k in HALF_KEYS[name]:
+        if out.get(k) is not None:
+            out[k] = round_bf16(out[k])
+    return out
+
+
 def load_op(name):
     if name not in OPS:
         raise ValueError(f"unknown op {name!r}; expected one of {OPS}")
@@ -31,10 +56,13 @@ def cases(op):
     return out
 
 
-def to_torch(inputs, device):
-    """Move a generator's NumPy dict to torch tensors on `device` (None entries stay None)."""
+def to_torch(inputs, device, bf16=None):
+    """Move a generator's NumPy dict to torch tensors on `device` (None entries stay None).  bf16 = an op name:
+    that op's 16-bit tensors (float32 arrays of bf16 values, see as_bf16) become torch.bfloat16."""
     import torch
     out = {}
     for k, v in inputs.items():
         out[k] = None if v is None else torch.from_numpy(v).to(device)
+        if bf16 is not None and v is not None and k in HALF_KEYS[bf16]:
+            out[k] = out[k].to(torch.bfloat16)
     return out
