@@ -168,6 +168,17 @@ VMK_API size_t vmk_dsa_attend_workspace_bytes(int B);
 VMK_API int vmk_dsa_attend(const void* q, const void* kv, const int32_t* idx, const int32_t* cnt, void* out,
                    int B, int L, void* ws, size_t ws_bytes, int32_t* status, void* stream);
 
+/* ---- prefix and spec on bf16 tensors ---------------------------------------------------------------
+ * vmk_prefix_decode (kernels/prefix_opus55_v8.py:282-355) and vmk_spec_verify (kernels/spec_opus55_v7.py:467-521)
+ * with q, K, V and out in bf16; the reference's kernels are fp16 only (README.md:140).  Same shapes, workspaces,
+ * masks and status word; scores, statistics and accumulators stay fp32, P is rounded to bf16 before P.V. */
+VMK_API int vmk_prefix_decode_bf16(const void* q, const void* kp, const void* vp, const void* ks, const void* vs,
+                                   const int32_t* slens, void* out, int N, int Hq, int Hkv, int D, int P, int S,
+                                   void* ws, size_t ws_bytes, int32_t* status, void* stream);
+VMK_API int vmk_spec_verify_bf16(const void* q, const void* k, const void* v, const uint32_t* bits, int bits_words,
+                                 void* out, int B, int kd, int Hq, int Hkv, int D, int L, void* ws, size_t ws_bytes,
+                                 int32_t* status, void* stream);
+
 /* ---- dsa on bf16 tensors --------------------------------------------------------------------------
  * The reference's kernels read fp16 only and produce invalid values on bf16 inputs (README.md:140); these are
  * vmk_dsa_decode (kernels/dsa_opus55_v7.py:946-977), vmk_dsa_indexer_hist and vmk_dsa_attend with q, kv, iq,

@@ -61,3 +61,44 @@ def test_dsa_bf16_needs_the_tensor_memory_kernels():
         assert e.value.code == -2
     finally:
         dsa_b200.set_attend_variant("tcgen05")
+
+
+prefix = ops.load_op("prefix")
+spec = ops.load_op("spec")
+
+
+@pytest.mark.parametrize("shape,dist", [(dict(N=4, P=1000, S=77), "randn"), (dict(N=8, P=4096, S=256), "randn"),
+                                        (dict(N=6, P=777, S=300, ragged=True), "randn"),
+                                        (dict(N=3, P=640, S=5), "large"),
+                                        (dict(N=40, P=2100, S=200), "randn"),            # tcgen05 kernel on the prefix
+                                        (dict(N=70, P=5000, S=64, ragged=True), "randn")], ids=lambda x: str(x))
+def test_prefix_bf16_against_the_oracle(shape, dist):
+    from verified_metal_kernels_b200.kernels import prefix_b200
+    inp = ops.as_bf16("prefix", prefix.make_inputs(shape, seed=23, dist=dist))
+    d = ops.to_torch(ops.cand_inputs("prefix", inp), "cuda", bf16="prefix")
+    out = prefix_b200.kernel(**d)
+    torch.cuda.synchronize()
+    _verify.assert_clean_status()
+    assert out.dtype == torch.bfloat16
+    truth = ref64.REF64["prefix"](**{k: inp.get(k) for k in ops.KEYS["prefix"]})
+    rep = judge.judge_l2(out.float().cpu().numpy(), truth, half=True, dist=dist)
+    assert rep["ok"], rep
+    # bf16 keeps 8 significand bits: the output rounding alone is 2^-9 of the row's magnitude
+    assert rep["err_max"] <= 6e-3, rep
+
+
+@pytest.mark.parametrize("shape,dist", [(dict(B=2, L=1500, k=8), "randn"), (dict(B=1, L=8192, k=8), "chain"),
+                                        (dict(B=2, L=700, k=16), "large"),
+                                        (dict(B=2, L=3000, k=32), "randn"),               # tcgen05 kernel
+                                        (dict(B=1, L=4096, k=64, max_depth=8), "randn")], ids=lambda x: str(x))
+def test_spec_bf16_against_the_oracle(shape, dist):
+    from verified_metal_kernels_b200.kernels import spec_b200
+    inp = ops.as_bf16("spec", spec.make_inputs(shape, seed=29, dist=dist))
+    d = ops.to_torch(ops.cand_inputs("spec", inp), "cuda", bf16="spec")
+    out = spec_b200.kernel(**d)
+    torch.cuda.synchronize()
+    _verify.assert_clean_status()
+    assert out.dtype == torch.bfloat16
+    truth = ref64.REF64["spec"](**{k: inp.get(k) for k in ops.KEYS["spec"]})
+    rep = judge.judge_l2(out.float().cpu().numpy(), truth, half=True, dist=dist)
+    assert rep["ok"] and rep["err_max"] <= 6e-3, rep

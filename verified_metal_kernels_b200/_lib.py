@@ -17,8 +17,10 @@ SIGNATURES = {
     "vmk_error_string": (_c.c_char_p, [_i]),
     "vmk_prefix_workspace_bytes": (_sz, [_i] * 6),
     "vmk_prefix_decode": (_i, [_vp] * 7 + [_i] * 6 + [_vp, _sz, _vp, _vp]),
+    "vmk_prefix_decode_bf16": (_i, [_vp] * 7 + [_i] * 6 + [_vp, _sz, _vp, _vp]),
     "vmk_spec_workspace_bytes": (_sz, [_i] * 6),
     "vmk_spec_verify": (_i, [_vp] * 4 + [_i] + [_vp] + [_i] * 6 + [_vp, _sz, _vp, _vp]),
+    "vmk_spec_verify_bf16": (_i, [_vp] * 4 + [_i] + [_vp] + [_i] * 6 + [_vp, _sz, _vp, _vp]),
     "vmk_prefix_decode_paged": (_i, [_vp] * 3 + [_i] * 2 + [_vp, _i, _vp, _i, _vp, _vp] + [_i] * 6 + [_vp, _sz, _vp, _vp]),
     "vmk_spec_verify_paged": (_i, [_vp] * 4 + [_i] * 3 + [_vp, _i, _vp] + [_i] * 6 + [_vp, _sz, _vp, _vp]),
     "vmk_spec_verify_noalloc": (_i, [_vp] * 4 + [_i] + [_vp] + [_i] * 6 + [_vp, _vp]),

@@ -7,15 +7,15 @@ namespace vmk {
 // ------------------------------------------------------------------------------------------------
 // kernels
 // ------------------------------------------------------------------------------------------------
-template <int RT, int KS, int STAGES, bool HAS_B, int MIN_CTAS>
+template <int RT, int KS, int STAGES, bool HAS_B, int MIN_CTAS, bool BF>
 __global__ void __launch_bounds__(256, MIN_CTAS) attn_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int cta = blockIdx.x;
   if (!HAS_B || cta < p.a.n_cta) {
-    attn_core<RT, KS, STAGES>(p.a, p.sc, p.status, cta, smem);
+    attn_core<RT, KS, STAGES, BF>(p.a, p.sc, p.status, cta, smem);
   } else {
-    attn_core<1, 4, STAGES>(p.b, p.sc, p.status, cta - p.a.n_cta, smem);
+    attn_core<1, 4, STAGES, BF>(p.b, p.sc, p.status, cta - p.a.n_cta, smem);
   }
 }
 
@@ -29,7 +29,8 @@ struct CombineParams {
   CombineSide a, b;
   int has_b;
   int Hkv, G, Hq;
-  __half* out;       // (outers, Hq, 128) fp16, or null
+  __half* out;       // (outers, Hq, 128) fp16 or bf16, or null
+  int bf16;
   float* pm;         // when out is null: un-normalised merged partial per row
   float* pl;
   float* po;
@@ -79,7 +80,7 @@ __global__ void __launch_bounds__(128) combine_kernel(const CombineParams p) {
     lsum += w * s_l[t];
   }
   if (p.out != nullptr) {
-    p.out[(size_t)row * kHD + d] = __float2half(acc / lsum);
+    store16(&p.out[(size_t)row * kHD + d], acc / lsum, p.bf16);
   } else {
     p.po[(size_t)row * kHD + d] = acc;
     if (d == 0) {
@@ -108,7 +109,7 @@ static int launch_combine(const CombineParams& c, int rows, cudaStream_t stream)
 // Merge of `parts` partials per row (used after an exchange between GPUs).
 __global__ void __launch_bounds__(128) lse_merge_kernel(const float* __restrict__ m, const float* __restrict__ l,
                                                          const float* __restrict__ o, int parts, int rows, int D,
-                                                         __half* __restrict__ out) {
+                                                         __half* __restrict__ out, int bf16) {
   const int row = blockIdx.x;
   float M = -INFINITY;
   for (int s = 0; s < parts; ++s) M = fmaxf(M, m[(size_t)s * rows + row]);
@@ -120,7 +121,7 @@ __global__ void __launch_bounds__(128) lse_merge_kernel(const float* __restrict_
       acc += w * o[((size_t)s * rows + row) * D + d];
       lsum += w * l[(size_t)s * rows + row];
     }
-    out[(size_t)row * D + d] = __float2half(acc / lsum);
+    store16(&out[(size_t)row * D + d], acc / lsum, bf16);
   }
 }
 
@@ -262,10 +263,10 @@ static SpecPlan plan_spec(int B, int kd, int Hq, int Hkv, int key_lo, int key_hi
 // ------------------------------------------------------------------------------------------------
 // launch
 // ------------------------------------------------------------------------------------------------
-template <int RT, int KS, int STAGES, bool HAS_B, int MIN_CTAS>
+template <int RT, int KS, int STAGES, bool HAS_B, int MIN_CTAS, bool BF>
 static int launch_attn_inst(const AttnParams& p, int n_cta, cudaStream_t stream) {
   constexpr int smem = attn_smem_bytes<(RT > 1 ? RT : 1), STAGES>();
-  auto kern = attn_kernel<RT, KS, STAGES, HAS_B, MIN_CTAS>;
+  auto kern = attn_kernel<RT, KS, STAGES, HAS_B, MIN_CTAS, BF>;
   static bool configured = false;   // per instantiation; the attribute is per device function
   static int configured_dev = -1;
   int dev = 0;
@@ -280,14 +281,19 @@ static int launch_attn_inst(const AttnParams& p, int n_cta, cudaStream_t stream)
   return check_launch(cudaGetLastError());
 }
 
+template <bool HAS_B, bool BF>
+static int launch_attn_dt(const AttnParams& p, int rt, int n_cta, cudaStream_t stream) {
+  switch (rt) {
+    case 1: return launch_attn_inst<1, 4, 3, HAS_B, 2, BF>(p, n_cta, stream);
+    case 2: return launch_attn_inst<2, 4, 3, HAS_B, 2, BF>(p, n_cta, stream);
+    case 4: return launch_attn_inst<4, 2, 4, HAS_B, 1, BF>(p, n_cta, stream);
+    default: return launch_attn_inst<8, 1, 4, HAS_B, 1, BF>(p, n_cta, stream);
+  }
+}
+
 template <bool HAS_B>
 static int launch_attn(const AttnParams& p, int rt, int n_cta, cudaStream_t stream) {
-  switch (rt) {
-    case 1: return launch_attn_inst<1, 4, 3, HAS_B, 2>(p, n_cta, stream);
-    case 2: return launch_attn_inst<2, 4, 3, HAS_B, 2>(p, n_cta, stream);
-    case 4: return launch_attn_inst<4, 2, 4, HAS_B, 1>(p, n_cta, stream);
-    default: return launch_attn_inst<8, 1, 4, HAS_B, 1>(p, n_cta, stream);
-  }
+  return p.bf16 ? launch_attn_dt<HAS_B, true>(p, rt, n_cta, stream) : launch_attn_dt<HAS_B, false>(p, rt, n_cta, stream);
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -336,7 +342,7 @@ static int prefix_impl(const void* q, const void* kp, const void* vp, const void
                        const int32_t* slens, void* out, int N, int Hq, int Hkv, int D, int P, int S, int key_lo,
                        int key_hi, int with_suffix, float* pm, float* plv, float* po, void* ws, size_t ws_bytes,
                        int32_t* status, cudaStream_t stream, PageArgs pg_a = PageArgs{nullptr, 0, 0, 0},
-                       PageArgs pg_b = PageArgs{nullptr, 0, 0, 0}) {
+                       PageArgs pg_b = PageArgs{nullptr, 0, 0, 0}, int bf16 = 0) {
   if (N <= 0 || Hq <= 0 || Hkv <= 0 || P <= 0 || S < 0) return VMK_E_BADARG;
   if (D != kHD || Hq % Hkv != 0 || Hq / Hkv > 16) return VMK_E_UNSUPPORTED;
   if ((long long)N * (Hq / Hkv) > (1 << 24)) return VMK_E_UNSUPPORTED;
@@ -354,6 +360,7 @@ static int prefix_impl(const void* q, const void* kp, const void* vp, const void
   memset(&p, 0, sizeof(p));
   p.sc = kLog2e / sqrtf((float)D);
   p.status = status;
+  p.bf16 = bf16;
   int rc = role_tmaps(&p.a, kp, vp, P, Hkv, Hkv, pg_a);
   if (rc) return rc;
   p.a.q = static_cast<const __half*>(q);
@@ -394,6 +401,7 @@ static int prefix_impl(const void* q, const void* kp, const void* vp, const void
   if (pl.has_b) c.b = CombineSide{p.b.part_o, p.b.part_ml, pl.b.nsplit, pl.b.MP, 1};
   c.Hkv = Hkv; c.G = G; c.Hq = Hq;
   c.out = static_cast<__half*>(out);
+  c.bf16 = bf16;
   c.pm = pm; c.pl = plv; c.po = po;
   return launch_combine(c, N * Hq, stream);
 }
@@ -401,7 +409,7 @@ static int prefix_impl(const void* q, const void* kp, const void* vp, const void
 static int spec_impl(const void* q, const void* k, const void* v, const uint32_t* bits, int bits_words, void* out,
                      int B, int kd, int Hq, int Hkv, int D, int L, int key_lo, int key_hi, float* pm, float* plv,
                      float* po, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream,
-                     PageArgs pg = PageArgs{nullptr, 0, 0, 0}) {
+                     PageArgs pg = PageArgs{nullptr, 0, 0, 0}, int bf16 = 0) {
   if (B <= 0 || kd <= 0 || Hq <= 0 || Hkv <= 0 || L <= 0 || bits_words <= 0) return VMK_E_BADARG;
   if (D != kHD || Hq % Hkv != 0 || Hq / Hkv > 16) return VMK_E_UNSUPPORTED;
   if (kd > L || kd > VMK_SPEC_MAX_DRAFTS || kd > 32 * bits_words || bits_words > kMaxMaskWords) return VMK_E_UNSUPPORTED;
@@ -418,6 +426,7 @@ static int spec_impl(const void* q, const void* k, const void* v, const uint32_t
   memset(&p, 0, sizeof(p));
   p.sc = kLog2e / sqrtf((float)D);
   p.status = status;
+  p.bf16 = bf16;
   int rc = role_tmaps(&p.a, k, v, L, (uint64_t)B * Hkv, Hkv, pg);
   if (rc) return rc;
   p.a.q = static_cast<const __half*>(q);
@@ -438,6 +447,7 @@ static int spec_impl(const void* q, const void* k, const void* v, const uint32_t
   c.a = CombineSide{p.a.part_o, p.a.part_ml, pl.a.nsplit, pl.a.MP, kd};
   c.Hkv = Hkv; c.G = G; c.Hq = Hq;
   c.out = static_cast<__half*>(out);
+  c.bf16 = bf16;
   c.pm = pm; c.pl = plv; c.po = po;
   return launch_combine(c, B * kd * Hq, stream);
 }
@@ -564,6 +574,24 @@ extern "C" int vmk_lse_merge(const float* m, const float* l, const float* o, int
                              void* stream) {
   if (!m || !l || !o || !out || parts <= 0 || rows <= 0 || D <= 0) return VMK_E_BADARG;
   lse_merge_kernel<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(m, l, o, parts, rows, D,
-                                                                          static_cast<__half*>(out));
+                                                                          static_cast<__half*>(out), 0);
   return check_launch(cudaGetLastError());
+}
+
+// ---- the same ops on bf16 tensors (q, K, V and out) --------------------------------------------------------
+extern "C" int vmk_prefix_decode_bf16(const void* q, const void* kp, const void* vp, const void* ks, const void* vs,
+                                      const int32_t* slens, void* out, int N, int Hq, int Hkv, int D, int P, int S,
+                                      void* ws, size_t ws_bytes, int32_t* status, void* stream) {
+  if (!out) return VMK_E_BADARG;
+  return prefix_impl(q, kp, vp, ks, vs, slens, out, N, Hq, Hkv, D, P, S, 0, P, 1, nullptr, nullptr, nullptr, ws,
+                     ws_bytes, status, static_cast<cudaStream_t>(stream), PageArgs{nullptr, 0, 0, 0},
+                     PageArgs{nullptr, 0, 0, 0}, 1);
+}
+
+extern "C" int vmk_spec_verify_bf16(const void* q, const void* k, const void* v, const uint32_t* bits, int bits_words,
+                                    void* out, int B, int kd, int Hq, int Hkv, int D, int L, void* ws, size_t ws_bytes,
+                                    int32_t* status, void* stream) {
+  if (!out) return VMK_E_BADARG;
+  return spec_impl(q, k, v, bits, bits_words, out, B, kd, Hq, Hkv, D, L, 0, L, nullptr, nullptr, nullptr, ws,
+                   ws_bytes, status, static_cast<cudaStream_t>(stream), PageArgs{nullptr, 0, 0, 0}, 1);
 }

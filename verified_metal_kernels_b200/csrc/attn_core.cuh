@@ -57,6 +57,7 @@ struct AttnParams {
   AttnRole a, b;            // b is used only by kernels instantiated with HAS_B
   float sc;                 // softmax scale * log2(e)
   int32_t* status;
+  int bf16;                 // q, K, V and out are bf16 instead of fp16
 };
 
 template <int RT, int STAGES>
@@ -64,8 +65,12 @@ constexpr int attn_smem_bytes() {
   return STAGES * kStageBytes + RT * 16 * kQStride + STAGES * 8 + 1024 /* alignment slack */;
 }
 
-template <int RT, int KS, int STAGES>
+template <int RT, int KS, int STAGES, bool BF>
 __device__ __forceinline__ void attn_core(const AttnRole& R, float sc, int32_t* status, int cta, uint8_t* smem) {
+  // the warp-level MMA of the call's 16-bit type
+  auto mma = [](float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    if constexpr (BF) mma_16816_bf16(c, a, b0, b1); else mma_16816(c, a, b0, b1);
+  };
   constexpr int NW = RT * KS;          // computing warps
   constexpr int KPW = kBK / KS;        // keys per warp per block
   constexpr int NT8 = KPW / 8;         // score n-tiles per warp
@@ -216,8 +221,8 @@ __device__ __forceinline__ void attn_core(const AttnRole& R, float sc, int32_t* 
         const uint32_t ch = kk * 2 + (mi & 1);
         uint32_t b[4];
         ldsm_x4(b, smem_u32(st + (ch >> 3) * kHalfTile + swz128(key, ch & 7)));
-        mma_16816(sacc[2 * np], qf[kk], b[0], b[1]);
-        mma_16816(sacc[2 * np + 1], qf[kk], b[2], b[3]);
+        mma(sacc[2 * np], qf[kk], b[0], b[1]);
+        mma(sacc[2 * np + 1], qf[kk], b[2], b[3]);
       }
     }
 
@@ -279,10 +284,10 @@ __device__ __forceinline__ void attn_core(const AttnRole& R, float sc, int32_t* 
 #pragma unroll
     for (int k2 = 0; k2 < KPW / 16; ++k2) {
       uint32_t pa[4];
-      pa[0] = pack_half2(sacc[2 * k2][0], sacc[2 * k2][1]);
-      pa[1] = pack_half2(sacc[2 * k2][2], sacc[2 * k2][3]);
-      pa[2] = pack_half2(sacc[2 * k2 + 1][0], sacc[2 * k2 + 1][1]);
-      pa[3] = pack_half2(sacc[2 * k2 + 1][2], sacc[2 * k2 + 1][3]);
+      pa[0] = pack2(sacc[2 * k2][0], sacc[2 * k2][1], BF);
+      pa[1] = pack2(sacc[2 * k2][2], sacc[2 * k2][3], BF);
+      pa[2] = pack2(sacc[2 * k2 + 1][0], sacc[2 * k2 + 1][1], BF);
+      pa[3] = pack2(sacc[2 * k2 + 1][2], sacc[2 * k2 + 1][3], BF);
 #pragma unroll
       for (int dp = 0; dp < 8; ++dp) {
         // transposed matrices: (keys 0-7, d 0-7) (keys 8-15, d 0-7) (keys 0-7, d 8-15) (keys 8-15, d 8-15)
@@ -291,8 +296,8 @@ __device__ __forceinline__ void attn_core(const AttnRole& R, float sc, int32_t* 
         const uint32_t ch = dp * 2 + (mi >> 1);
         uint32_t b[4];
         ldsm_x4_t(b, smem_u32(st + (2 + (ch >> 3)) * kHalfTile + swz128(key, ch & 7)));
-        mma_16816(oacc[2 * dp], pa, b[0], b[1]);
-        mma_16816(oacc[2 * dp + 1], pa, b[2], b[3]);
+        mma(oacc[2 * dp], pa, b[0], b[1]);
+        mma(oacc[2 * dp + 1], pa, b[2], b[3]);
       }
     }
   }
@@ -341,7 +346,7 @@ __device__ __forceinline__ void attn_core(const AttnRole& R, float sc, int32_t* 
     if (R.direct) {
       const size_t outer = (size_t)zg * R.rows_outer + grow / R.G;
       const int head = h * R.G + grow % R.G;
-      R.out[(outer * R.Hq + head) * kHD + d] = __float2half(acc / lsum);
+      store16(&R.out[(outer * R.Hq + head) * kHD + d], acc / lsum, BF);
     } else {
       R.part_o[(slot * R.MP + grow) * kHD + d] = acc;
       if (d == 0) {

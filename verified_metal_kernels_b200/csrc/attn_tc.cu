@@ -24,6 +24,8 @@
 // Partials (m, l, o) per row are emitted exactly as by the warp-level kernel, so the combine pass and
 // the multi-GPU merge are shared.  Every mbarrier wait is bounded; a wait that runs out sets the status
 // word and the CTA winds down through the common exit, where tensor memory is freed.
+#include <type_traits>
+
 #include "attn_core.cuh"
 #include "tcgen05.cuh"
 
@@ -145,7 +147,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
   } else if (warp == 1) {
     // ------------------------------------------------------------------------------ Q.K^T issuer
     if (lane == 0 && nblk > 0) {
-      constexpr uint32_t idesc_qk = umma_idesc_f16(128, kTcBK, 0);
+      const uint32_t idesc_qk = umma_idesc_16(128, kTcBK, 0, p.bf16);
       const int ntile = has_b ? 2 : 1;
       // Descriptor words.  High words are constants of the layout; low words are (address >> 4) plus a
       // constant per K step: +2 per 32-byte step inside a 128-byte swizzled row, + half-tile / 16 for the
@@ -182,7 +184,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
   } else if (warp == 10) {
     // ------------------------------------------------------------------------------ P.V issuer
     if (lane == 0 && nblk > 0) {
-      constexpr uint32_t idesc_pv = umma_idesc_f16(128, 128, 1);
+      const uint32_t idesc_pv = umma_idesc_16(128, 128, 1, p.bf16);
       const int ntile = has_b ? 2 : 1;
       // V rows 16k .. 16k+16 (keys) x 128 d, MN-major: 8-key groups 1024 B apart (+128 per 16-key step), the
       // two 64-wide d halves kKvHalf apart.  P_t[:, 16k .. 16k+16) = 8 columns of packed fp16 pairs.
@@ -325,7 +327,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
       // over the first 64 columns of the scores
       if (quarter == 2) TC_E(2 + t, j, 3);
       float ps0 = 0.f, ps1 = 0.f;
-      auto to_p = [&](uint32_t (&sc32)[32], int c) {
+      // (the 16-bit type is a compile-time tag here: a per-element choice would put both conversions on the
+      // XU pipe, which is the one this loop is bound by)
+      auto to_p = [&](auto bf_tag, uint32_t (&sc32)[32], int c) {
+        constexpr bool BF = decltype(bf_tag)::value;
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -333,14 +338,21 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
           const float b = fast_exp2(fmaf(__uint_as_float(sc32[i + 1]), p.sc, -mu));
           ps0 += a;
           ps1 += b;
-          pk[i >> 1] = pack_half2(a, b);
+          pk[i >> 1] = BF ? pack_bf16x2(a, b) : pack_half2(a, b);
         }
         tmem_st16(tS + c * 16, pk);
       };
-      to_p(s0, 0);
-      to_p(s1, 1);
-      to_p(s2, 2);
-      to_p(s3, 3);
+      if (p.bf16) {
+        to_p(std::true_type{}, s0, 0);
+        to_p(std::true_type{}, s1, 1);
+        to_p(std::true_type{}, s2, 2);
+        to_p(std::true_type{}, s3, 3);
+      } else {
+        to_p(std::false_type{}, s0, 0);
+        to_p(std::false_type{}, s1, 1);
+        to_p(std::false_type{}, s2, 2);
+        to_p(std::false_type{}, s3, 3);
+      }
       l += ps0 + ps1;
       if (quarter == 2) TC_E(2 + t, j, 4);
       if (tail && (kend < R.klen || R.page_table != nullptr) && t == 0) {
@@ -390,10 +402,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             uint4 v;
-            v.x = pack_half2(__uint_as_float(o[8 * i]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
-            v.y = pack_half2(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
-            v.z = pack_half2(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
-            v.w = pack_half2(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
+            v.x = pack2(__uint_as_float(o[8 * i]) * inv, __uint_as_float(o[8 * i + 1]) * inv, p.bf16);
+            v.y = pack2(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv, p.bf16);
+            v.z = pack2(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv, p.bf16);
+            v.w = pack2(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv, p.bf16);
             reinterpret_cast<uint4*>(dst)[i] = v;
           }
         } else {

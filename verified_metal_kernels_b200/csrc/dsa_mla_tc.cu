@@ -422,7 +422,11 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
         {
           uint32_t pk[16];
 #pragma unroll
-          for (int e = 0; e < 16; ++e) pk[e] = pack2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1]), p.bf16);
+          for (int e = 0; e < 16; ++e) pk[e] = pack_half2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1]));
+          if (p.bf16) {                                  // one uniform branch per block, not a choice per element
+#pragma unroll
+            for (int e = 0; e < 16; ++e) pk[e] = pack_bf16x2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1]));
+          }
           tmem_st16(tPw, pk);
           tmem_st_wait();
           tc_fence_before();

@@ -9,17 +9,20 @@ from ._common import need, stage_in
 
 
 def kernel(q, k, v, bits):
-    """q (B,kd,Hq,D), k/v (B,Hkv,L,D) fp16, bits (B,kd) int32 -- or (B,kd,W) int32 words for kd > 32 --
+    """q (B,kd,Hq,D), k/v (B,Hkv,L,D) fp16 (or all bf16), bits (B,kd) int32 -- or (B,kd,W) int32 words for kd > 32 --
     -> (B,kd,Hq,D) fp16.  The drafts are the last kd cache positions; bit j of bits[b,i] set means
     draft i attends draft j.  Inputs are not modified; host tensors are copied in and the result is
     returned on the host."""
     (q, k, v, bits), host = stage_in([q, k, v, bits])
-    need(q, "q", torch.float16, dims=4)
+    if not isinstance(q, torch.Tensor) or q.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError("q: expected a float16 or bfloat16 tensor")
+    dt = q.dtype                                   # fp16 (the reference's) or bf16, the same for q, k and v
+    need(q, "q", dt, dims=4)
     B, kd, Hq, D = q.shape
-    need(k, "k", torch.float16, dims=4)
+    need(k, "k", dt, dims=4)
     Hkv, Lk = k.shape[1], k.shape[2]
-    need(k, "k", torch.float16, shape=(B, Hkv, Lk, D))
-    need(v, "v", torch.float16, shape=(B, Hkv, Lk, D))
+    need(k, "k", dt, shape=(B, Hkv, Lk, D))
+    need(v, "v", dt, shape=(B, Hkv, Lk, D))
     if not isinstance(bits, torch.Tensor) or bits.dtype != torch.int32:
         raise TypeError("bits: expected an int32 tensor")
     if bits.dim() == 2:
@@ -38,7 +41,7 @@ def kernel(q, k, v, bits):
         if nbytes == 0:
             raise _lib.VmkError(-2, "spec: unsupported shape")
         ws = _lib.workspace(nbytes, dev, stream.cuda_stream)
-        rc = L.vmk_spec_verify(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(bits), words, _lib.ptr(out), B, kd, Hq,
+        rc = (L.vmk_spec_verify_bf16 if dt == torch.bfloat16 else L.vmk_spec_verify)(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(bits), words, _lib.ptr(out), B, kd, Hq,
                                Hkv, D, Lk, _lib.ptr(ws), ws.numel(), _lib.ptr(_lib.status_word(dev)),
                                stream.cuda_stream)
     _lib.check(rc, "vmk_spec_verify")
