@@ -231,8 +231,8 @@ def stage_times(inp, steps, torch):
 
 def side_line(config, torch, steps):
     """rows/s and HBM fraction of one named configuration on one GPU, L2 flushed between iterations.
-    Configurations: prefix_small, spec_chain, spec_tree, spec_tree_paged, dsa_small (the single-GPU ones) and
-    prefix_sweep."""
+    Configurations: prefix_small, spec_chain, spec_tree, spec_tree_paged, dsa_small (the single-GPU ones),
+    prefix_sweep and decode (the extension op)."""
     from verified_metal_kernels_b200 import load_kernel, ops
     g = torch.Generator(device="cuda")
     g.manual_seed(1)
@@ -272,6 +272,17 @@ def side_line(config, torch, steps):
             inp = dict(q=inp["q"], k_pages=r16(B * T + 7, 8, page, 128), v_pages=r16(B * T + 7, 8, page, 128),
                        page_table=perm.contiguous(), L=L, bits=inp["bits"])
             name += f", paged cache (page {page})"
+    elif config == "decode":
+        # plain single-token decode (extension op): 64 requests with caches of 16k..32k keys
+        from verified_metal_kernels_b200.ops import decode as op
+        opname = "decode"
+        shape = op.CONFIG_BENCH
+        B, L = shape["B"], shape["L"]
+        lens = torch.randint(L // 2, L + 1, (B,), generator=g, device="cuda", dtype=torch.int32)
+        inp = dict(q=r16(B, 32, 128), k=r16(B, 8, L, 128), v=r16(B, 8, L, 128), lens=lens)
+        nbytes = op.algorithmic_bytes(shape, lens.cpu().numpy())
+        rows, name = B, f"decode B={B} L~U[{L // 2},{L}]"
+        flops = 4.0 * 32 * 128 * float(lens.sum())
     else:
         opname = "dsa"
         op = ops.load_op(opname)
@@ -280,7 +291,11 @@ def side_line(config, torch, steps):
         nbytes = op.algorithmic_bytes(shape)
         rows, name = shape["B"], "dsa B=8 L=32768"
         flops = 2.0 * 64 * 128 * shape["L"] * shape["B"] + 2.0 * 128 * (576 + 512) * 2048 * shape["B"]
-    fn = load_kernel(opname)
+    if opname == "decode":
+        from verified_metal_kernels_b200.kernels import decode_b200
+        fn = decode_b200.kernel
+    else:
+        fn = load_kernel(opname)
     if config == "spec_tree_paged":
         from verified_metal_kernels_b200.kernels import spec_b200
         fn = spec_b200.kernel_paged
@@ -517,7 +532,7 @@ def main():
             del inp
             torch.cuda.empty_cache()
             line["ops"] = {c: side_line(c, torch, 10)
-                           for c in ("prefix_small", "spec_chain", "spec_tree", "spec_tree_paged", "dsa_small", "prefix_sweep")}
+                           for c in ("prefix_small", "spec_chain", "spec_tree", "spec_tree_paged", "dsa_small", "prefix_sweep", "decode")}
         if not a.no_cpu and world == 1:
             n = 2
             t = cpu_sample(n, L)

@@ -168,6 +168,21 @@ VMK_API size_t vmk_dsa_attend_workspace_bytes(int B);
 VMK_API int vmk_dsa_attend(const void* q, const void* kv, const int32_t* idx, const int32_t* cnt, void* out,
                    int B, int L, void* ws, size_t ws_bytes, int32_t* status, void* stream);
 
+/* ---- decode: plain single-token decode --------------------------------------------------------------
+ * The op the reference measures beside its three ("single-token decode", POST.md:42,47) and names as the natural
+ * fourth on the same main loop; it ships no kernel for it.  One query per request over that request's own cache:
+ *   q (B,Hq,D)  k,v (B,Hkv,L,D)  lens (B) int32, 1 <= lens[b] <= L  out (B,Hq,D); bf16 = 0 (fp16) or 1.
+ * Rows [lens[b], L) of request b may hold anything (NaN included).  The paged form takes one pool
+ * (pages,Hkv,page_size,D) and page_table (B,table_stride) as vmk_spec_verify_paged does, L then being the
+ * largest length (table_stride * page_size >= L). */
+VMK_API size_t vmk_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int L);
+VMK_API int vmk_decode(const void* q, const void* k, const void* v, const int32_t* lens, void* out, int B, int Hq,
+                       int Hkv, int D, int L, int bf16, void* ws, size_t ws_bytes, int32_t* status, void* stream);
+VMK_API int vmk_decode_paged(const void* q, const void* k_pages, const void* v_pages, const int32_t* page_table,
+                             int pages, int page_size, int table_stride, const int32_t* lens, void* out, int B,
+                             int Hq, int Hkv, int D, int L, int bf16, void* ws, size_t ws_bytes, int32_t* status,
+                             void* stream);
+
 /* ---- prefix and spec on bf16 tensors ---------------------------------------------------------------
  * vmk_prefix_decode (kernels/prefix_opus55_v8.py:282-355) and vmk_spec_verify (kernels/spec_opus55_v7.py:467-521)
  * with q, K, V and out in bf16; the reference's kernels are fp16 only (README.md:140).  Same shapes, workspaces,

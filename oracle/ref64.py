@@ -134,3 +134,21 @@ def dsa_ref64(q, kv, iq, ik, w, lens=None, sel=None, **_):
 
 
 REF64 = dict(prefix=prefix_ref64, spec=spec_ref64, dsa=dsa_ref64)
+
+
+def decode_ref64(q, k, v, lens, **_):
+    """Plain single-token decode (an op the reference measures but does not define, POST.md:42): request b's
+    query attends keys [0, lens[b]) of its own cache.  Same arithmetic as spec_ref64 (ops/spec.py:69-82) with one
+    unmasked row per request.  q (B,Hq,D), k/v (B,Hkv,L,D) -> (B,Hq,D) float64."""
+    q, k, v = _f64(q), _f64(k), _f64(v)
+    B, Hq, D = q.shape
+    Hkv = k.shape[1]
+    G = Hq // Hkv
+    out = np.empty((B, Hq, D), dtype=np.float64)
+    for b in range(B):
+        n = int(lens[b])
+        qb = q[b].reshape(Hkv, G, D)
+        for h in range(Hkv):
+            s = (qb[h] @ k[b, h, :n].T) / np.sqrt(D)
+            out[b, h * G:(h + 1) * G] = _softmax_rows_times(s, v[b, h, :n])
+    return out

@@ -409,11 +409,14 @@ static int prefix_impl(const void* q, const void* kp, const void* vp, const void
 static int spec_impl(const void* q, const void* k, const void* v, const uint32_t* bits, int bits_words, void* out,
                      int B, int kd, int Hq, int Hkv, int D, int L, int key_lo, int key_hi, float* pm, float* plv,
                      float* po, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream,
-                     PageArgs pg = PageArgs{nullptr, 0, 0, 0}, int bf16 = 0) {
+                     PageArgs pg = PageArgs{nullptr, 0, 0, 0}, int bf16 = 0, const int32_t* klens = nullptr) {
+  // klens (B): per-request cache lengths.  Only without a draft mask (bits == nullptr, kd == 1: plain decode),
+  // because the mask is anchored at the common length L.
+  if (klens != nullptr && (bits != nullptr || kd != 1)) return VMK_E_UNSUPPORTED;
   if (B <= 0 || kd <= 0 || Hq <= 0 || Hkv <= 0 || L <= 0 || bits_words <= 0) return VMK_E_BADARG;
   if (D != kHD || Hq % Hkv != 0 || Hq / Hkv > 16) return VMK_E_UNSUPPORTED;
   if (kd > L || kd > VMK_SPEC_MAX_DRAFTS || kd > 32 * bits_words || bits_words > kMaxMaskWords) return VMK_E_UNSUPPORTED;
-  if (!q || !k || !v || !bits || (!out && !(pm && plv && po)) || !ws) return VMK_E_BADARG;
+  if (!q || !k || !v || (!bits && !klens) || (!out && !(pm && plv && po)) || !ws) return VMK_E_BADARG;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || (reinterpret_cast<uintptr_t>(bits) & 3) ||
       (reinterpret_cast<uintptr_t>(ws) & 255))
     return VMK_E_BADARG;
@@ -436,7 +439,8 @@ static int spec_impl(const void* q, const void* k, const void* v, const uint32_t
   p.a.n_groups = B * Hkv; p.a.Hkv = Hkv; p.a.G = G; p.a.Hq = Hq;
   p.a.rows_outer = kd;
   p.a.klen = L; p.a.key_lo = key_lo; p.a.key_hi = key_hi;
-  p.a.mask_start = L - kd;
+  p.a.mask_start = bits ? L - kd : INT_MAX;
+  p.a.klens = klens;
   fill_role(&p.a, pl.a, static_cast<uint8_t*>(ws));
   p.a.direct = (out != nullptr && pl.a.nsplit == 1 && key_hi > key_lo) ? 1 : 0;
   rc = pl.a.tc ? launch_attn_tc(p, pl.a.n_cta, stream) : launch_attn<false>(p, pl.a.rt, pl.a.n_cta, stream);
@@ -576,6 +580,28 @@ extern "C" int vmk_lse_merge(const float* m, const float* l, const float* o, int
   lse_merge_kernel<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(m, l, o, parts, rows, D,
                                                                           static_cast<__half*>(out), 0);
   return check_launch(cudaGetLastError());
+}
+
+// ---- plain single-token decode: one query per request over its own cache of lens[b] keys ---------------------
+extern "C" size_t vmk_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int L) {
+  return vmk_spec_workspace_bytes(B, 1, Hq, Hkv, D, L);
+}
+
+extern "C" int vmk_decode(const void* q, const void* k, const void* v, const int32_t* lens, void* out, int B, int Hq,
+                          int Hkv, int D, int L, int bf16, void* ws, size_t ws_bytes, int32_t* status, void* stream) {
+  if (!out || !lens || (bf16 != 0 && bf16 != 1)) return VMK_E_BADARG;
+  return spec_impl(q, k, v, nullptr, 1, out, B, 1, Hq, Hkv, D, L, 0, L, nullptr, nullptr, nullptr, ws, ws_bytes, status,
+                   static_cast<cudaStream_t>(stream), PageArgs{nullptr, 0, 0, 0}, bf16, lens);
+}
+
+extern "C" int vmk_decode_paged(const void* q, const void* k_pages, const void* v_pages, const int32_t* page_table,
+                                int pages, int page_size, int table_stride, const int32_t* lens, void* out, int B,
+                                int Hq, int Hkv, int D, int L, int bf16, void* ws, size_t ws_bytes, int32_t* status,
+                                void* stream) {
+  if (!out || !lens || pages <= 0 || (bf16 != 0 && bf16 != 1)) return VMK_E_BADARG;
+  return spec_impl(q, k_pages, v_pages, nullptr, 1, out, B, 1, Hq, Hkv, D, L, 0, L, nullptr, nullptr, nullptr, ws,
+                   ws_bytes, status, static_cast<cudaStream_t>(stream),
+                   PageArgs{page_table, pages, page_size, table_stride}, bf16, lens);
 }
 
 // ---- the same ops on bf16 tensors (q, K, V and out) --------------------------------------------------------
