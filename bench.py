@@ -427,6 +427,8 @@ def main():
     ap.add_argument("--cache", type=int, default=DSA["L"], help="dsa cache length (default: the sweep's 131072)")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="N>1: weak = --batch requests per rank (default), strong = --batch requests in total")
+    ap.add_argument("--batch-invariant", action="store_true",
+                    help="time the library with vmk_set_batch_invariant(1) (fixed kernels and cut points)")
     ap.add_argument("--no-side", action="store_true", help="skip the prefix / spec side lines")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
@@ -448,6 +450,8 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     build.build()
+    if a.batch_invariant:
+        _lib.lib().vmk_set_batch_invariant(1)
     if a.side_only:
         print(json.dumps(side_line(a.side_only, torch, a.steps)))
         return 0

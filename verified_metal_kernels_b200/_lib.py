@@ -22,6 +22,7 @@ SIGNATURES = {
     "vmk_spec_verify": (_i, [_vp] * 4 + [_i] + [_vp] + [_i] * 6 + [_vp, _sz, _vp, _vp]),
     "vmk_spec_verify_bf16": (_i, [_vp] * 4 + [_i] + [_vp] + [_i] * 6 + [_vp, _sz, _vp, _vp]),
     "vmk_prefix_decode_paged": (_i, [_vp] * 3 + [_i] * 2 + [_vp, _i, _vp, _i, _vp, _vp] + [_i] * 6 + [_vp, _sz, _vp, _vp]),
+    "vmk_set_batch_invariant": (_i, [_i]),
     "vmk_decode_workspace_bytes": (_sz, [_i] * 5),
     "vmk_decode": (_i, [_vp] * 5 + [_i] * 6 + [_vp, _sz, _vp, _vp]),
     "vmk_decode_paged": (_i, [_vp] * 4 + [_i] * 3 + [_vp, _vp] + [_i] * 6 + [_vp, _sz, _vp, _vp]),

@@ -130,6 +130,8 @@ __global__ void __launch_bounds__(128) lse_merge_kernel(const float* __restrict_
 // ------------------------------------------------------------------------------------------------
 int launch_attn_tc(const AttnParams& p, int n_cta, cudaStream_t stream);   // attn_tc.cu
 
+int g_batch_invariant = 0;
+
 static int g_attn_tc = 1;   // 1: row tiles of 128 run on tcgen05 (attn_tc.cu); 0: always the warp-level kernel
 constexpr int kTcRowsMin = 65;     // stacked rows from which the tensor-memory kernel is used
 constexpr int kTcSplitCap = 32;
@@ -187,8 +189,22 @@ static void plan_role_tc(RolePlan* r, int groups, int rows, int keys) {
   r->n_cta = units * r->nsplit;
 }
 
+// Batch-invariant plan: the arithmetic of a row must not depend on what else is in the batch, so the kernel, the
+// warp layout and the cut points of the key range are fixed: warp-level kernel, 16-row tiles with the 64 keys of a
+// block over four warps, splits of 2048 keys (512 for the private suffixes).
+static void plan_role_invariant(RolePlan* r, int groups, int rows, int keys, bool fixed_small) {
+  r->tc = false;
+  r->rt = 1; r->ks = 4;
+  r->row_tiles = cdiv(rows, 16);
+  r->MP = rows;
+  r->split_len = fixed_small ? 512 : 2048;
+  r->nsplit = cdiv(keys > 0 ? keys : 1, r->split_len);
+  r->n_cta = groups * r->row_tiles * r->nsplit;
+}
+
 static void plan_role(RolePlan* r, int groups, int rows, int keys, int target, bool fixed_small) {
   r->tc = false;
+  if (g_batch_invariant) { plan_role_invariant(r, groups, rows, keys, fixed_small); return; }
   if (!fixed_small && g_attn_tc && rows >= kTcRowsMin) { plan_role_tc(r, groups, rows, keys); return; }
   if (fixed_small) { r->rt = 1; r->ks = 4; } else pick_layout(rows, &r->rt, &r->ks);
   const int mt = r->rt * 16;
@@ -197,6 +213,9 @@ static void plan_role(RolePlan* r, int groups, int rows, int keys, int target, b
   const int units = groups * r->row_tiles;
   const int blocks = cdiv(keys > 0 ? keys : 1, kBK);
   int want = cdiv(target > 0 ? target : 1, units > 0 ? units : 1);
+  // never more than 2048 keys per CTA: with many groups of unequal (ragged) lengths, short pieces balance the SMs,
+  // and a piece's partial record (130 floats per row) is small beside the 1 MB of K and V it stands for
+  if (!fixed_small && want < cdiv(blocks, 32)) want = cdiv(blocks, 32);
   if (want > blocks) want = blocks;
   if (want < 1) want = 1;
   r->split_len = cdiv(blocks, want) * kBK;
@@ -462,6 +481,13 @@ static int spec_impl(const void* q, const void* k, const void* v, const uint32_t
 // C ABI
 // ------------------------------------------------------------------------------------------------
 using namespace vmk;
+
+// 1: results of a row (a request's output) are bit-identical whatever else is in the batch, for every op of the
+// library, at the price of speed (fixed kernels, layouts and cut points instead of ones chosen for the batch).
+extern "C" VMK_API int vmk_set_batch_invariant(int on) {
+  g_batch_invariant = on ? 1 : 0;
+  return VMK_OK;
+}
 
 // Test hook: 1 = row tiles of 128 use the tcgen05 kernel (default), 0 = warp-level kernel everywhere.
 extern "C" VMK_API int vmk_attn_set_tc(int on) {

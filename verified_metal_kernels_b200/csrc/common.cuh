@@ -195,6 +195,9 @@ int make_tmap_3d(CUtensorMap* tm, const void* base, uint64_t width, uint64_t row
                  uint32_t box_w, uint32_t box_rows);
 
 int sm_count();
+
+// 1: every planner cuts the work the same way whatever the batch holds (vmk_set_batch_invariant); defined in attn.cu
+extern int g_batch_invariant;
 int check_launch(cudaError_t e);
 
 inline int cdiv(int a, int b) { return (a + b - 1) / b; }
