@@ -71,11 +71,12 @@ VMK_API int vmk_prefix_decode(const void* q, const void* kp, const void* vp, con
  *   pages suffix_table[n][0..]; suffix_stride * page_size >= S.  Both may be null when S == 0.
  * A page id outside [0, pages) reads as zeros; rows of a page beyond the end of its prefix or suffix may hold
  * anything (NaN included).  Workspace: vmk_prefix_workspace_bytes(N, Hq, Hkv, D, P, S).  The result equals
- * vmk_prefix_decode on the de-paged tensors bit for bit. */
+ * vmk_prefix_decode on the de-paged tensors bit for bit.  bf16 = 0: fp16 tensors, 1: bf16 tensors. */
 VMK_API int vmk_prefix_decode_paged(const void* q, const void* k_pages, const void* v_pages, int pages, int page_size,
                                     const int32_t* prefix_table, int prefix_pages, const int32_t* suffix_table,
                                     int suffix_stride, const int32_t* slens, void* out, int N, int Hq, int Hkv,
-                                    int D, int P, int S, void* ws, size_t ws_bytes, int32_t* status, void* stream);
+                                    int D, int P, int S, int bf16, void* ws, size_t ws_bytes, int32_t* status,
+                                    void* stream);
 
 /* ---- spec: speculative chain / tree verification ----------------------------------------------
  * Replaces the reference's permute / partial / combine launches (kernels/spec_opus55_v7.py:467-521).
@@ -96,10 +97,10 @@ VMK_API int vmk_spec_verify(const void* q, const void* k, const void* v, const u
  *   page_table[b][i]; table_stride * page_size >= L.  Entries beyond ceil(L / page_size) are not read; a page id
  *   outside [0, pages) reads as zeros.  Rows of the last page beyond L may hold anything (NaN included).
  * Everything else as vmk_spec_verify, same workspace size; the result equals vmk_spec_verify on the
- * de-paged cache bit for bit. */
+ * de-paged cache bit for bit.  bf16 = 0: fp16 tensors, 1: bf16 tensors. */
 VMK_API int vmk_spec_verify_paged(const void* q, const void* k_pages, const void* v_pages, const int32_t* page_table,
                                   int pages, int page_size, int table_stride, const uint32_t* bits, int bits_words,
-                                  void* out, int B, int kd, int Hq, int Hkv, int D, int L, void* ws,
+                                  void* out, int B, int kd, int Hq, int Hkv, int D, int L, int bf16, void* ws,
                                   size_t ws_bytes, int32_t* status, void* stream);
 
 /* vmk_spec_verify without any caller-provided scratch.  This entry point has no counterpart in the
@@ -215,6 +216,19 @@ VMK_API int vmk_dsa_indexer_hist_bf16(const void* iq, const void* ik, const floa
                                       float* scores, uint32_t* hist, int B, int L, int32_t* status, void* stream);
 VMK_API int vmk_dsa_attend_bf16(const void* q, const void* kv, const int32_t* idx, const int32_t* cnt, void* out,
                                 int B, int L, void* ws, size_t ws_bytes, int32_t* status, void* stream);
+
+/* vmk_dsa_decode over a PAGED cache (the layout of serving stacks; the reference names the paged variant as
+ * left out, README.md:141-142; its contiguous launch path is kernels/dsa_opus55_v7.py:946-977).
+ *   kv_pages (pages, page_size, 576), ik_pages (pages, page_size, 128): one pool each, paged alike; page_size a
+ *   multiple of 128.  page_table (B, table_stride) int32: positions [i*page_size, (i+1)*page_size) of request b
+ *   are page page_table[b][i] of both pools.  lens (B) is required; L is the largest length the call may see
+ *   (2048 < L <= table_stride * page_size) and sizes the workspace: vmk_dsa_workspace_bytes(B, L).
+ * Positions at or beyond lens[b] may hold anything.  idx_out holds logical positions.  bf16 = 0 / 1.  The result
+ * equals vmk_dsa_decode on the de-paged tensors bit for bit. */
+VMK_API int vmk_dsa_decode_paged(const void* q, const void* kv_pages, const void* iq, const void* ik_pages,
+                                 const float* w, const int32_t* page_table, int pages, int page_size,
+                                 int table_stride, const int32_t* lens, void* out, int32_t* idx_out, int32_t* cnt_out,
+                                 int B, int L, int bf16, void* ws, size_t ws_bytes, int32_t* status, void* stream);
 
 /* ---- merge of split partials -------------------------------------------------------------------
  * Log-sum-exp merge used after a KV split across GPUs (the reference merges its in-GPU splits the

@@ -102,3 +102,16 @@ def test_spec_bf16_against_the_oracle(shape, dist):
     truth = ref64.REF64["spec"](**{k: inp.get(k) for k in ops.KEYS["spec"]})
     rep = judge.judge_l2(out.float().cpu().numpy(), truth, half=True, dist=dist)
     assert rep["ok"] and rep["err_max"] <= 6e-3, rep
+
+
+def test_paged_bf16_equals_contiguous_bf16_bit_for_bit():
+    from verified_metal_kernels_b200.kernels import spec_b200
+    inp = ops.as_bf16("spec", spec.make_inputs(dict(B=2, L=3000, k=32), seed=3))
+    d = ops.to_torch(ops.cand_inputs("spec", inp), "cuda", bf16="spec")
+    ref = spec_b200.kernel(**d)
+    kp, vp, table = spec.to_pages(inp["k"], inp["v"], 128, seed=5)
+    out = spec_b200.kernel_paged(d["q"], torch.from_numpy(kp).cuda().to(torch.bfloat16),
+                                 torch.from_numpy(vp).cuda().to(torch.bfloat16), torch.from_numpy(table).cuda(), 3000,
+                                 d["bits"])
+    torch.cuda.synchronize()
+    assert out.dtype == torch.bfloat16 and torch.equal(out, ref)

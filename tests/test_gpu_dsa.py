@@ -241,3 +241,32 @@ def test_host_resident_cache_gives_the_same_bits_as_the_device_call(dist):
     host["kv"] = d["kv"].cpu()
     assert torch.equal(dsa_b200.kernel(**host), out_d.cpu())
     _verify.assert_clean_status()
+
+
+@pytest.mark.parametrize("shape,dist,page_size,bf16", [
+    (dict(B=3, L=9000), "ragged", 128, False),
+    (dict(B=2, L=6000), "randn", 512, False),
+    (dict(B=40, L=3000), "ragged", 128, False),       # units cut by range boundaries in stage 3
+    (dict(B=2, L=7000), "ragged", 256, True),
+], ids=lambda x: str(x))
+def test_paged_cache_equals_the_contiguous_call_bit_for_bit(shape, dist, page_size, bf16):
+    """vmk_dsa_decode_paged on shuffled page pools (index keys and latent rows paged alike; unused pages and rows
+    NaN) against vmk_dsa_decode on the contiguous tensors: same selection, same output bits."""
+    inp = op.make_inputs(shape, seed=71, dist=dist)
+    B, L = shape["B"], shape["L"]
+    if inp.get("lens") is None:
+        inp["lens"] = np.full(B, L, dtype=np.int32)
+    if bf16:
+        inp = ops.as_bf16("dsa", inp)
+    d = ops.to_torch(ops.cand_inputs("dsa", inp), "cuda", bf16="dsa" if bf16 else None)
+    ref, ridx, rcnt = dsa_b200.kernel(**d, return_selection=True)
+    kvp, ikp, table = op.to_pages(inp["kv"], inp["ik"], inp["lens"], page_size, seed=9)
+    tt = lambda a: (torch.from_numpy(a).cuda().to(torch.bfloat16) if bf16 else torch.from_numpy(a).cuda())
+    out, idx, cnt = dsa_b200.kernel_paged(d["q"], tt(kvp), d["iq"], tt(ikp), d["w"], torch.from_numpy(table).cuda(),
+                                          d["lens"], return_selection=True)
+    torch.cuda.synchronize()
+    _verify.assert_clean_status()
+    assert torch.equal(cnt, rcnt)
+    for b in range(B):
+        assert torch.equal(idx[b, :cnt[b]], ridx[b, :rcnt[b]]), b
+    assert torch.equal(out, ref)

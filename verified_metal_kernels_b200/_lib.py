@@ -21,15 +21,16 @@ SIGNATURES = {
     "vmk_spec_workspace_bytes": (_sz, [_i] * 6),
     "vmk_spec_verify": (_i, [_vp] * 4 + [_i] + [_vp] + [_i] * 6 + [_vp, _sz, _vp, _vp]),
     "vmk_spec_verify_bf16": (_i, [_vp] * 4 + [_i] + [_vp] + [_i] * 6 + [_vp, _sz, _vp, _vp]),
-    "vmk_prefix_decode_paged": (_i, [_vp] * 3 + [_i] * 2 + [_vp, _i, _vp, _i, _vp, _vp] + [_i] * 6 + [_vp, _sz, _vp, _vp]),
+    "vmk_prefix_decode_paged": (_i, [_vp] * 3 + [_i] * 2 + [_vp, _i, _vp, _i, _vp, _vp] + [_i] * 7 + [_vp, _sz, _vp, _vp]),
     "vmk_set_batch_invariant": (_i, [_i]),
     "vmk_decode_workspace_bytes": (_sz, [_i] * 5),
     "vmk_decode": (_i, [_vp] * 5 + [_i] * 6 + [_vp, _sz, _vp, _vp]),
     "vmk_decode_paged": (_i, [_vp] * 4 + [_i] * 3 + [_vp, _vp] + [_i] * 6 + [_vp, _sz, _vp, _vp]),
-    "vmk_spec_verify_paged": (_i, [_vp] * 4 + [_i] * 3 + [_vp, _i, _vp] + [_i] * 6 + [_vp, _sz, _vp, _vp]),
+    "vmk_spec_verify_paged": (_i, [_vp] * 4 + [_i] * 3 + [_vp, _i, _vp] + [_i] * 7 + [_vp, _sz, _vp, _vp]),
     "vmk_spec_verify_noalloc": (_i, [_vp] * 4 + [_i] + [_vp] + [_i] * 6 + [_vp, _vp]),
     "vmk_dsa_workspace_bytes": (_sz, [_i] * 2),
     "vmk_dsa_decode": (_i, [_vp] * 9 + [_i] * 2 + [_vp, _sz, _vp, _vp]),
+    "vmk_dsa_decode_paged": (_i, [_vp] * 6 + [_i] * 3 + [_vp] * 4 + [_i] * 3 + [_vp, _sz, _vp, _vp]),
     "vmk_dsa_decode_bf16": (_i, [_vp] * 9 + [_i] * 2 + [_vp, _sz, _vp, _vp]),
     "vmk_dsa_indexer": (_i, [_vp] * 5 + [_i] * 2 + [_vp, _vp]),
     "vmk_dsa_select": (_i, [_vp] * 4 + [_i] * 2 + [_vp]),

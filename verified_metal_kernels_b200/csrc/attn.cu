@@ -511,12 +511,13 @@ extern "C" int vmk_prefix_decode(const void* q, const void* kp, const void* vp, 
 extern "C" int vmk_prefix_decode_paged(const void* q, const void* k_pages, const void* v_pages, int pages, int page_size,
                                        const int32_t* prefix_table, int prefix_pages, const int32_t* suffix_table,
                                        int suffix_stride, const int32_t* slens, void* out, int N, int Hq, int Hkv, int D,
-                                       int P, int S, void* ws, size_t ws_bytes, int32_t* status, void* stream) {
-  if (!out || pages <= 0 || !prefix_table || (S > 0 && (!suffix_table || !slens))) return VMK_E_BADARG;
+                                       int P, int S, int bf16, void* ws, size_t ws_bytes, int32_t* status, void* stream) {
+  if (!out || pages <= 0 || !prefix_table || (S > 0 && (!suffix_table || !slens)) || (bf16 != 0 && bf16 != 1))
+    return VMK_E_BADARG;
   return prefix_impl(q, k_pages, v_pages, k_pages, v_pages, slens, out, N, Hq, Hkv, D, P, S, 0, P, 1, nullptr, nullptr,
                      nullptr, ws, ws_bytes, status, static_cast<cudaStream_t>(stream),
                      PageArgs{prefix_table, pages, page_size, prefix_pages},
-                     PageArgs{suffix_table, pages, page_size, suffix_stride});
+                     PageArgs{suffix_table, pages, page_size, suffix_stride}, bf16);
 }
 
 extern "C" int vmk_prefix_partial(const void* q, const void* kp, const void* vp, const void* ks, const void* vs,
@@ -543,11 +544,12 @@ extern "C" int vmk_spec_verify(const void* q, const void* k, const void* v, cons
 
 extern "C" int vmk_spec_verify_paged(const void* q, const void* k_pages, const void* v_pages, const int32_t* page_table,
                                      int pages, int page_size, int table_stride, const uint32_t* bits, int bits_words,
-                                     void* out, int B, int kd, int Hq, int Hkv, int D, int L, void* ws, size_t ws_bytes,
-                                     int32_t* status, void* stream) {
-  if (!out || pages <= 0) return VMK_E_BADARG;
+                                     void* out, int B, int kd, int Hq, int Hkv, int D, int L, int bf16, void* ws,
+                                     size_t ws_bytes, int32_t* status, void* stream) {
+  if (!out || pages <= 0 || (bf16 != 0 && bf16 != 1)) return VMK_E_BADARG;
   return spec_impl(q, k_pages, v_pages, bits, bits_words, out, B, kd, Hq, Hkv, D, L, 0, L, nullptr, nullptr, nullptr, ws,
-                   ws_bytes, status, static_cast<cudaStream_t>(stream), PageArgs{page_table, pages, page_size, table_stride});
+                   ws_bytes, status, static_cast<cudaStream_t>(stream), PageArgs{page_table, pages, page_size, table_stride},
+                   bf16);
 }
 
 extern "C" int vmk_spec_partial(const void* q, const void* k, const void* v, const uint32_t* bits, int bits_words,

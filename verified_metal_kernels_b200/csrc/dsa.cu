@@ -12,7 +12,8 @@ constexpr int kDK = 576;       // latent row: 512 latent + 64 rope
 constexpr int kDV = 512;       // value = first 512 columns of the row
 
 int indexer_tc_launch(const CUtensorMap& tmIK, const CUtensorMap& tmIQ, const float* w, const int32_t* lens,
-                      float* scores, uint32_t* hist, int B, int L, int32_t* status, cudaStream_t stream, int bf16);
+                      float* scores, uint32_t* hist, int B, int L, int32_t* status, cudaStream_t stream, int bf16,
+                      const int32_t* page_table, int page_size, int table_stride, int pages);
 struct MlaTcParams {
   const __half* q;
   const __half* kv;
@@ -25,6 +26,8 @@ struct MlaTcParams {
   float sc;
   int32_t* status;
   int bf16;
+  const int32_t* page_table;
+  int page_size, table_stride, pages;
 };
 int mla_tc_launch(const MlaTcParams& p, float* workspace, cudaStream_t stream);   // dsa_mla_tc.cu
 size_t mla_tc_workspace(int B);
@@ -525,20 +528,35 @@ int indexer_chunks(int B, int tiles) {
   return best;
 }
 
-// bf16 = 1: the 16-bit tensors of the call are bf16 (only the tcgen05 implementations take them).
+// Paged caches: the index keys (pages, page_size, 128) and the latent rows (pages, page_size, 576) share one page
+// table (B, table_stride); pages == 0 means contiguous (B, L, .) tensors.
+struct DsaPages {
+  const int32_t* table;
+  int pages, page_size, table_stride;
+};
+
+// bf16 = 1: the 16-bit tensors of the call are bf16 (only the tcgen05 implementations take them, and only they
+// take a paged cache).
 static int indexer_impl(const void* iq, const void* ik, const float* w, const int32_t* lens, float* scores,
-                        uint32_t* hist, int B, int L, int32_t* status, cudaStream_t stream, int variant, int bf16 = 0) {
+                        uint32_t* hist, int B, int L, int32_t* status, cudaStream_t stream, int variant, int bf16 = 0,
+                        DsaPages pg = DsaPages{nullptr, 0, 0, 0}) {
   if (!iq || !ik || !w || !scores || B <= 0 || L <= 0) return VMK_E_BADARG;
-  if (bf16 && variant != 1) return VMK_E_UNSUPPORTED;
+  if ((bf16 || pg.pages > 0) && variant != 1) return VMK_E_UNSUPPORTED;
+  if (pg.pages > 0 && (!pg.table || pg.page_size < kIdxTile || pg.page_size % kIdxTile != 0 || pg.table_stride <= 0 ||
+                       (long long)pg.table_stride * pg.page_size < L))
+    return VMK_E_BADARG;
   if (!aligned16(iq) || !aligned16(ik) || B > 65535) return VMK_E_BADARG;
   if (L <= kTopK) return VMK_OK;                        // nothing to rank
   IndexerParams p;
   memset(&p, 0, sizeof(p));
-  int rc = make_tmap_3d(&p.tmIK, ik, kDI, L, B, 64, kIdxTile);
+  int rc = pg.pages > 0 ? make_tmap_3d(&p.tmIK, ik, kDI, pg.page_size, pg.pages, 64, kIdxTile)
+                        : make_tmap_3d(&p.tmIK, ik, kDI, L, B, 64, kIdxTile);
   if (rc) return rc;
   rc = make_tmap_3d(&p.tmIQ, iq, kDI, kHI, B, 64, kHI);
   if (rc) return rc;
-  if (variant == 1) return indexer_tc_launch(p.tmIK, p.tmIQ, w, lens, scores, hist, B, L, status, stream, bf16);
+  if (variant == 1)
+    return indexer_tc_launch(p.tmIK, p.tmIQ, w, lens, scores, hist, B, L, status, stream, bf16, pg.table, pg.page_size,
+                             pg.table_stride, pg.pages);
   p.w = w; p.lens = lens; p.scores = scores; p.B = B; p.L = L; p.status = status;
   static int configured_dev = -1;
   int dev = 0;
@@ -554,9 +572,10 @@ static int indexer_impl(const void* iq, const void* ik, const float* w, const in
 }
 
 static int attend_impl(const void* q, const void* kv, const int32_t* idx, const int32_t* cnt, void* out, int B,
-                       int L, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream, int bf16 = 0) {
+                       int L, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream, int bf16 = 0,
+                       DsaPages pg = DsaPages{nullptr, 0, 0, 0}) {
   if (!q || !kv || !idx || !cnt || !out || B <= 0 || L <= 0) return VMK_E_BADARG;
-  if (bf16 && g_attend_variant != 1) return VMK_E_UNSUPPORTED;
+  if ((bf16 || pg.pages > 0) && g_attend_variant != 1) return VMK_E_UNSUPPORTED;
   if (!aligned16(q) || !aligned16(kv) || !aligned16(out) || B > 65535) return VMK_E_BADARG;
   const int ns = mla_splits(B);
   if (!ws || ws_bytes < attend_ws(B) || (reinterpret_cast<uintptr_t>(ws) & 255)) return VMK_E_WORKSPACE;
@@ -578,6 +597,8 @@ static int attend_impl(const void* q, const void* kv, const int32_t* idx, const 
     MlaTcParams t;
     t.q = p.q; t.kv = p.kv; t.idx = p.idx; t.cnt = p.cnt; t.out = p.out; t.part_o = nullptr; t.part_ml = nullptr;
     t.B = B; t.L = L; t.ncta = 0; t.sc = p.sc; t.status = status; t.bf16 = bf16;
+    t.page_table = pg.pages > 0 ? pg.table : nullptr;
+    t.page_size = pg.page_size; t.table_stride = pg.table_stride; t.pages = pg.pages;
     return mla_tc_launch(t, static_cast<float*>(ws), stream);
   }
   static int configured_dev = -1;
@@ -655,7 +676,8 @@ extern "C" size_t vmk_dsa_workspace_bytes(int B, int L) { return (B > 0 && L > 0
 
 static int decode_impl(const void* q, const void* kv, const void* iq, const void* ik, const float* w,
                        const int32_t* lens, void* out, int32_t* idx_out, int32_t* cnt_out, int B, int L, void* ws,
-                       size_t ws_bytes, int32_t* status, void* stream, int bf16) {
+                       size_t ws_bytes, int32_t* status, void* stream, int bf16,
+                       DsaPages pg = DsaPages{nullptr, 0, 0, 0}) {
   if (B <= 0 || L <= 0 || !ws || (reinterpret_cast<uintptr_t>(ws) & 255)) return VMK_E_BADARG;
   const DsaPlan pl = plan_dsa(B, L);
   if (ws_bytes < pl.ws_bytes) return VMK_E_WORKSPACE;
@@ -671,12 +693,12 @@ static int decode_impl(const void* q, const void* kv, const void* iq, const void
     hist = reinterpret_cast<uint32_t*>(base + pl.off_hist);
     if (cudaMemsetAsync(hist, 0, (size_t)B * kSelBins * 4, st) != cudaSuccess) return VMK_E_LAUNCH;
   }
-  int rc = indexer_impl(iq, ik, w, lens, scores, hist, B, L, status, st, g_indexer_variant, bf16);
+  int rc = indexer_impl(iq, ik, w, lens, scores, hist, B, L, status, st, g_indexer_variant, bf16, pg);
   if (rc) return rc;
   if (!idx || !cnt) return VMK_E_BADARG;
   rc = select_launch(scores, hist, lens, idx, cnt, B, L, st);
   if (rc) return rc;
-  return attend_impl(q, kv, idx, cnt, out, B, L, base + pl.off_attend, attend_ws(B), status, st, bf16);
+  return attend_impl(q, kv, idx, cnt, out, B, L, base + pl.off_attend, attend_ws(B), status, st, bf16, pg);
 }
 
 extern "C" int vmk_dsa_decode(const void* q, const void* kv, const void* iq, const void* ik, const float* w,
@@ -703,4 +725,16 @@ extern "C" int vmk_dsa_indexer_hist_bf16(const void* iq, const void* ik, const f
 extern "C" int vmk_dsa_attend_bf16(const void* q, const void* kv, const int32_t* idx, const int32_t* cnt, void* out,
                                    int B, int L, void* ws, size_t ws_bytes, int32_t* status, void* stream) {
   return attend_impl(q, kv, idx, cnt, out, B, L, ws, ws_bytes, status, static_cast<cudaStream_t>(stream), 1);
+}
+
+// ---- the op over a paged cache (index keys and latent rows paged alike) ----------------------------------------
+extern "C" int vmk_dsa_decode_paged(const void* q, const void* kv_pages, const void* iq, const void* ik_pages,
+                                    const float* w, const int32_t* page_table, int pages, int page_size,
+                                    int table_stride, const int32_t* lens, void* out, int32_t* idx_out,
+                                    int32_t* cnt_out, int B, int L, int bf16, void* ws, size_t ws_bytes, int32_t* status,
+                                    void* stream) {
+  if (pages <= 0 || !page_table || !lens || (bf16 != 0 && bf16 != 1)) return VMK_E_BADARG;
+  if (L <= kTopK) return VMK_E_UNSUPPORTED;          // a cache this short is not worth paging: use vmk_dsa_decode
+  return decode_impl(q, kv_pages, iq, ik_pages, w, lens, out, idx_out, cnt_out, B, L, ws, ws_bytes, status, stream, bf16,
+                     DsaPages{page_table, pages, page_size, table_stride});
 }

@@ -37,6 +37,9 @@ struct TcParams {
   uint32_t* hist;        // (B, 2048) counts of the top 11 key bits, accumulated with atomics; nullable
   int B, L;
   int bf16;              // the index queries and keys are bf16 instead of fp16
+  const int32_t* page_table;   // paged keys: positions [i * page_size, (i+1) * page_size) of request b are page
+                               // page_table[b * table_stride + i] of tmIK = (pages, page_size, 128); null = (B, L, 128)
+  int page_size, table_stride, pages;
   int32_t* status;
 };
 
@@ -95,16 +98,31 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
       mbar_expect_tx(iq_full, kIqBytes);
       tma_load_3d(sIQ, &p.tmIQ, 0, 0, b, iq_full);
       tma_load_3d(sIQ + kIqBytes / 2, &p.tmIQ, 64, 0, b, iq_full);
+      // Paged keys: a 128-position tile lies inside one page (page_size is a multiple of 128).  The table entry of
+      // the NEXT tile is requested one iteration ahead, so that its latency hides behind the wait for a free slot.
+      auto page_of = [&](int pos) -> int {
+        const int pi = pos / p.page_size;
+        return pi < p.table_stride ? p.page_table[(size_t)b * p.table_stride + pi] : -1;
+      };
+      int pg_next = (p.page_table != nullptr && nt > 0) ? page_of(t0 * kTile) : 0;
       for (int j = 0; j < nt; ++j) {
         const int s = j % kStages;
+        const int pg = pg_next;
+        if (p.page_table != nullptr && j + 1 < nt) pg_next = page_of((t0 + j + 1) * kTile);
         if (j >= kStages && !mbar_wait(&empty[s], (uint32_t)(((j / kStages) - 1) & 1))) {
           timed_out = true;
           break;
         }
         uint8_t* st = smem + s * kTileBytes;
         mbar_expect_tx(&full[s], kTileBytes);
-        tma_load_3d(st, &p.tmIK, 0, (t0 + j) * kTile, b, &full[s]);
-        tma_load_3d(st + kTileBytes / 2, &p.tmIK, 64, (t0 + j) * kTile, b, &full[s]);
+        int y = (t0 + j) * kTile, z = b;
+        if (p.page_table != nullptr) {
+          // a page id outside the pool makes the TMA coordinate out of range, which reads zeros
+          z = (pg >= 0 && pg < p.pages) ? pg : p.pages;
+          y %= p.page_size;
+        }
+        tma_load_3d(st, &p.tmIK, 0, y, z, &full[s]);
+        tma_load_3d(st + kTileBytes / 2, &p.tmIK, 64, y, z, &full[s]);
       }
     }
   } else if (warp == 1) {
@@ -192,13 +210,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
 int indexer_chunks(int B, int tiles);
 
 int indexer_tc_launch(const CUtensorMap& tmIK, const CUtensorMap& tmIQ, const float* w, const int32_t* lens,
-                      float* scores, uint32_t* hist, int B, int L, int32_t* status, cudaStream_t stream, int bf16) {
+                      float* scores, uint32_t* hist, int B, int L, int32_t* status, cudaStream_t stream, int bf16, const int32_t* page_table, int page_size,
+                      int table_stride, int pages) {
   TcParams p;
   memset(&p, 0, sizeof(p));
   p.tmIK = tmIK;
   p.tmIQ = tmIQ;
   p.w = w; p.lens = lens; p.scores = scores; p.hist = hist; p.B = B; p.L = L; p.status = status;
   p.bf16 = bf16;
+  p.page_table = page_table; p.page_size = page_size; p.table_stride = table_stride; p.pages = pages;
   static int configured_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);

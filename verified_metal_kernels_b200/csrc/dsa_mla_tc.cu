@@ -61,6 +61,9 @@ struct MlaTcParams {
   float sc;
   int32_t* status;
   int bf16;            // q, kv and out are bf16 instead of fp16
+  const int32_t* page_table;   // paged cache: row l of request b is row l % page_size of page
+                               // page_table[b * table_stride + l / page_size] of kv = (pages, page_size, 576); null = (B, L, 576)
+  int page_size, table_stride, pages;
 };
 
 // First block slot of CTA c when `total` slots are cut into `ncta` ranges.
@@ -163,7 +166,7 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
     int base = 0;                                       // blocks of the units before this one
     for (int u = u_first; u <= u_last && !timed_out; ++u) {
       const UnitWork w = unit_work(p, u, slot0, slot1);
-      const __half* kvb = p.kv + (size_t)w.b * p.L * kDK;
+      const __half* kvb = p.page_table != nullptr ? p.kv : p.kv + (size_t)w.b * p.L * kDK;
       const int32_t* idxb = p.idx + (size_t)w.b * kMlaTopK;
       const int own = w.half * 4, other = 4 - own;
       if (warp == 9 && u + 1 <= u_last) {
@@ -201,8 +204,15 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
           for (int r4 = 0; r4 < 16; ++r4) {
             const int row = r4 * 4 + rsub;
             const int ridx = (r4 < 8) ? __shfl_sync(0xffffffffu, ia, row & 31) : __shfl_sync(0xffffffffu, ib, row & 31);
-            const bool valid = ridx >= 0;
-            const uint8_t* src = reinterpret_cast<const uint8_t*>(kvb + (size_t)(valid ? ridx : 0) * kDK) + c8 * 16;
+            bool valid = ridx >= 0;
+            size_t grow = valid ? (size_t)ridx : 0;                 // row of the tensor kvb points at
+            if (p.page_table != nullptr && valid) {
+              const int pi = ridx / p.page_size;
+              const int pg = p.page_table[(size_t)w.b * p.table_stride + pi];
+              valid = pg >= 0 && pg < p.pages;                    // a page outside the pool reads as zeros
+              grow = valid ? (size_t)pg * p.page_size + (ridx - pi * p.page_size) : 0;
+            }
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(kvb + grow * kDK) + c8 * 16;
             uint8_t* dst = st + row * 128 + ((c8 ^ (row & 7)) << 4);
 #pragma unroll
             for (int blk = 0; blk < 4; ++blk)

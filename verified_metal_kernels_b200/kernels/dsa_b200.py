@@ -74,6 +74,45 @@ def kernel(q, kv, iq, ik, w, lens=None, return_selection=False):
     return (out, idx, cnt) if return_selection else out
 
 
+def kernel_paged(q, kv_pages, iq, ik_pages, w, page_table, lens, return_selection=False):
+    """`dsa` over a paged cache: kv_pages (pages,page_size,576) and ik_pages (pages,page_size,128) are pools paged
+    alike, page_table (B,T) int32 maps positions [i * page_size, (i + 1) * page_size) of request b to page
+    page_table[b, i]; lens (B,) int32 are the cache lengths (required); page_size a multiple of 128 and
+    T * page_size > 2048.  fp16 or bf16.  The result (and the selection, in logical positions) equals kernel() on
+    the de-paged tensors bit for bit."""
+    dt = _half(q)
+    need(q, "q", dt, dims=3)
+    B = q.shape[0]
+    need(q, "q", dt, shape=(B, H, DK))
+    need(kv_pages, "kv_pages", dt, dims=3)
+    pages, page_size = kv_pages.shape[0], kv_pages.shape[1]
+    need(kv_pages, "kv_pages", dt, shape=(pages, page_size, DK))
+    need(ik_pages, "ik_pages", dt, shape=(pages, page_size, DI))
+    need(iq, "iq", dt, shape=(B, HI, DI))
+    need(w, "w", torch.float32, shape=(B, HI))
+    need(page_table, "page_table", torch.int32, dims=2)
+    T = page_table.shape[1]
+    need(page_table, "page_table", torch.int32, shape=(B, T))
+    need(lens, "lens", torch.int32, shape=(B,))
+    L = T * page_size
+    if page_size % 128 != 0 or L <= TOPK:
+        raise ValueError("page_size must be a multiple of 128 and the table must cover more than 2048 positions")
+    lib = _lib.lib()
+    dev = q.device
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream()
+        out = torch.empty(B, H, DC, dtype=dt, device=dev)
+        idx = torch.empty(B, TOPK, dtype=torch.int32, device=dev) if return_selection else None
+        cnt = torch.empty(B, dtype=torch.int32, device=dev) if return_selection else None
+        ws = _lib.workspace(lib.vmk_dsa_workspace_bytes(B, L), dev, stream.cuda_stream)
+        rc = lib.vmk_dsa_decode_paged(_lib.ptr(q), _lib.ptr(kv_pages), _lib.ptr(iq), _lib.ptr(ik_pages), _lib.ptr(w),
+                                      _lib.ptr(page_table), pages, page_size, T, _lib.ptr(lens), _lib.ptr(out),
+                                      _lib.ptr(idx), _lib.ptr(cnt), B, L, 1 if dt == torch.bfloat16 else 0,
+                                      _lib.ptr(ws), ws.numel(), _lib.ptr(_lib.status_word(dev)), stream.cuda_stream)
+    _lib.check(rc, "vmk_dsa_decode_paged")
+    return (out, idx, cnt) if return_selection else out
+
+
 def _kernel_host_cache(q, kv, iq, ik, w, lens, return_selection):
     """The op with the latent cache left in page-locked host memory (see kernel)."""
     (q, iq, ik, w, lens), _ = stage_in([q, iq, ik, w, lens])

@@ -52,12 +52,15 @@ def kernel_paged(q, k_pages, v_pages, prefix_table, P, suffix_table=None, slens=
     prefix is P keys in pages prefix_table (T_p,) int32; request n's private suffix is slens[n] keys in pages
     suffix_table[n] ((N, T_s) int32).  page_size a multiple of 64.  Returns (N,Hq,D) fp16, equal to kernel() on
     the de-paged tensors bit for bit."""
-    need(q, "q", torch.float16, dims=3)
+    if not isinstance(q, torch.Tensor) or q.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError("q: expected a float16 or bfloat16 tensor")
+    dt = q.dtype
+    need(q, "q", dt, dims=3)
     N, Hq, D = q.shape
-    need(k_pages, "k_pages", torch.float16, dims=4)
+    need(k_pages, "k_pages", dt, dims=4)
     pages, Hkv, page_size = k_pages.shape[0], k_pages.shape[1], k_pages.shape[2]
-    need(k_pages, "k_pages", torch.float16, shape=(pages, Hkv, page_size, D))
-    need(v_pages, "v_pages", torch.float16, shape=(pages, Hkv, page_size, D))
+    need(k_pages, "k_pages", dt, shape=(pages, Hkv, page_size, D))
+    need(v_pages, "v_pages", dt, shape=(pages, Hkv, page_size, D))
     need(prefix_table, "prefix_table", torch.int32, dims=1)
     Tp = prefix_table.shape[0]
     if page_size % 64 != 0 or P <= 0 or Tp * page_size < P:
@@ -80,7 +83,8 @@ def kernel_paged(q, k_pages, v_pages, prefix_table, P, suffix_table=None, slens=
         ws = _lib.workspace(nbytes, dev, stream.cuda_stream)
         rc = lib.vmk_prefix_decode_paged(_lib.ptr(q), _lib.ptr(k_pages), _lib.ptr(v_pages), pages, page_size,
                                          _lib.ptr(prefix_table), Tp, _lib.ptr(suffix_table), Ts, _lib.ptr(slens),
-                                         _lib.ptr(out), N, Hq, Hkv, D, P, S, _lib.ptr(ws), ws.numel(),
+                                         _lib.ptr(out), N, Hq, Hkv, D, P, S, 1 if dt == torch.bfloat16 else 0,
+                                         _lib.ptr(ws), ws.numel(),
                                          _lib.ptr(_lib.status_word(dev)), stream.cuda_stream)
     _lib.check(rc, "vmk_prefix_decode_paged")
     return out

@@ -53,12 +53,15 @@ def kernel_paged(q, k_pages, v_pages, page_table, L, bits):
     request, page_table (B, T) int32 maps keys [i * page_size, (i + 1) * page_size) of request b to page
     page_table[b, i]; L is the (common) cache length, T * page_size >= L, page_size a multiple of 64.
     q, bits and the result as in kernel(); the result equals kernel() on the de-paged cache bit for bit."""
-    need(q, "q", torch.float16, dims=4)
+    if not isinstance(q, torch.Tensor) or q.dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError("q: expected a float16 or bfloat16 tensor")
+    dt = q.dtype
+    need(q, "q", dt, dims=4)
     B, kd, Hq, D = q.shape
-    need(k_pages, "k_pages", torch.float16, dims=4)
+    need(k_pages, "k_pages", dt, dims=4)
     pages, Hkv, page_size = k_pages.shape[0], k_pages.shape[1], k_pages.shape[2]
-    need(k_pages, "k_pages", torch.float16, shape=(pages, Hkv, page_size, D))
-    need(v_pages, "v_pages", torch.float16, shape=(pages, Hkv, page_size, D))
+    need(k_pages, "k_pages", dt, shape=(pages, Hkv, page_size, D))
+    need(v_pages, "v_pages", dt, shape=(pages, Hkv, page_size, D))
     need(page_table, "page_table", torch.int32, dims=2)
     T = page_table.shape[1]
     need(page_table, "page_table", torch.int32, shape=(B, T))
@@ -79,6 +82,7 @@ def kernel_paged(q, k_pages, v_pages, page_table, L, bits):
         ws = _lib.workspace(nbytes, dev, stream.cuda_stream)
         rc = lib.vmk_spec_verify_paged(_lib.ptr(q), _lib.ptr(k_pages), _lib.ptr(v_pages), _lib.ptr(page_table), pages,
                                        page_size, T, _lib.ptr(bits), words, _lib.ptr(out), B, kd, Hq, Hkv, D, L,
+                                       1 if dt == torch.bfloat16 else 0,
                                        _lib.ptr(ws), ws.numel(), _lib.ptr(_lib.status_word(dev)), stream.cuda_stream)
     _lib.check(rc, "vmk_spec_verify_paged")
     return out
