@@ -226,6 +226,16 @@ def stage_times(inp, steps, torch):
     out["select_ms"] = avg(lambda: L.vmk_dsa_select_hist(scores.data_ptr(), hist.data_ptr(), None, idx.data_ptr(),
                                                          cnt.data_ptr(), B, Lk, st))
     out["attend_ms"] = avg(lambda: dsa_b200.attend(inp["q"], inp["kv"], idx, cnt))
+    # stage 1 on fp8 index queries and keys (a different input format, reported beside the fp16 stage)
+    iq8, iqs = dsa_b200.quantize_e4m3(inp["iq"])
+    ik8 = torch.empty(B, Lk, 128, dtype=torch.uint8, device=scores.device)
+    iks = torch.empty(B, Lk, dtype=torch.float32, device=scores.device)
+    for b0 in range(0, B, 8):                              # in pieces: the float copy of ik is 4 x its size
+        ik8[b0:b0 + 8], iks[b0:b0 + 8] = dsa_b200.quantize_e4m3(inp["ik"][b0:b0 + 8])
+    out["indexer_fp8_ms"] = avg(lambda: L.vmk_dsa_indexer_hist_fp8(iq8.data_ptr(), iqs.data_ptr(), ik8.data_ptr(),
+                                                                   iks.data_ptr(), inp["w"].data_ptr(), None,
+                                                                   scores.data_ptr(), hist.data_ptr(), B, Lk,
+                                                                   status.data_ptr(), st))
     return out
 
 

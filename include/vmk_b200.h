@@ -230,6 +230,17 @@ VMK_API int vmk_dsa_decode_paged(const void* q, const void* kv_pages, const void
                                  int table_stride, const int32_t* lens, void* out, int32_t* idx_out, int32_t* cnt_out,
                                  int B, int L, int bf16, void* ws, size_t ws_bytes, int32_t* status, void* stream);
 
+/* Stage 1 with the index queries and keys stored in fp8, the format DeepSeek-V3.2-style deployments keep their
+ * index keys in; the reference's op takes fp16 (ops/dsa.py:22-50) and lists this step as outside it
+ * (ops/dsa.py:8-9).  It halves the stream that dominates the op.
+ *   iq8 (B,64,128), ik8 (B,L,128): e4m3 bytes;  iq_scale (B,64), ik_scale (B,L) fp32, positive: the value of an
+ *   element is scale * e4m3.  scores[b,l] = ik_scale[b,l] * sum_h w[b,h] * iq_scale[b,h] * relu(iq8[b,h] . ik8[b,l])
+ *   (the scales are positive, so they commute with the ReLU); hist as vmk_dsa_indexer_hist.
+ * Continue with vmk_dsa_select_hist and vmk_dsa_attend. */
+VMK_API int vmk_dsa_indexer_hist_fp8(const void* iq8, const float* iq_scale, const void* ik8, const float* ik_scale,
+                                     const float* w, const int32_t* lens, float* scores, uint32_t* hist, int B, int L,
+                                     int32_t* status, void* stream);
+
 /* ---- merge of split partials -------------------------------------------------------------------
  * Log-sum-exp merge used after a KV split across GPUs (the reference merges its in-GPU splits the
  * same way, kernels/prefix_opus55_v8.py:211-261).  m, l (parts,rows) and o (parts,rows,D) fp32 with m

@@ -30,6 +30,7 @@ SIGNATURES = {
     "vmk_spec_verify_noalloc": (_i, [_vp] * 4 + [_i] + [_vp] + [_i] * 6 + [_vp, _vp]),
     "vmk_dsa_workspace_bytes": (_sz, [_i] * 2),
     "vmk_dsa_decode": (_i, [_vp] * 9 + [_i] * 2 + [_vp, _sz, _vp, _vp]),
+    "vmk_dsa_indexer_hist_fp8": (_i, [_vp] * 8 + [_i] * 2 + [_vp, _vp]),
     "vmk_dsa_decode_paged": (_i, [_vp] * 6 + [_i] * 3 + [_vp] * 4 + [_i] * 3 + [_vp, _sz, _vp, _vp]),
     "vmk_dsa_decode_bf16": (_i, [_vp] * 9 + [_i] * 2 + [_vp, _sz, _vp, _vp]),
     "vmk_dsa_indexer": (_i, [_vp] * 5 + [_i] * 2 + [_vp, _vp]),

@@ -48,6 +48,21 @@ int make_tmap_3d(CUtensorMap* tm, const void* base, uint64_t width, uint64_t row
   return r == CUDA_SUCCESS ? VMK_OK : VMK_E_DRIVER;
 }
 
+// The same for a tensor of bytes (fp8): (groups, rows, 128) with one 128-byte swizzled row per tensor row.
+int make_tmap_3d_u8(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t groups, uint32_t box_rows) {
+  auto fn = encode_fn();
+  if (fn == nullptr) return VMK_E_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || box_rows > 256) return VMK_E_BADARG;
+  cuuint64_t dims[3] = {128, rows, groups};
+  cuuint64_t strides[2] = {128, 128 * rows};
+  cuuint32_t box[3] = {128, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? VMK_OK : VMK_E_DRIVER;
+}
+
 }  // namespace vmk
 
 extern "C" int vmk_version(void) { return 100; }

@@ -193,6 +193,7 @@ constexpr int kSelShift = 21;
 // Returns 0 or a VMK_E_* code.
 int make_tmap_3d(CUtensorMap* tm, const void* base, uint64_t width, uint64_t rows, uint64_t groups,
                  uint32_t box_w, uint32_t box_rows);
+int make_tmap_3d_u8(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t groups, uint32_t box_rows);
 
 int sm_count();
 

@@ -13,7 +13,8 @@ constexpr int kDV = 512;       // value = first 512 columns of the row
 
 int indexer_tc_launch(const CUtensorMap& tmIK, const CUtensorMap& tmIQ, const float* w, const int32_t* lens,
                       float* scores, uint32_t* hist, int B, int L, int32_t* status, cudaStream_t stream, int bf16,
-                      const int32_t* page_table, int page_size, int table_stride, int pages);
+                      const int32_t* page_table, int page_size, int table_stride, int pages, const float* iq_scale,
+                      const float* ik_scale);
 struct MlaTcParams {
   const __half* q;
   const __half* kv;
@@ -556,7 +557,7 @@ static int indexer_impl(const void* iq, const void* ik, const float* w, const in
   if (rc) return rc;
   if (variant == 1)
     return indexer_tc_launch(p.tmIK, p.tmIQ, w, lens, scores, hist, B, L, status, stream, bf16, pg.table, pg.page_size,
-                             pg.table_stride, pg.pages);
+                             pg.table_stride, pg.pages, nullptr, nullptr);
   p.w = w; p.lens = lens; p.scores = scores; p.B = B; p.L = L; p.status = status;
   static int configured_dev = -1;
   int dev = 0;
@@ -737,4 +738,22 @@ extern "C" int vmk_dsa_decode_paged(const void* q, const void* kv_pages, const v
   if (L <= kTopK) return VMK_E_UNSUPPORTED;          // a cache this short is not worth paging: use vmk_dsa_decode
   return decode_impl(q, kv_pages, iq, ik_pages, w, lens, out, idx_out, cnt_out, B, L, ws, ws_bytes, status, stream, bf16,
                      DsaPages{page_table, pages, page_size, table_stride});
+}
+
+// ---- stage 1 with the index queries and keys in fp8 (e4m3) ------------------------------------------------------
+extern "C" int vmk_dsa_indexer_hist_fp8(const void* iq8, const float* iq_scale, const void* ik8, const float* ik_scale,
+                                        const float* w, const int32_t* lens, float* scores, uint32_t* hist, int B, int L,
+                                        int32_t* status, void* stream) {
+  if (!iq8 || !iq_scale || !ik8 || !ik_scale || !w || !scores || !hist || B <= 0 || L <= 0 || B > 65535)
+    return VMK_E_BADARG;
+  if (!aligned16(iq8) || !aligned16(ik8)) return VMK_E_BADARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(hist, 0, (size_t)B * kSelBins * 4, st) != cudaSuccess) return VMK_E_LAUNCH;
+  if (L <= kTopK) return VMK_OK;                        // nothing to rank
+  CUtensorMap tmIK, tmIQ;
+  int rc = make_tmap_3d_u8(&tmIK, ik8, L, B, kIdxTile);
+  if (rc) return rc;
+  rc = make_tmap_3d_u8(&tmIQ, iq8, kHI, B, kHI);
+  if (rc) return rc;
+  return indexer_tc_launch(tmIK, tmIQ, w, lens, scores, hist, B, L, status, st, 0, nullptr, 0, 0, 0, iq_scale, ik_scale);
 }

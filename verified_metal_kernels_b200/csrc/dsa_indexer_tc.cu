@@ -7,8 +7,8 @@
 //   warp 1     allocates tensor memory, issues 8 tcgen05.mma (M128 N64 K16) per tile into one of four
 //              accumulator buffers, commits the ring slot back to the producer and the accumulator
 //              to the epilogue
-//   warps 2-5  epilogue: tcgen05.ld of their 32 lanes x 64 columns, fp32 ReLU and head-weighted sum,
-//              one coalesced fp32 score per position
+//   warps 2-9  epilogue, two sets of four warps on alternate tiles: tcgen05.ld of their 32 lanes x 64 columns,
+//              fp32 ReLU and head-weighted sum, one coalesced fp32 score per position
 // Every mbarrier wait is bounded; a wait that runs out sets the status word and the CTA winds down
 // through the common exit, where the allocating warp frees its tensor memory.
 #include "tcgen05.cuh"
@@ -23,7 +23,7 @@ constexpr int kAccs = 4;                               // accumulator buffers of
 constexpr int kTileBytes = kTile * kDI * 2;            // 32 KiB
 constexpr int kIqBytes = kHI * kDI * 2;                // 16 KiB
 constexpr int kTmemCols = kAccs * kHI;                 // 256
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 320;
 // ring | iq | w | histogram | barriers | tmem base
 constexpr int kTcSmem =
     kStages * kTileBytes + kIqBytes + kHI * 4 + kSelBins * 4 + (2 * kStages + 2 * kAccs + 1) * 8 + 16 + 1024;
@@ -40,12 +40,19 @@ struct TcParams {
   const int32_t* page_table;   // paged keys: positions [i * page_size, (i+1) * page_size) of request b are page
                                // page_table[b * table_stride + i] of tmIK = (pages, page_size, 128); null = (B, L, 128)
   int page_size, table_stride, pages;
+  const float* iq_scale;       // fp8 index keys only: per (request, head) scale of iq (B, 64), and
+  const float* ik_scale;       // per position scale of ik (B, L); tmIK / tmIQ then describe bytes
   int32_t* status;
 };
 
 __device__ __forceinline__ float relu_nan(float x) { return (x < 0.f) ? 0.f : x; }
 
+// FP8: ik and iq are e4m3 bytes with scales (a tile is 16 KiB, one 128-byte swizzled row per position; four
+// kind::f8f6f4 MMAs of K = 32 per tile).  The shared-memory layout keeps the fp16 sizes.
+template <bool FP8>
 __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_constant__ TcParams p) {
+  constexpr int kTileLoad = FP8 ? kTileBytes / 2 : kTileBytes;   // bytes one tile brings in
+  constexpr int kIqLoad = FP8 ? kIqBytes / 2 : kIqBytes;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sIQ = smem + kStages * kTileBytes;
@@ -82,7 +89,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
     mbar_init(iq_full, 1);
     fence_mbar_init();
   }
-  if (tid < kHI) sW[tid] = p.w[b * kHI + tid];
+  if (tid < kHI) sW[tid] = p.w[b * kHI + tid] * (FP8 ? p.iq_scale[b * kHI + tid] : 1.f);
   if (p.hist != nullptr)
     for (int i = tid; i < kSelBins; i += kTcThreads) sHist[i] = 0u;
   if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
@@ -95,9 +102,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
   if (warp == 0) {
     // ---------------------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      mbar_expect_tx(iq_full, kIqBytes);
+      mbar_expect_tx(iq_full, kIqLoad);
       tma_load_3d(sIQ, &p.tmIQ, 0, 0, b, iq_full);
-      tma_load_3d(sIQ + kIqBytes / 2, &p.tmIQ, 64, 0, b, iq_full);
+      if (!FP8) tma_load_3d(sIQ + kIqBytes / 2, &p.tmIQ, 64, 0, b, iq_full);
       // Paged keys: a 128-position tile lies inside one page (page_size is a multiple of 128).  The table entry of
       // the NEXT tile is requested one iteration ahead, so that its latency hides behind the wait for a free slot.
       auto page_of = [&](int pos) -> int {
@@ -114,7 +121,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
           break;
         }
         uint8_t* st = smem + s * kTileBytes;
-        mbar_expect_tx(&full[s], kTileBytes);
+        mbar_expect_tx(&full[s], kTileLoad);
         int y = (t0 + j) * kTile, z = b;
         if (p.page_table != nullptr) {
           // a page id outside the pool makes the TMA coordinate out of range, which reads zeros
@@ -122,7 +129,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
           y %= p.page_size;
         }
         tma_load_3d(st, &p.tmIK, 0, y, z, &full[s]);
-        tma_load_3d(st + kTileBytes / 2, &p.tmIK, 64, y, z, &full[s]);
+        if (!FP8) tma_load_3d(st + kTileBytes / 2, &p.tmIK, 64, y, z, &full[s]);
       }
     }
   } else if (warp == 1) {
@@ -131,7 +138,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
       if (!mbar_wait(iq_full, 0)) timed_out = true;
       const uint32_t iq_addr = smem_u32(sIQ);
       // Instruction descriptor: fp16 or bf16 A and B (both K-major), fp32 accumulate, M = 128, N = 64.
-      const uint32_t idesc = umma_idesc_16(kTile, kHI, 0, p.bf16);
+      const uint32_t idesc = umma_idesc_16(kTile, kHI, 0, FP8 ? 0 : p.bf16);
       for (int j = 0; j < nt && !timed_out; ++j) {
         const int s = j % kStages, a = j % kAccs;
         if (j >= kAccs && !mbar_wait(&acc_empty[a], (uint32_t)(((j / kAccs) - 1) & 1))) {
@@ -145,24 +152,39 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
         tc_fence_after();
         const uint32_t a_addr = smem_u32(smem + s * kTileBytes);
         const uint32_t d_tmem = tmem_base + (uint32_t)(a * kHI);
+        if (FP8) {
 #pragma unroll
-        for (int k = 0; k < kDI / 16; ++k) {
-          // K step k: 64-element half (k / 4), 32-byte offset (k % 4) inside the 128-byte swizzled row
-          const uint64_t da = umma_desc_sw128(a_addr + (k >> 2) * (kTileBytes / 2) + (k & 3) * 32);
-          const uint64_t db = umma_desc_sw128(iq_addr + (k >> 2) * (kIqBytes / 2) + (k & 3) * 32);
-          umma_f16(d_tmem, da, db, idesc, k > 0 ? 1u : 0u);
+          for (int k = 0; k < kDI / 32; ++k)    // K step k: 32 bytes further inside the one 128-byte swizzled row
+            umma_f8(d_tmem, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(iq_addr + k * 32), idesc, k > 0 ? 1u : 0u);
+        } else {
+#pragma unroll
+          for (int k = 0; k < kDI / 16; ++k) {
+            // K step k: 64-element half (k / 4), 32-byte offset (k % 4) inside the 128-byte swizzled row
+            const uint64_t da = umma_desc_sw128(a_addr + (k >> 2) * (kTileBytes / 2) + (k & 3) * 32);
+            const uint64_t db = umma_desc_sw128(iq_addr + (k >> 2) * (kIqBytes / 2) + (k & 3) * 32);
+            umma_f16(d_tmem, da, db, idesc, k > 0 ? 1u : 0u);
+          }
         }
         umma_commit(&empty[s]);        // the ring slot may be refilled once these MMAs have read it
         umma_commit(&acc_full[a]);     // the accumulator is complete
       }
     }
   } else {
-    // ---------------------------------------------------------------------------- epilogue (warps 2..5)
+    // ---------------------------------------------------------------------------- epilogue (warps 2..9)
+    // Two sets of four warps take alternate tiles (tile j uses accumulator j % 4, so a set always sees the same two
+    // accumulators): with fp8 keys a tile arrives every ~700 cycles at the HBM rate, more than one set can keep up with.
+    const int set = (warp - 2) >> 2;
     const int quarter = warp & 3;                         // tensor-memory lanes [32 q, 32 q + 32)
     const int row = quarter * 32 + lane;                  // position inside the tile
     float* dst = p.scores + (size_t)b * p.L;
-    for (int j = 0; j < nt; ++j) {
+    // (16-bit keys are HBM-bound with one set: the second set then stays idle)
+    constexpr int kSets = FP8 ? 2 : 1;
+    for (int j = set < kSets ? set : nt; j < nt; j += kSets) {
       const int a = j % kAccs;
+      const int pos = (t0 + j) * kTile + row;
+      // fp8: this position's key scale, requested before the wait so that its latency hides behind it
+      float kscale = 1.f;
+      if (FP8 && pos < n) kscale = p.ik_scale[(size_t)b * p.L + pos];
       const bool ok = mbar_wait(&acc_full[a], (uint32_t)((j / kAccs) & 1));
       if (!__all_sync(0xffffffffu, ok)) {
         timed_out = true;
@@ -182,8 +204,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
       for (int h = 0; h < 32; ++h) s += sW[h] * relu_nan(__uint_as_float(r0[h]));
 #pragma unroll
       for (int h = 0; h < 32; ++h) s += sW[32 + h] * relu_nan(__uint_as_float(r1[h]));
-      const int pos = (t0 + j) * kTile + row;
       if (pos < n) {
+        if (FP8) s *= kscale;
         dst[pos] = s;
         // first level of the top-k radix select, fused here so that the select pass starts one level down
         if (p.hist != nullptr) atomicAdd(&sHist[score_key(s) >> kSelShift], 1u);
@@ -211,7 +233,7 @@ int indexer_chunks(int B, int tiles);
 
 int indexer_tc_launch(const CUtensorMap& tmIK, const CUtensorMap& tmIQ, const float* w, const int32_t* lens,
                       float* scores, uint32_t* hist, int B, int L, int32_t* status, cudaStream_t stream, int bf16, const int32_t* page_table, int page_size,
-                      int table_stride, int pages) {
+                      int table_stride, int pages, const float* iq_scale, const float* ik_scale) {
   TcParams p;
   memset(&p, 0, sizeof(p));
   p.tmIK = tmIK;
@@ -219,16 +241,21 @@ int indexer_tc_launch(const CUtensorMap& tmIK, const CUtensorMap& tmIQ, const fl
   p.w = w; p.lens = lens; p.scores = scores; p.hist = hist; p.B = B; p.L = L; p.status = status;
   p.bf16 = bf16;
   p.page_table = page_table; p.page_size = page_size; p.table_stride = table_stride; p.pages = pages;
+  p.iq_scale = iq_scale; p.ik_scale = ik_scale;
+  const bool fp8 = iq_scale != nullptr;
   static int configured_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured_dev != dev) {
-    cudaError_t e = cudaFuncSetAttribute(indexer_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem);
+    cudaError_t e = cudaFuncSetAttribute(indexer_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem);
+    if (e != cudaSuccess) return check_launch(e);
+    e = cudaFuncSetAttribute(indexer_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem);
     if (e != cudaSuccess) return check_launch(e);
     configured_dev = dev;
   }
   const int chunks = indexer_chunks(B, cdiv(L, kTile));
-  indexer_tc_kernel<<<dim3(chunks, B), kTcThreads, kTcSmem, stream>>>(p);
+  if (fp8) indexer_tc_kernel<true><<<dim3(chunks, B), kTcThreads, kTcSmem, stream>>>(p);
+  else indexer_tc_kernel<false><<<dim3(chunks, B), kTcThreads, kTcSmem, stream>>>(p);
   return check_launch(cudaGetLastError());
 }
 

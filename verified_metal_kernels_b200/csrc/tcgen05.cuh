@@ -30,6 +30,18 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t 
       : "memory");
 }
 
+// kind::f8f6f4 with e4m3 operands (format fields 0) and fp32 accumulation: the instruction descriptor has the
+// same bits as umma_idesc_f16, one instruction covers K = 32 elements (32 bytes of a K-major row).
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // Same instruction with the descriptors passed as (low, high) 32-bit words.  The single issuing thread
 // is latency-bound on scalar code, so callers precompute the high words and the base of the low words
 // and only add a constant per K step.

@@ -183,6 +183,44 @@ def indexer_hist(iq, ik, w, lens=None):
     return scores, hist
 
 
+def quantize_e4m3(x):
+    """Row-wise fp8 quantisation of a (..., 128) tensor: (bytes of torch.float8_e4m3fn values as uint8, fp32 scale
+    per row) with x ~ scale * e4m3, scale = max|row| / 448 (1 for an all-zero row)."""
+    amax = x.float().abs().amax(dim=-1)
+    scale = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+    q = (x.float() / scale.unsqueeze(-1)).to(torch.float8_e4m3fn)
+    return q.view(torch.uint8).contiguous(), scale.contiguous()
+
+
+def indexer_hist_fp8(iq8, iq_scale, ik8, ik_scale, w, lens=None):
+    """Stage 1 on fp8 index queries and keys (see quantize_e4m3): (scores (B,L) fp32, hist (B,2048) int32)."""
+    need(ik8, "ik8", torch.uint8, dims=3)
+    B, L = ik8.shape[0], ik8.shape[1]
+    need(ik8, "ik8", torch.uint8, shape=(B, L, DI))
+    need(iq8, "iq8", torch.uint8, shape=(B, HI, DI))
+    need(iq_scale, "iq_scale", torch.float32, shape=(B, HI))
+    need(ik_scale, "ik_scale", torch.float32, shape=(B, L))
+    need(w, "w", torch.float32, shape=(B, HI))
+    lib = _lib.lib()
+    with torch.cuda.device(ik8.device):
+        scores = torch.zeros(B, L, dtype=torch.float32, device=ik8.device)
+        hist = torch.empty(B, 2048, dtype=torch.int32, device=ik8.device)
+        rc = lib.vmk_dsa_indexer_hist_fp8(_lib.ptr(iq8), _lib.ptr(iq_scale), _lib.ptr(ik8), _lib.ptr(ik_scale), _lib.ptr(w),
+                                          _lib.ptr(lens), _lib.ptr(scores), _lib.ptr(hist), B, L,
+                                          _lib.ptr(_lib.status_word(ik8.device)), torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "vmk_dsa_indexer_hist_fp8")
+    return scores, hist
+
+
+def kernel_fp8_index(q, kv, iq8, iq_scale, ik8, ik_scale, w, lens=None, return_selection=False):
+    """The op with the index queries and keys in fp8 (q and kv stay fp16 or bf16): stage 1 on fp8, then the
+    usual select and sparse attention."""
+    scores, hist = indexer_hist_fp8(iq8, iq_scale, ik8, ik_scale, w, lens)
+    idx, cnt = select(scores, lens, hist)
+    out = attend(q, kv, idx, cnt)
+    return (out, idx, cnt) if return_selection else out
+
+
 def select(scores, lens=None, hist=None):
     """Stage 2 alone: (idx (B,2048) int32 ascending, cnt (B,) int32).  `hist` is stage 1's fused histogram."""
     need(scores, "scores", torch.float32, dims=2)
