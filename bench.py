@@ -282,11 +282,11 @@ def side_line(config, torch, steps):
             inp = dict(q=inp["q"], k_pages=r16(B * T + 7, 8, page, 128), v_pages=r16(B * T + 7, 8, page, 128),
                        page_table=perm.contiguous(), L=L, bits=inp["bits"])
             name += f", paged cache (page {page})"
-    elif config == "decode":
+    elif config in ("decode", "decode_small"):
         # plain single-token decode (extension op): 64 requests with caches of 16k..32k keys
         from verified_metal_kernels_b200.ops import decode as op
         opname = "decode"
-        shape = op.CONFIG_BENCH
+        shape = op.CONFIG_BENCH if config == "decode" else dict(B=8, L=16384)     # the small one is for profiling
         B, L = shape["B"], shape["L"]
         lens = torch.randint(L // 2, L + 1, (B,), generator=g, device="cuda", dtype=torch.int32)
         inp = dict(q=r16(B, 32, 128), k=r16(B, 8, L, 128), v=r16(B, 8, L, 128), lens=lens)
