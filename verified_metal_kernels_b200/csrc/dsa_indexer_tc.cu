@@ -4,7 +4,7 @@
 // tcgen05 accumulator of 128 lanes x 64 fp32 columns in tensor memory.  A CTA owns a contiguous run of
 // tiles of one request and is warp-specialised:
 //   warp 0     TMA producer: 32 KiB ik tiles into a 6-deep shared-memory ring (128-byte swizzle)
-//   warp 1     allocates tensor memory, issues 8 tcgen05.mma (M128 N64 K16) per tile into one of four
+//   warp 1     (and warp 10 for fp8 keys) allocates tensor memory, issues 8 tcgen05.mma (M128 N64 K16) per tile into one of four
 //              accumulator buffers, commits the ring slot back to the producer and the accumulator
 //              to the epilogue
 //   warps 2-9  epilogue, two sets of four warps on alternate tiles: tcgen05.ld of their 32 lanes x 64 columns,
@@ -23,7 +23,7 @@ constexpr int kAccs = 4;                               // accumulator buffers of
 constexpr int kTileBytes = kTile * kDI * 2;            // 32 KiB
 constexpr int kIqBytes = kHI * kDI * 2;                // 16 KiB
 constexpr int kTmemCols = kAccs * kHI;                 // 256
-constexpr int kTcThreads = 320;
+constexpr int kTcThreads = 352;
 // ring | iq | w | histogram | barriers | tmem base
 constexpr int kTcSmem =
     kStages * kTileBytes + kIqBytes + kHI * 4 + kSelBins * 4 + (2 * kStages + 2 * kAccs + 1) * 8 + 16 + 1024;
@@ -51,7 +51,8 @@ __device__ __forceinline__ float relu_nan(float x) { return (x < 0.f) ? 0.f : x;
 // kind::f8f6f4 MMAs of K = 32 per tile).  The shared-memory layout keeps the fp16 sizes.
 template <bool FP8>
 __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_constant__ TcParams p) {
-  constexpr int kTileLoad = FP8 ? kTileBytes / 2 : kTileBytes;   // bytes one tile brings in
+  constexpr int kTileLoad = FP8 ? kTileBytes / 2 : kTileBytes;   // bytes one tile brings in = size of a ring slot
+  constexpr int kSt = kStages;                                   // ring slots (twelve fp8 slots were no faster)
   constexpr int kIqLoad = FP8 ? kIqBytes / 2 : kIqBytes;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -59,8 +60,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
   float* sW = reinterpret_cast<float*>(sIQ + kIqBytes);
   uint32_t* sHist = reinterpret_cast<uint32_t*>(sW + kHI);
   uint64_t* full = reinterpret_cast<uint64_t*>(sHist + kSelBins);
-  uint64_t* empty = full + kStages;
-  uint64_t* acc_full = empty + kStages;
+  uint64_t* empty = full + kSt;
+  uint64_t* acc_full = empty + kSt;
   uint64_t* acc_empty = acc_full + kAccs;
   uint64_t* iq_full = acc_empty + kAccs;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(iq_full + 1);
@@ -78,7 +79,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
   const int nt = t1 - t0;
 
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kSt; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
@@ -113,14 +114,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
       };
       int pg_next = (p.page_table != nullptr && nt > 0) ? page_of(t0 * kTile) : 0;
       for (int j = 0; j < nt; ++j) {
-        const int s = j % kStages;
+        const int s = j % kSt;
         const int pg = pg_next;
         if (p.page_table != nullptr && j + 1 < nt) pg_next = page_of((t0 + j + 1) * kTile);
-        if (j >= kStages && !mbar_wait(&empty[s], (uint32_t)(((j / kStages) - 1) & 1))) {
+        if (j >= kSt && !mbar_wait(&empty[s], (uint32_t)(((j / kSt) - 1) & 1))) {
           timed_out = true;
           break;
         }
-        uint8_t* st = smem + s * kTileBytes;
+        uint8_t* st = smem + s * kTileLoad;
         mbar_expect_tx(&full[s], kTileLoad);
         int y = (t0 + j) * kTile, z = b;
         if (p.page_table != nullptr) {
@@ -132,25 +133,29 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
         if (!FP8) tma_load_3d(st + kTileBytes / 2, &p.tmIK, 64, y, z, &full[s]);
       }
     }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+  } else if (warp == 1 || warp == 10) {
+    // ---------------------------------------------------------------------------- MMA issuers
+    // With fp8 keys the two issuing threads take alternate tiles (their accumulators differ): a tile's four
+    // instructions take ~390 cycles, and the two waits in front of them would otherwise cost as much again.
+    constexpr int kIssuers = FP8 ? 2 : 1;
+    const int mi = warp == 1 ? 0 : 1;
+    if (lane == 0 && mi < kIssuers) {
       if (!mbar_wait(iq_full, 0)) timed_out = true;
       const uint32_t iq_addr = smem_u32(sIQ);
       // Instruction descriptor: fp16 or bf16 A and B (both K-major), fp32 accumulate, M = 128, N = 64.
       const uint32_t idesc = umma_idesc_16(kTile, kHI, 0, FP8 ? 0 : p.bf16);
-      for (int j = 0; j < nt && !timed_out; ++j) {
-        const int s = j % kStages, a = j % kAccs;
+      for (int j = mi; j < nt && !timed_out; j += kIssuers) {
+        const int s = j % kSt, a = j % kAccs;
         if (j >= kAccs && !mbar_wait(&acc_empty[a], (uint32_t)(((j / kAccs) - 1) & 1))) {
           timed_out = true;
           break;
         }
-        if (!mbar_wait(&full[s], (uint32_t)((j / kStages) & 1))) {
+        if (!mbar_wait(&full[s], (uint32_t)((j / kSt) & 1))) {
           timed_out = true;
           break;
         }
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(smem + s * kTileBytes);
+        const uint32_t a_addr = smem_u32(smem + s * kTileLoad);
         const uint32_t d_tmem = tmem_base + (uint32_t)(a * kHI);
         if (FP8) {
 #pragma unroll
@@ -169,7 +174,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
         umma_commit(&acc_full[a]);     // the accumulator is complete
       }
     }
-  } else {
+  } else if (warp >= 2 && warp <= 9) {
     // ---------------------------------------------------------------------------- epilogue (warps 2..9)
     // Two sets of four warps take alternate tiles (tile j uses accumulator j % 4, so a set always sees the same two
     // accumulators): with fp8 keys a tile arrives every ~700 cycles at the HBM rate, more than one set can keep up with.
