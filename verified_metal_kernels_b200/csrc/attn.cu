@@ -163,8 +163,8 @@ static int tc_split_cap(int units) {
   return cap < 1 ? 1 : cap;
 }
 
-// tcgen05 path: one CTA per SM, 256-row tiles, 64-key blocks.  The split count minimises
-// waves x (blocks per CTA + a fixed per-CTA overhead of about six blocks), which avoids a mostly empty
+// tcgen05 path: one CTA per SM, 256-row tiles, 128-key blocks.  The split count minimises
+// waves x (blocks per CTA + a fixed per-CTA overhead of about three blocks), which avoids a mostly empty
 // last wave.
 static void plan_role_tc(RolePlan* r, int groups, int rows, int keys) {
   constexpr int kTcBlock = 128;      // keys per block of the tensor-memory kernel
