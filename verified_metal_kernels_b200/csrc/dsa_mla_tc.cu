@@ -521,7 +521,9 @@ extern "C" VMK_API int vmk_debug_mla_trace(long long* out) {
 // Merge of the units a range boundary cuts.  grid (ncta, 4): CTA (c, hq) looks at the boundary where range c
 // starts; if it lies inside a unit and is the first such boundary of that unit, it merges the unit's partials
 // (the last unit of range c - 1, then the first unit of ranges c, c + 1, ... while they start inside the unit)
-// for heads [32 hq, 32 hq + 32).  256 threads: lane = head, warp w = column groups [8w, 8w + 8).
+// for heads [32 hq, 32 hq + 32).  grid (ncta, 4, 4), 256 threads: lane = head, CTA z and warp w = the two column
+// groups of four [16 z + 2 w, 16 z + 2 w + 2): short serial work per thread, since with few requests only a handful
+// of CTAs have anything to merge.
 __global__ void __launch_bounds__(256) mla_tc_combine_kernel(const float* __restrict__ part_o,
                                                              const float* __restrict__ part_ml, int B, int ncta,
                                                              __half* __restrict__ out, int bf16) {
@@ -533,7 +535,7 @@ __global__ void __launch_bounds__(256) mla_tc_combine_kernel(const float* __rest
   const int u = s / kUnitSlots;
   const int prev = range_start(c - 1, total, ncta);
   if (prev > u * kUnitSlots) return;                    // an earlier boundary inside the unit does the merge
-  const int head = blockIdx.y * 32 + (threadIdx.x & 31), cg0 = (threadIdx.x >> 5) * 8;
+  const int head = blockIdx.y * 32 + (threadIdx.x & 31), cg0 = blockIdx.z * 16 + (threadIdx.x >> 5) * 2;
   const int unit_end = (u + 1) * kUnitSlots;
   // range c - 1 holds this unit as its last unit (record 1) unless the unit is also its first
   const size_t part_prev = (size_t)(c - 1) * 2 + (prev / kUnitSlots == u ? 0 : 1);
@@ -541,16 +543,16 @@ __global__ void __launch_bounds__(256) mla_tc_combine_kernel(const float* __rest
   while (c_end < ncta && range_start(c_end, total, ncta) < unit_end) ++c_end;
   float M = part_ml[(part_prev * kMH + head) * 2];
   for (int cc = c; cc < c_end; ++cc) M = fmaxf(M, part_ml[((size_t)cc * 2 * kMH + head) * 2]);
-  float4 acc[8];
+  float4 acc[2];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int i = 0; i < 2; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   float lsum = 0.f;
   auto add = [&](size_t part) {
     const float m = part_ml[(part * kMH + head) * 2];
     const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
     const float4* src = reinterpret_cast<const float4*>(part_o) + (part * 64 + cg0) * kMH + head;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < 2; ++i) {
       const float4 o = src[(size_t)i * kMH];
       acc[i].x += w * o.x; acc[i].y += w * o.y; acc[i].z += w * o.z; acc[i].w += w * o.w;
     }
@@ -560,15 +562,12 @@ __global__ void __launch_bounds__(256) mla_tc_combine_kernel(const float* __rest
   for (int cc = c; cc < c_end; ++cc) add((size_t)cc * 2);
   const float inv = 1.f / lsum;
   __half* dst = out + ((size_t)(u % B) * kMH + head) * kDV + (u / B) * 256 + cg0 * 4;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    uint4 v;
-    v.x = pack2(acc[2 * i].x * inv, acc[2 * i].y * inv, bf16);
-    v.y = pack2(acc[2 * i].z * inv, acc[2 * i].w * inv, bf16);
-    v.z = pack2(acc[2 * i + 1].x * inv, acc[2 * i + 1].y * inv, bf16);
-    v.w = pack2(acc[2 * i + 1].z * inv, acc[2 * i + 1].w * inv, bf16);
-    reinterpret_cast<uint4*>(dst)[i] = v;
-  }
+  uint4 v;
+  v.x = pack2(acc[0].x * inv, acc[0].y * inv, bf16);
+  v.y = pack2(acc[0].z * inv, acc[0].w * inv, bf16);
+  v.z = pack2(acc[1].x * inv, acc[1].y * inv, bf16);
+  v.w = pack2(acc[1].z * inv, acc[1].w * inv, bf16);
+  *reinterpret_cast<uint4*>(dst) = v;
 }
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -618,7 +617,7 @@ int mla_tc_launch(const MlaTcParams& p0, float* workspace, cudaStream_t stream) 
   if (rc || p.ncta == 1) return rc;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3(p.ncta, 4);
+  cfg.gridDim = dim3(p.ncta, 4, 4);
   cfg.blockDim = dim3(256);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
