@@ -151,10 +151,19 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_tc_kernel(const MlaTcParam
     fence_mbar_init();
   }
   if (warp == 11) tmem_alloc(tmem_slot, kMlaCols);
+  if (warp == 9) {
+    // the first request's query rows towards L2: they do not depend on the kernel before this one
+    const uint8_t* fq = reinterpret_cast<const uint8_t*>(p.q + (size_t)(u_first % p.B) * kMH * kDK);
+    for (int i = lane; i < kMH * kDK * 2 / 128; i += 32)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(fq + (size_t)i * 128));
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Launched as a programmatic dependent: everything above overlaps the tail of the kernel before (the top-k
+  // selection, in the fused call); the candidate lists and counts are read only below this line.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   bool timed_out = false;
   if (warp == 0) MLA_M(0);
@@ -612,19 +621,22 @@ int mla_tc_launch(const MlaTcParams& p0, float* workspace, cudaStream_t stream) 
   const size_t n = (size_t)p.ncta * 2 * kMH;
   p.part_o = workspace;
   p.part_ml = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + align_up(n * 256 * 4, 256));
-  mla_tc_kernel<<<p.ncta, kMlaThreads, kMlaTcSmem, stream>>>(p);
-  int rc = check_launch(cudaGetLastError());
-  if (rc || p.ncta == 1) return rc;
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3(p.ncta, 4, 4);
-  cfg.blockDim = dim3(256);
-  cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(p.ncta);
+  cfg.blockDim = dim3(kMlaThreads);
+  cfg.dynamicSmemBytes = kMlaTcSmem;
+  cfg.stream = stream;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  int rc = check_launch(cudaLaunchKernelEx(&cfg, mla_tc_kernel, p));
+  if (rc || p.ncta == 1) return rc;
+  cfg.gridDim = dim3(p.ncta, 4, 4);
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = 0;
   return check_launch(cudaLaunchKernelEx(&cfg, mla_tc_combine_kernel, (const float*)p.part_o, (const float*)p.part_ml, p.B,
                                          p.ncta, p.out, p.bf16));
 }

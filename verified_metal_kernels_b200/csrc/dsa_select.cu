@@ -291,6 +291,9 @@ __global__ void __launch_bounds__(kSelThreads, 1) select_kernel(const float* __r
                                                              const int32_t* __restrict__ lens,
                                                              int32_t* __restrict__ idx, int32_t* __restrict__ cnt,
                                                              int L, int csize) {
+  // the kernel after this one (the sparse attention, in the fused call) may set itself up while this one runs;
+  // it waits for this grid to finish before it reads the lists written here
+  asm volatile("griddepcontrol.launch_dependents;");
   __shared__ SelShared sh;
   extern __shared__ uint32_t cand[];          // [kCandCap] keys, then [kCandCap] positions
   uint32_t* ckey = cand;
