@@ -187,6 +187,33 @@ def test_deterministic_and_inputs_untouched():
         assert torch.equal(v, dinp[k]), f"input {k} was modified"
 
 
+@pytest.mark.parametrize("B,L", [(8, 32768), (3, 9000)])
+def test_back_to_back_fused_calls_equal_the_staged_calls(B, L):
+    """Stage 3 starts before stage 2 has finished (a dependent launch) and reads the lists only after it has.
+    Two different inputs alternate through the same workspace with no synchronisation between the calls: a
+    list read too early would be the other input's, and the output would differ from the staged result."""
+    fn = load_kernel("dsa")
+    cases = []
+    for seed in (41, 42):
+        d = _verify.device_inputs("dsa", op.make_inputs(dict(B=B, L=L), seed=seed))
+        scores, hist = dsa_b200.indexer_hist(d["iq"], d["ik"], d["w"], d["lens"])
+        torch.cuda.synchronize()
+        idx, cnt = dsa_b200.select(scores, d["lens"], hist=hist)
+        torch.cuda.synchronize()
+        want = dsa_b200.attend(d["q"], d["kv"], idx, cnt)
+        torch.cuda.synchronize()
+        cases.append((d, want))
+    assert not torch.equal(cases[0][1], cases[1][1])
+    outs = []
+    for it in range(24):
+        d, _ = cases[it & 1]
+        outs.append(fn(**d))
+    torch.cuda.synchronize()
+    _verify.assert_clean_status()
+    for it, o in enumerate(outs):
+        assert torch.equal(o, cases[it & 1][1]), f"call {it} differs from the staged result"
+
+
 def test_argument_errors():
     inp = op.make_inputs(dict(B=1, L=64), seed=0)
     d = _verify.device_inputs("dsa", inp)
