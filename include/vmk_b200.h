@@ -260,6 +260,39 @@ VMK_API int vmk_spec_partial(const void* q, const void* k, const void* v, const 
                      int B, int kd, int Hq, int Hkv, int D, int L, int key_lo, int key_hi, float* part_m,
                      float* part_l, float* part_o, void* ws, size_t ws_bytes, int32_t* status, void* stream);
 
+/* The same partials as ONE packed record per output row, `records` (rows, 130) fp32 = (m, l, o[128]): the form
+ * in which a rank's partials cross to another GPU in a single exchange (one all-to-all or all-gather of one
+ * buffer), and the input of vmk_lse_merge_packed.  The reference merges its in-GPU splits from separate
+ * (m, l) and o arrays (kernels/prefix_opus55_v8.py:211-261); its split plan is kernels/prefix_opus55_v8.py:320-331.
+ *   vmk_prefix_partial_packed: q points at head h0 of request 0 of a (N, q_heads, D) tensor and the call covers
+ *   heads [h0, h0 + Hq) (q_heads >= Hq; q_heads == Hq for all heads), with kp, vp (Hkv, P, D) and ks, vs
+ *   (N, Hkv, S, D) the matching slice of kv heads.  rows = N*Hq, row (n, head) at n*Hq + head.  key_lo == key_hi
+ *   skips the shared prefix (suffix-only partials); with_suffix = 0 skips the private suffixes; at least one of
+ *   the two must be left.  bf16 = 0 / 1.  Workspace: vmk_prefix_workspace_bytes(N, Hq, Hkv, D, P, S).
+ *   vmk_spec_partial_packed: as vmk_spec_partial; rows = B*kd*Hq.  mask_start is the first position of k, v that
+ *   is a draft: -1 (or L - kd) when the tensor ends with the drafts; any value >= L when k, v are a slice of a
+ *   longer cache whose drafts lie in another rank's slice, so that no key of this call is masked.
+ *   vmk_lse_merge_packed: records (parts, rows, 130) -> out (rows, 128) fp16 (bf16 = 0) or bf16 (1); D must be 128. */
+VMK_API int vmk_prefix_partial_packed(const void* q, int q_heads, const void* kp, const void* vp, const void* ks,
+                                      const void* vs, const int32_t* slens, int N, int Hq, int Hkv, int D, int P,
+                                      int S, int key_lo, int key_hi, int with_suffix, int bf16, float* records,
+                                      void* ws, size_t ws_bytes, int32_t* status, void* stream);
+VMK_API int vmk_spec_partial_packed(const void* q, const void* k, const void* v, const uint32_t* bits, int bits_words,
+                                    int B, int kd, int Hq, int Hkv, int D, int L, int key_lo, int key_hi,
+                                    int mask_start, int bf16, float* records, void* ws, size_t ws_bytes,
+                                    int32_t* status, void* stream);
+VMK_API int vmk_lse_merge_packed(const float* records, int parts, int rows, int D, int bf16, void* out, void* stream);
+
+/* ---- process-wide behaviour switches, for A/B comparisons and cross-checks ----------------------------
+ * No counterpart in the reference (its variants are separate kernel files).  Each returns VMK_OK.
+ *   vmk_attn_set_tc(0): prefix / spec row tiles of more than 64 rows use the warp-level kernel instead of
+ *   the tcgen05 one (1, the default).
+ *   vmk_dsa_set_indexer_variant(v), vmk_dsa_set_attend_variant(v): 1 = tcgen05 kernels (default), 0 = the
+ *   warp-level mma.sync kernels kept as cross-checks (fp16, contiguous caches only); other values are refused. */
+VMK_API int vmk_attn_set_tc(int on);
+VMK_API int vmk_dsa_set_indexer_variant(int variant);
+VMK_API int vmk_dsa_set_attend_variant(int variant);
+
 #ifdef __cplusplus
 }
 #endif

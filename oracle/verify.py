@@ -37,6 +37,10 @@ def import_kernel(path):
     return mod.kernel
 
 
+def rel_is_package(path):
+    return os.path.relpath(os.path.abspath(path), ROOT).startswith("verified_metal_kernels_b200" + os.sep)
+
+
 def load_kernel_any(path):
     """Kernel modules inside the package use relative imports: import those by module name."""
     rel = os.path.relpath(os.path.abspath(path), ROOT)
@@ -60,6 +64,9 @@ def child_outputs(opname, kernel_path, out):
             o = fn(**inp)
             o = o[0] if isinstance(o, (tuple, list)) else o
             torch.cuda.synchronize()
+            if rel_is_package(kernel_path):         # this library's kernels report device-side trouble in a status word
+                import verified_metal_kernels_b200
+                verified_metal_kernels_b200.check_status(o.device)      # raises: the case fails like any exception
             arrays[key] = o.float().cpu().numpy()
             meta[key] = dict(ok=True, dtype=str(o.dtype), s=time.time() - t0)
         except Exception as e:                      # any exception is a failed case

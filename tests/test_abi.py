@@ -31,6 +31,16 @@ def test_header_and_binding_agree(lib):
         assert hasattr(raw, s), f"{s} declared in include/vmk_b200.h but not exported"
 
 
+def test_nothing_is_exported_that_the_header_does_not_declare(lib):
+    """Every dynamic symbol named vmk_* is declared in the header, except the trace readers of debug builds."""
+    import subprocess
+    out = subprocess.run(["nm", "-D", "--defined-only", _lib.LIB_PATH], capture_output=True, text=True, check=True).stdout
+    exported = {ln.split()[-1] for ln in out.splitlines() if ln.split() and ln.split()[-1].startswith("vmk_")}
+    assert exported, "no vmk_* symbol found in the dynamic symbol table"
+    extra = exported - set(header_symbols()) - set(_lib.DEBUG_EXPORTS)
+    assert not extra, f"exported but not declared in include/vmk_b200.h: {sorted(extra)}"
+
+
 def test_every_declaration_cites_the_reference():
     text = open(os.path.join(ROOT, "include", "vmk_b200.h")).read()
     assert text.count("kernels/") >= 6 and "verify.py:" in text
@@ -61,6 +71,15 @@ def test_bad_arguments_are_rejected_before_any_launch(lib):
     assert lib.vmk_dsa_decode(None, None, None, None, None, None, None, None, None, 1, 64, None, 0, None, None) == -1
     assert lib.vmk_dsa_select(None, None, None, None, 1, 64, None) == -1
     assert lib.vmk_lse_merge(None, None, None, 2, 4, 128, None, None) == -1
+    assert lib.vmk_lse_merge_packed(None, 2, 4, 128, 0, None, None) == -1
+    assert lib.vmk_lse_merge_packed(256, 2, 4, 64, 0, 256, None) == -2             # D != 128
+    assert lib.vmk_prefix_partial_packed(None, 32, None, None, None, None, None, 1, 32, 8, 128, 8, 8, 0, 8, 1, 0, None,
+                                         None, 0, None, None) == -1
+    # a slice of heads wider than the tensor it is cut from
+    assert lib.vmk_prefix_partial_packed(256, 4, 256, 256, 256, 256, None, 1, 8, 2, 128, 8, 8, 0, 8, 1, 0, 256,
+                                         256, 1 << 20, None, None) == -1
+    assert lib.vmk_spec_partial_packed(None, None, None, None, 1, 1, 4, 32, 8, 128, 64, 0, 64, -1, 0, None, None, 0,
+                                       None, None) == -1
     # misaligned pointer
     assert lib.vmk_prefix_decode(8, 16, 16, 16, 16, None, 16, 1, 32, 8, 128, 8, 8, 256, 1 << 20, None, None) == -1
 

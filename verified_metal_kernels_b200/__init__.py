@@ -17,3 +17,14 @@ def load_kernel(opname):
     """The op's `kernel` callable (imports torch and loads libvmk_b200.so)."""
     import importlib
     return importlib.import_module(KERNEL_MODULES[opname]).kernel
+
+
+def check_status(device=None):
+    """Synchronises `device` (default: the current CUDA device), reads and clears the status word the kernels OR
+    bits into, and raises VmkDeviceStatusError when it is non-zero (bit 0: a bounded device-side wait ran out and
+    the whole call's output is invalid; bit 1: an out-of-range index or length was clamped).  Calls made with host
+    tensors do this themselves; device-resident calls leave it to the caller, who knows when it synchronises."""
+    import torch
+    from . import _lib
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    _lib.raise_on_status(dev, "check_status")

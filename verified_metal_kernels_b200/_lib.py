@@ -45,9 +45,15 @@ SIGNATURES = {
     "vmk_lse_merge": (_i, [_vp] * 3 + [_i] * 3 + [_vp, _vp]),
     "vmk_prefix_partial": (_i, [_vp] * 6 + [_i] * 9 + [_vp] * 3 + [_vp, _sz, _vp, _vp]),
     "vmk_spec_partial": (_i, [_vp] * 4 + [_i] + [_i] * 8 + [_vp] * 3 + [_vp, _sz, _vp, _vp]),
+    "vmk_prefix_partial_packed": (_i, [_vp, _i] + [_vp] * 5 + [_i] * 10 + [_vp, _vp, _sz, _vp, _vp]),
+    "vmk_spec_partial_packed": (_i, [_vp] * 4 + [_i] * 11 + [_vp, _vp, _sz, _vp, _vp]),
+    "vmk_lse_merge_packed": (_i, [_vp] + [_i] * 4 + [_vp, _vp]),
+    "vmk_attn_set_tc": (_i, [_i]),
+    "vmk_dsa_set_indexer_variant": (_i, [_i]),
+    "vmk_dsa_set_attend_variant": (_i, [_i]),
 }
-# exported for experiments, not part of the documented ABI
-_EXTRA = {"vmk_dsa_set_indexer_variant": (_i, [_i]), "vmk_attn_set_tc": (_i, [_i]), "vmk_dsa_set_attend_variant": (_i, [_i])}
+# exported by debug builds only (-DVMK_MLA_TIMING, -DVMK_TC_TIMING, -DVMK_SEL_TIMING): device-side event traces
+DEBUG_EXPORTS = ("vmk_debug_mla_trace", "vmk_debug_tc_trace", "vmk_debug_sel_timing")
 
 _lib = None
 
@@ -58,6 +64,18 @@ class VmkError(RuntimeError):
         super().__init__(f"{what}: libvmk_b200 error {code} ({error_string(code)})")
 
 
+class VmkDeviceStatusError(VmkError):
+    """The device status word was non-zero after a call: bit 0 = a bounded device-side wait ran out (the CTA that
+    gave up wrote no result, so the WHOLE call's output is invalid), bit 1 = an index or length outside its tensor
+    was clamped."""
+
+    def __init__(self, status, what):
+        self.code, self.status = None, status
+        bits = [n for b, n in ((1, "a bounded device-side wait ran out: the output is invalid"),
+                               (2, "an out-of-range index or length was clamped")) if status & b]
+        RuntimeError.__init__(self, f"{what}: device status word {status} ({'; '.join(bits) or 'unknown bits'})")
+
+
 def lib():
     """The loaded library (loads it on first use; raises if it has not been built)."""
     global _lib
@@ -66,7 +84,7 @@ def lib():
             raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m verified_metal_kernels_b200.build` "
                                "(nvcc, sm_100a); there is no fallback path")
         L = ctypes.CDLL(LIB_PATH)
-        for name, (res, args) in {**SIGNATURES, **_EXTRA}.items():
+        for name, (res, args) in SIGNATURES.items():
             fn = getattr(L, name)
             fn.restype, fn.argtypes = res, args
         _lib = L
@@ -128,3 +146,22 @@ def read_status(device):
     if v:
         s.zero_()
     return v
+
+
+def raise_on_status(device, what):
+    """Synchronises, reads and clears the device status word; raises VmkDeviceStatusError when it is non-zero."""
+    v = read_status(device)
+    if v:
+        raise VmkDeviceStatusError(v, what)
+
+
+def finish(out, host, check, device, what):
+    """Common tail of the kernel modules.  A call made with host tensors returns a host tensor: the copy back
+    synchronises, so the status word is read there and a non-zero word raises.  A device-resident call returns
+    without synchronising; it checks only when asked (check=True), otherwise the caller reads the word with
+    check_status(device) once it has synchronised."""
+    if host:
+        out = out.cpu()
+    if host or check:
+        raise_on_status(device, what)
+    return out

@@ -31,9 +31,10 @@ struct CombineParams {
   int Hkv, G, Hq;
   __half* out;       // (outers, Hq, 128) fp16 or bf16, or null
   int bf16;
-  float* pm;         // when out is null: un-normalised merged partial per row
-  float* pl;
-  float* po;
+  float* pm;         // when out is null: un-normalised merged partial per row, row r at pm[r * ml_stride],
+  float* pl;         // pl[r * ml_stride] and po[r * o_stride + d]; (1, 128) for separate arrays, (130, 130) with
+  float* po;         // pl = pm + 1, po = pm + 2 for one packed record (m, l, o[128]) per row
+  int ml_stride, o_stride;
 };
 
 constexpr int kMaxParts = 640;     // upper bound of splits merged into one row (both sides together)
@@ -82,10 +83,10 @@ __global__ void __launch_bounds__(128) combine_kernel(const CombineParams p) {
   if (p.out != nullptr) {
     store16(&p.out[(size_t)row * kHD + d], acc / lsum, p.bf16);
   } else {
-    p.po[(size_t)row * kHD + d] = acc;
+    p.po[(size_t)row * p.o_stride + d] = acc;
     if (d == 0) {
-      p.pm[row] = M;
-      p.pl[row] = lsum;
+      p.pm[(size_t)row * p.ml_stride] = M;
+      p.pl[(size_t)row * p.ml_stride] = lsum;
     }
   }
 }
@@ -123,6 +124,26 @@ __global__ void __launch_bounds__(128) lse_merge_kernel(const float* __restrict_
     }
     store16(&out[(size_t)row * D + d], acc / lsum, bf16);
   }
+}
+
+// The same merge over packed records: rec (parts, rows, 130) with (m, l, o[128]) per row, the layout in which
+// partials arrive from other GPUs.  One CTA of 128 threads per row; thread d owns column d.
+__global__ void __launch_bounds__(128) lse_merge_packed_kernel(const float* __restrict__ rec, int parts, int rows,
+                                                                __half* __restrict__ out, int bf16) {
+  constexpr int kRec = kHD + 2;
+  const int row = blockIdx.x, d = threadIdx.x;
+  const float* r0 = rec + (size_t)row * kRec;
+  const size_t step = (size_t)rows * kRec;
+  float M = -INFINITY;
+  for (int s = 0; s < parts; ++s) M = fmaxf(M, r0[s * step]);
+  float acc = 0.f, lsum = 0.f;
+  for (int s = 0; s < parts; ++s) {
+    const float ms = r0[s * step];
+    const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+    acc += w * r0[s * step + 2 + d];
+    lsum += w * r0[s * step + 1];
+  }
+  store16(&out[(size_t)row * kHD + d], acc / lsum, bf16);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -234,7 +255,7 @@ static size_t place(RolePlan* r, int groups, size_t off, int cap) {
 
 struct PrefixPlan {
   RolePlan a, b;
-  bool has_b;
+  bool has_a, has_b;       // shared-prefix role (keys [key_lo, key_hi) not empty), private-suffix role
   size_t ws_bytes;
 };
 
@@ -242,6 +263,7 @@ static PrefixPlan plan_prefix(int N, int Hq, int Hkv, int P, int S, int key_lo, 
   PrefixPlan pl;
   const int G = Hq / Hkv;
   const int sms = sm_count();
+  pl.has_a = key_hi > key_lo;
   pl.has_b = with_suffix && S > 0;
   // Suffix role: one group per (request, kv head), G rows; aim for chunks of at least 128 keys.
   int target_b = 0;
@@ -256,10 +278,15 @@ static PrefixPlan plan_prefix(int N, int Hq, int Hkv, int P, int S, int key_lo, 
   } else {
     pl.b = RolePlan{};
   }
-  int target_a = 2 * sms - target_b;
-  if (target_a < sms) target_a = sms;
-  plan_role(&pl.a, Hkv, N * G, key_hi - key_lo, target_a, false);
-  size_t off = place(&pl.a, Hkv, 0, pl.a.tc ? tc_split_cap(Hkv * pl.a.row_tiles) : cdiv(2 * sms, Hkv * pl.a.row_tiles));
+  size_t off = 0;
+  if (pl.has_a) {
+    int target_a = 2 * sms - target_b;
+    if (target_a < sms) target_a = sms;
+    plan_role(&pl.a, Hkv, N * G, key_hi - key_lo, target_a, false);
+    off = place(&pl.a, Hkv, 0, pl.a.tc ? tc_split_cap(Hkv * pl.a.row_tiles) : cdiv(2 * sms, Hkv * pl.a.row_tiles));
+  } else {
+    pl.a = RolePlan{};
+  }
   if (pl.has_b) off = place(&pl.b, N * Hkv, off, pl.b.nsplit);
   pl.ws_bytes = align_up(off, 256);
   return pl;
@@ -327,6 +354,22 @@ static void fill_role(AttnRole* r, const RolePlan& pl, uint8_t* ws) {
   r->part_ml = reinterpret_cast<float*>(ws + pl.off_ml);
 }
 
+// Where a call that returns partials instead of the final output puts them: three separate arrays
+// (rows), (rows), (rows, 128), or one packed record of 130 floats (m, l, o[128]) per row, the form that
+// travels between GPUs in a single exchange.
+struct PartialOut {
+  float* pm;
+  float* pl;
+  float* po;
+  int ml_stride, o_stride;
+  bool any() const { return pm && pl && po; }
+};
+static PartialOut partial_none() { return PartialOut{nullptr, nullptr, nullptr, 1, kHD}; }
+static PartialOut partial_arrays(float* m, float* l, float* o) { return PartialOut{m, l, o, 1, kHD}; }
+static PartialOut partial_packed(float* rec) {
+  return PartialOut{rec, rec ? rec + 1 : nullptr, rec ? rec + 2 : nullptr, kHD + 2, kHD + 2};
+}
+
 // Pages of a paged cache: pool (pages, Hkv, page_size, D) addressed through table (groups, table_stride);
 // pages == 0 means the caches are contiguous.
 struct PageArgs {
@@ -357,15 +400,19 @@ static int role_tmaps(AttnRole* r, const void* k, const void* v, int keys, uint6
 
 // pg_a / pg_b: page tables of the shared prefix (one row) and of the private suffixes (one row per request);
 // with pages > 0, kp/vp and ks/vs all point at the page pool.
+// q_heads: heads per request in q's memory (the distance between two requests' rows, in heads); Hq when the
+// call covers every head, larger when q points at a slice of heads [h0, h0 + Hq) of a wider tensor.
 static int prefix_impl(const void* q, const void* kp, const void* vp, const void* ks, const void* vs,
                        const int32_t* slens, void* out, int N, int Hq, int Hkv, int D, int P, int S, int key_lo,
-                       int key_hi, int with_suffix, float* pm, float* plv, float* po, void* ws, size_t ws_bytes,
+                       int key_hi, int with_suffix, PartialOut po, void* ws, size_t ws_bytes,
                        int32_t* status, cudaStream_t stream, PageArgs pg_a = PageArgs{nullptr, 0, 0, 0},
-                       PageArgs pg_b = PageArgs{nullptr, 0, 0, 0}, int bf16 = 0) {
+                       PageArgs pg_b = PageArgs{nullptr, 0, 0, 0}, int bf16 = 0, int q_heads = 0) {
   if (N <= 0 || Hq <= 0 || Hkv <= 0 || P <= 0 || S < 0) return VMK_E_BADARG;
   if (D != kHD || Hq % Hkv != 0 || Hq / Hkv > 16) return VMK_E_UNSUPPORTED;
   if ((long long)N * (Hq / Hkv) > (1 << 24)) return VMK_E_UNSUPPORTED;
-  if (!q || !kp || !vp || (S > 0 && with_suffix && (!ks || !vs)) || (!out && !(pm && plv && po)) || !ws)
+  if (q_heads == 0) q_heads = Hq;
+  if (q_heads < Hq) return VMK_E_BADARG;
+  if (!q || (key_hi > key_lo && (!kp || !vp)) || (S > 0 && with_suffix && (!ks || !vs)) || (!out && !po.any()) || !ws)
     return VMK_E_BADARG;
   if (!aligned16(q) || !aligned16(kp) || !aligned16(vp) || !aligned16(ks) || !aligned16(vs) || !aligned16(out) ||
       (reinterpret_cast<uintptr_t>(ws) & 255))
@@ -373,31 +420,38 @@ static int prefix_impl(const void* q, const void* kp, const void* vp, const void
   if (key_lo < 0 || key_hi > P || key_lo > key_hi) return VMK_E_BADARG;
   const int G = Hq / Hkv;
   const PrefixPlan pl = plan_prefix(N, Hq, Hkv, P, S, key_lo, key_hi, with_suffix != 0);
+  if (!pl.has_a && !pl.has_b) return VMK_E_BADARG;      // no keys at all: every row would be empty
   if (ws_bytes < pl.ws_bytes) return VMK_E_WORKSPACE;
+  if (pl.a.nsplit + (pl.has_b ? pl.b.nsplit : 0) > kMaxParts) return VMK_E_UNSUPPORTED;   // before any launch
 
   AttnParams p;
   memset(&p, 0, sizeof(p));
   p.sc = kLog2e / sqrtf((float)D);
   p.status = status;
   p.bf16 = bf16;
-  int rc = role_tmaps(&p.a, kp, vp, P, Hkv, Hkv, pg_a);
-  if (rc) return rc;
-  p.a.q = static_cast<const __half*>(q);
-  p.a.n_groups = Hkv; p.a.Hkv = Hkv; p.a.G = G; p.a.Hq = Hq;
-  p.a.rows_outer = N;
-  p.a.klen = P; p.a.key_lo = key_lo; p.a.key_hi = key_hi;
-  p.a.mask_start = INT_MAX;
-  fill_role(&p.a, pl.a, static_cast<uint8_t*>(ws));
+  int rc = VMK_OK;
+  if (pl.has_a) {
+    rc = role_tmaps(&p.a, kp, vp, P, Hkv, Hkv, pg_a);
+    if (rc) return rc;
+    p.a.q = static_cast<const __half*>(q);
+    p.a.n_groups = Hkv; p.a.Hkv = Hkv; p.a.G = G; p.a.Hq = q_heads;
+    p.a.rows_outer = N;
+    p.a.klen = P; p.a.key_lo = key_lo; p.a.key_hi = key_hi;
+    p.a.mask_start = INT_MAX;
+    fill_role(&p.a, pl.a, static_cast<uint8_t*>(ws));
+  }
   if (pl.has_b) {
     rc = role_tmaps(&p.b, ks, vs, S, (uint64_t)N * Hkv, Hkv, pg_b);
     if (rc) return rc;
     p.b.q = static_cast<const __half*>(q);
     p.b.klens = slens;
-    p.b.n_groups = N * Hkv; p.b.Hkv = Hkv; p.b.G = G; p.b.Hq = Hq;
+    p.b.n_groups = N * Hkv; p.b.Hkv = Hkv; p.b.G = G; p.b.Hq = q_heads;
     p.b.rows_outer = 1;
     p.b.klen = S; p.b.key_lo = 0; p.b.key_hi = S;
     p.b.mask_start = INT_MAX;
     fill_role(&p.b, pl.b, static_cast<uint8_t*>(ws));
+  }
+  if (pl.has_a && pl.has_b) {
     if (pl.a.tc) {
       // shared prefix on the tensor-memory kernel, private suffixes on the warp-level kernel
       rc = launch_attn_tc(p, pl.a.n_cta, stream);
@@ -408,34 +462,45 @@ static int prefix_impl(const void* q, const void* kp, const void* vp, const void
     } else {
       rc = launch_attn<true>(p, pl.a.rt, pl.a.n_cta + pl.b.n_cta, stream);
     }
-  } else {
+  } else if (pl.has_a) {
     rc = pl.a.tc ? launch_attn_tc(p, pl.a.n_cta, stream) : launch_attn<false>(p, pl.a.rt, pl.a.n_cta, stream);
+  } else {
+    AttnParams ps = p;
+    ps.a = p.b;
+    rc = launch_attn<false>(ps, 1, pl.b.n_cta, stream);
   }
   if (rc) return rc;
 
   CombineParams c;
   memset(&c, 0, sizeof(c));
-  c.a = CombineSide{p.a.part_o, p.a.part_ml, pl.a.nsplit, pl.a.MP, N};
+  if (pl.has_a) c.a = CombineSide{p.a.part_o, p.a.part_ml, pl.a.nsplit, pl.a.MP, N};
   c.has_b = pl.has_b ? 1 : 0;
   if (pl.has_b) c.b = CombineSide{p.b.part_o, p.b.part_ml, pl.b.nsplit, pl.b.MP, 1};
   c.Hkv = Hkv; c.G = G; c.Hq = Hq;
   c.out = static_cast<__half*>(out);
   c.bf16 = bf16;
-  c.pm = pm; c.pl = plv; c.po = po;
+  c.pm = po.pm; c.pl = po.pl; c.po = po.po;
+  c.ml_stride = po.ml_stride; c.o_stride = po.o_stride;
   return launch_combine(c, N * Hq, stream);
 }
 
 static int spec_impl(const void* q, const void* k, const void* v, const uint32_t* bits, int bits_words, void* out,
-                     int B, int kd, int Hq, int Hkv, int D, int L, int key_lo, int key_hi, float* pm, float* plv,
-                     float* po, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream,
-                     PageArgs pg = PageArgs{nullptr, 0, 0, 0}, int bf16 = 0, const int32_t* klens = nullptr) {
+                     int B, int kd, int Hq, int Hkv, int D, int L, int key_lo, int key_hi, PartialOut po,
+                     void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream,
+                     PageArgs pg = PageArgs{nullptr, 0, 0, 0}, int bf16 = 0, const int32_t* klens = nullptr,
+                     int mask_start = -1) {
+  // mask_start: first position of k, v that is a draft (subject to `bits`); -1 = L - kd, the tensor ends with the
+  // drafts.  A value >= L says the tensor is a slice of a longer cache whose drafts lie elsewhere: nothing is masked.
+  if (mask_start < 0) mask_start = L - kd;
+  if (mask_start < L && mask_start != L - kd) return VMK_E_BADARG;
   // klens (B): per-request cache lengths.  Only without a draft mask (bits == nullptr, kd == 1: plain decode),
   // because the mask is anchored at the common length L.
   if (klens != nullptr && (bits != nullptr || kd != 1)) return VMK_E_UNSUPPORTED;
   if (B <= 0 || kd <= 0 || Hq <= 0 || Hkv <= 0 || L <= 0 || bits_words <= 0) return VMK_E_BADARG;
   if (D != kHD || Hq % Hkv != 0 || Hq / Hkv > 16) return VMK_E_UNSUPPORTED;
-  if (kd > L || kd > VMK_SPEC_MAX_DRAFTS || kd > 32 * bits_words || bits_words > kMaxMaskWords) return VMK_E_UNSUPPORTED;
-  if (!q || !k || !v || (!bits && !klens) || (!out && !(pm && plv && po)) || !ws) return VMK_E_BADARG;
+  if ((mask_start < L && kd > L) || kd > VMK_SPEC_MAX_DRAFTS || kd > 32 * bits_words || bits_words > kMaxMaskWords)
+    return VMK_E_UNSUPPORTED;
+  if (!q || !k || !v || (!bits && !klens) || (!out && !po.any()) || !ws) return VMK_E_BADARG;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || (reinterpret_cast<uintptr_t>(bits) & 3) ||
       (reinterpret_cast<uintptr_t>(ws) & 255))
     return VMK_E_BADARG;
@@ -443,6 +508,7 @@ static int spec_impl(const void* q, const void* k, const void* v, const uint32_t
   const int G = Hq / Hkv;
   const SpecPlan pl = plan_spec(B, kd, Hq, Hkv, key_lo, key_hi);
   if (ws_bytes < pl.ws_bytes) return VMK_E_WORKSPACE;
+  if (pl.a.nsplit > kMaxParts) return VMK_E_UNSUPPORTED;            // before any launch
 
   AttnParams p;
   memset(&p, 0, sizeof(p));
@@ -458,7 +524,7 @@ static int spec_impl(const void* q, const void* k, const void* v, const uint32_t
   p.a.n_groups = B * Hkv; p.a.Hkv = Hkv; p.a.G = G; p.a.Hq = Hq;
   p.a.rows_outer = kd;
   p.a.klen = L; p.a.key_lo = key_lo; p.a.key_hi = key_hi;
-  p.a.mask_start = bits ? L - kd : INT_MAX;
+  p.a.mask_start = (bits && mask_start < L) ? mask_start : INT_MAX;
   p.a.klens = klens;
   fill_role(&p.a, pl.a, static_cast<uint8_t*>(ws));
   p.a.direct = (out != nullptr && pl.a.nsplit == 1 && key_hi > key_lo) ? 1 : 0;
@@ -471,7 +537,8 @@ static int spec_impl(const void* q, const void* k, const void* v, const uint32_t
   c.Hkv = Hkv; c.G = G; c.Hq = Hq;
   c.out = static_cast<__half*>(out);
   c.bf16 = bf16;
-  c.pm = pm; c.pl = plv; c.po = po;
+  c.pm = po.pm; c.pl = po.pl; c.po = po.po;
+  c.ml_stride = po.ml_stride; c.o_stride = po.o_stride;
   return launch_combine(c, B * kd * Hq, stream);
 }
 
@@ -497,14 +564,16 @@ extern "C" VMK_API int vmk_attn_set_tc(int on) {
 
 extern "C" size_t vmk_prefix_workspace_bytes(int N, int Hq, int Hkv, int D, int P, int S) {
   if (N <= 0 || Hq <= 0 || Hkv <= 0 || P <= 0 || S < 0 || D != kHD || Hq % Hkv != 0) return 0;
-  return plan_prefix(N, Hq, Hkv, P, S, 0, P, true).ws_bytes;
+  const PrefixPlan pl = plan_prefix(N, Hq, Hkv, P, S, 0, P, true);
+  if (pl.a.nsplit + (pl.has_b ? pl.b.nsplit : 0) > kMaxParts) return 0;       // the call would refuse this shape
+  return pl.ws_bytes;
 }
 
 extern "C" int vmk_prefix_decode(const void* q, const void* kp, const void* vp, const void* ks, const void* vs,
                                  const int32_t* slens, void* out, int N, int Hq, int Hkv, int D, int P, int S,
                                  void* ws, size_t ws_bytes, int32_t* status, void* stream) {
   if (!out) return VMK_E_BADARG;
-  return prefix_impl(q, kp, vp, ks, vs, slens, out, N, Hq, Hkv, D, P, S, 0, P, 1, nullptr, nullptr, nullptr, ws,
+  return prefix_impl(q, kp, vp, ks, vs, slens, out, N, Hq, Hkv, D, P, S, 0, P, 1, partial_none(), ws,
                      ws_bytes, status, static_cast<cudaStream_t>(stream));
 }
 
@@ -514,8 +583,7 @@ extern "C" int vmk_prefix_decode_paged(const void* q, const void* k_pages, const
                                        int P, int S, int bf16, void* ws, size_t ws_bytes, int32_t* status, void* stream) {
   if (!out || pages <= 0 || !prefix_table || (S > 0 && (!suffix_table || !slens)) || (bf16 != 0 && bf16 != 1))
     return VMK_E_BADARG;
-  return prefix_impl(q, k_pages, v_pages, k_pages, v_pages, slens, out, N, Hq, Hkv, D, P, S, 0, P, 1, nullptr, nullptr,
-                     nullptr, ws, ws_bytes, status, static_cast<cudaStream_t>(stream),
+  return prefix_impl(q, k_pages, v_pages, k_pages, v_pages, slens, out, N, Hq, Hkv, D, P, S, 0, P, 1, partial_none(), ws, ws_bytes, status, static_cast<cudaStream_t>(stream),
                      PageArgs{prefix_table, pages, page_size, prefix_pages},
                      PageArgs{suffix_table, pages, page_size, suffix_stride}, bf16);
 }
@@ -525,20 +593,22 @@ extern "C" int vmk_prefix_partial(const void* q, const void* kp, const void* vp,
                                   int key_hi, int with_suffix, float* part_m, float* part_l, float* part_o, void* ws,
                                   size_t ws_bytes, int32_t* status, void* stream) {
   if (!part_m || !part_l || !part_o) return VMK_E_BADARG;
-  return prefix_impl(q, kp, vp, ks, vs, slens, nullptr, N, Hq, Hkv, D, P, S, key_lo, key_hi, with_suffix, part_m,
-                     part_l, part_o, ws, ws_bytes, status, static_cast<cudaStream_t>(stream));
+  return prefix_impl(q, kp, vp, ks, vs, slens, nullptr, N, Hq, Hkv, D, P, S, key_lo, key_hi, with_suffix,
+                     partial_arrays(part_m, part_l, part_o), ws, ws_bytes, status, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" size_t vmk_spec_workspace_bytes(int B, int kd, int Hq, int Hkv, int D, int L) {
   if (B <= 0 || kd <= 0 || Hq <= 0 || Hkv <= 0 || L <= 0 || D != kHD || Hq % Hkv != 0) return 0;
-  return plan_spec(B, kd, Hq, Hkv, 0, L).ws_bytes;
+  const SpecPlan pl = plan_spec(B, kd, Hq, Hkv, 0, L);
+  if (pl.a.nsplit > kMaxParts) return 0;                                       // the call would refuse this shape
+  return pl.ws_bytes;
 }
 
 extern "C" int vmk_spec_verify(const void* q, const void* k, const void* v, const uint32_t* bits, int bits_words,
                                void* out, int B, int kd, int Hq, int Hkv, int D, int L, void* ws, size_t ws_bytes,
                                int32_t* status, void* stream) {
   if (!out) return VMK_E_BADARG;
-  return spec_impl(q, k, v, bits, bits_words, out, B, kd, Hq, Hkv, D, L, 0, L, nullptr, nullptr, nullptr, ws,
+  return spec_impl(q, k, v, bits, bits_words, out, B, kd, Hq, Hkv, D, L, 0, L, partial_none(), ws,
                    ws_bytes, status, static_cast<cudaStream_t>(stream));
 }
 
@@ -547,7 +617,7 @@ extern "C" int vmk_spec_verify_paged(const void* q, const void* k_pages, const v
                                      void* out, int B, int kd, int Hq, int Hkv, int D, int L, int bf16, void* ws,
                                      size_t ws_bytes, int32_t* status, void* stream) {
   if (!out || pages <= 0 || (bf16 != 0 && bf16 != 1)) return VMK_E_BADARG;
-  return spec_impl(q, k_pages, v_pages, bits, bits_words, out, B, kd, Hq, Hkv, D, L, 0, L, nullptr, nullptr, nullptr, ws,
+  return spec_impl(q, k_pages, v_pages, bits, bits_words, out, B, kd, Hq, Hkv, D, L, 0, L, partial_none(), ws,
                    ws_bytes, status, static_cast<cudaStream_t>(stream), PageArgs{page_table, pages, page_size, table_stride},
                    bf16);
 }
@@ -557,8 +627,30 @@ extern "C" int vmk_spec_partial(const void* q, const void* k, const void* v, con
                                 float* part_l, float* part_o, void* ws, size_t ws_bytes, int32_t* status,
                                 void* stream) {
   if (!part_m || !part_l || !part_o) return VMK_E_BADARG;
-  return spec_impl(q, k, v, bits, bits_words, nullptr, B, kd, Hq, Hkv, D, L, key_lo, key_hi, part_m, part_l, part_o,
-                   ws, ws_bytes, status, static_cast<cudaStream_t>(stream));
+  return spec_impl(q, k, v, bits, bits_words, nullptr, B, kd, Hq, Hkv, D, L, key_lo, key_hi,
+                   partial_arrays(part_m, part_l, part_o), ws, ws_bytes, status, static_cast<cudaStream_t>(stream));
+}
+
+// ---- partials as packed records (m, l, o[128]) of 130 floats per row: what crosses between GPUs ------------
+extern "C" int vmk_prefix_partial_packed(const void* q, int q_heads, const void* kp, const void* vp, const void* ks,
+                                         const void* vs, const int32_t* slens, int N, int Hq, int Hkv, int D, int P,
+                                         int S, int key_lo, int key_hi, int with_suffix, int bf16, float* records,
+                                         void* ws, size_t ws_bytes, int32_t* status, void* stream) {
+  if (!records || (reinterpret_cast<uintptr_t>(records) & 7) || (bf16 != 0 && bf16 != 1) || q_heads < Hq)
+    return VMK_E_BADARG;
+  return prefix_impl(q, kp, vp, ks, vs, slens, nullptr, N, Hq, Hkv, D, P, S, key_lo, key_hi, with_suffix,
+                     partial_packed(records), ws, ws_bytes, status, static_cast<cudaStream_t>(stream),
+                     PageArgs{nullptr, 0, 0, 0}, PageArgs{nullptr, 0, 0, 0}, bf16, q_heads);
+}
+
+extern "C" int vmk_spec_partial_packed(const void* q, const void* k, const void* v, const uint32_t* bits,
+                                       int bits_words, int B, int kd, int Hq, int Hkv, int D, int L, int key_lo,
+                                       int key_hi, int mask_start, int bf16, float* records, void* ws,
+                                       size_t ws_bytes, int32_t* status, void* stream) {
+  if (!records || (reinterpret_cast<uintptr_t>(records) & 7) || (bf16 != 0 && bf16 != 1)) return VMK_E_BADARG;
+  return spec_impl(q, k, v, bits, bits_words, nullptr, B, kd, Hq, Hkv, D, L, key_lo, key_hi, partial_packed(records),
+                   ws, ws_bytes, status, static_cast<cudaStream_t>(stream), PageArgs{nullptr, 0, 0, 0}, bf16, nullptr,
+                   mask_start);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -598,7 +690,7 @@ extern "C" int vmk_spec_verify_noalloc(const void* q, const void* k, const void*
   void* ws = nullptr;
   const int rc = spec_scratch_address(&ws);
   if (rc) return rc;
-  return spec_impl(q, k, v, bits, bits_words, out, B, kd, Hq, Hkv, D, L, 0, L, nullptr, nullptr, nullptr, ws,
+  return spec_impl(q, k, v, bits, bits_words, out, B, kd, Hq, Hkv, D, L, 0, L, partial_none(), ws,
                    (size_t)VMK_SPEC_NOALLOC_SCRATCH_BYTES, status, static_cast<cudaStream_t>(stream));
 }
 
@@ -610,6 +702,15 @@ extern "C" int vmk_lse_merge(const float* m, const float* l, const float* o, int
   return check_launch(cudaGetLastError());
 }
 
+extern "C" int vmk_lse_merge_packed(const float* records, int parts, int rows, int D, int bf16, void* out,
+                                    void* stream) {
+  if (!records || !out || parts <= 0 || rows <= 0 || (bf16 != 0 && bf16 != 1)) return VMK_E_BADARG;
+  if (D != kHD) return VMK_E_UNSUPPORTED;
+  lse_merge_packed_kernel<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(records, parts, rows,
+                                                                                  static_cast<__half*>(out), bf16);
+  return check_launch(cudaGetLastError());
+}
+
 // ---- plain single-token decode: one query per request over its own cache of lens[b] keys ---------------------
 extern "C" size_t vmk_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int L) {
   return vmk_spec_workspace_bytes(B, 1, Hq, Hkv, D, L);
@@ -618,7 +719,7 @@ extern "C" size_t vmk_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int 
 extern "C" int vmk_decode(const void* q, const void* k, const void* v, const int32_t* lens, void* out, int B, int Hq,
                           int Hkv, int D, int L, int bf16, void* ws, size_t ws_bytes, int32_t* status, void* stream) {
   if (!out || !lens || (bf16 != 0 && bf16 != 1)) return VMK_E_BADARG;
-  return spec_impl(q, k, v, nullptr, 1, out, B, 1, Hq, Hkv, D, L, 0, L, nullptr, nullptr, nullptr, ws, ws_bytes, status,
+  return spec_impl(q, k, v, nullptr, 1, out, B, 1, Hq, Hkv, D, L, 0, L, partial_none(), ws, ws_bytes, status,
                    static_cast<cudaStream_t>(stream), PageArgs{nullptr, 0, 0, 0}, bf16, lens);
 }
 
@@ -627,7 +728,7 @@ extern "C" int vmk_decode_paged(const void* q, const void* k_pages, const void* 
                                 int Hq, int Hkv, int D, int L, int bf16, void* ws, size_t ws_bytes, int32_t* status,
                                 void* stream) {
   if (!out || !lens || pages <= 0 || (bf16 != 0 && bf16 != 1)) return VMK_E_BADARG;
-  return spec_impl(q, k_pages, v_pages, nullptr, 1, out, B, 1, Hq, Hkv, D, L, 0, L, nullptr, nullptr, nullptr, ws,
+  return spec_impl(q, k_pages, v_pages, nullptr, 1, out, B, 1, Hq, Hkv, D, L, 0, L, partial_none(), ws,
                    ws_bytes, status, static_cast<cudaStream_t>(stream),
                    PageArgs{page_table, pages, page_size, table_stride}, bf16, lens);
 }
@@ -637,7 +738,7 @@ extern "C" int vmk_prefix_decode_bf16(const void* q, const void* kp, const void*
                                       const int32_t* slens, void* out, int N, int Hq, int Hkv, int D, int P, int S,
                                       void* ws, size_t ws_bytes, int32_t* status, void* stream) {
   if (!out) return VMK_E_BADARG;
-  return prefix_impl(q, kp, vp, ks, vs, slens, out, N, Hq, Hkv, D, P, S, 0, P, 1, nullptr, nullptr, nullptr, ws,
+  return prefix_impl(q, kp, vp, ks, vs, slens, out, N, Hq, Hkv, D, P, S, 0, P, 1, partial_none(), ws,
                      ws_bytes, status, static_cast<cudaStream_t>(stream), PageArgs{nullptr, 0, 0, 0},
                      PageArgs{nullptr, 0, 0, 0}, 1);
 }
@@ -646,6 +747,6 @@ extern "C" int vmk_spec_verify_bf16(const void* q, const void* k, const void* v,
                                     void* out, int B, int kd, int Hq, int Hkv, int D, int L, void* ws, size_t ws_bytes,
                                     int32_t* status, void* stream) {
   if (!out) return VMK_E_BADARG;
-  return spec_impl(q, k, v, bits, bits_words, out, B, kd, Hq, Hkv, D, L, 0, L, nullptr, nullptr, nullptr, ws,
+  return spec_impl(q, k, v, bits, bits_words, out, B, kd, Hq, Hkv, D, L, 0, L, partial_none(), ws,
                    ws_bytes, status, static_cast<cudaStream_t>(stream), PageArgs{nullptr, 0, 0, 0}, 1);
 }

@@ -18,9 +18,10 @@ def _common(q, lens):
     return q.dtype, B
 
 
-def kernel(q, k, v, lens):
+def kernel(q, k, v, lens, check=False):
     """q (B,Hq,D), k/v (B,Hkv,L,D) fp16 or bf16, lens (B,) int32 with 1 <= lens[b] <= L -> (B,Hq,D).
-    Rows at or beyond lens[b] are never used.  Host tensors are copied in and the result returned on the host."""
+    Rows at or beyond lens[b] are never used.  Host tensors are copied in and the result returned on the host
+    (with the device status word checked; device-resident calls check it only with check=True)."""
     (q, k, v, lens), host = stage_in([q, k, v, lens])
     dt, B = _common(q, lens)
     Hq, D = q.shape[1], q.shape[2]
@@ -41,10 +42,10 @@ def kernel(q, k, v, lens):
                             1 if dt == torch.bfloat16 else 0, _lib.ptr(ws), ws.numel(),
                             _lib.ptr(_lib.status_word(dev)), stream.cuda_stream)
     _lib.check(rc, "vmk_decode")
-    return out.cpu() if host else out
+    return _lib.finish(out, host, check, dev, "vmk_decode")
 
 
-def kernel_paged(q, k_pages, v_pages, page_table, lens):
+def kernel_paged(q, k_pages, v_pages, page_table, lens, check=False):
     """The same over a paged cache: k_pages / v_pages (pages,Hkv,page_size,D), page_table (B,T) int32, lens (B,)
     int32 with lens[b] <= T * page_size; page_size a multiple of 64."""
     dt, B = _common(q, lens)
@@ -73,4 +74,4 @@ def kernel_paged(q, k_pages, v_pages, page_table, lens):
                                   1 if dt == torch.bfloat16 else 0, _lib.ptr(ws), ws.numel(),
                                   _lib.ptr(_lib.status_word(dev)), stream.cuda_stream)
     _lib.check(rc, "vmk_decode_paged")
-    return out
+    return _lib.finish(out, False, check, dev, "vmk_decode_paged")

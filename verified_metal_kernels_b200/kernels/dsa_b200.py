@@ -42,7 +42,7 @@ def _check(q, kv, iq, ik, w, lens):
     return B, L
 
 
-def kernel(q, kv, iq, ik, w, lens=None, return_selection=False):
+def kernel(q, kv, iq, ik, w, lens=None, return_selection=False, check=False):
     """q (B,128,576), kv (B,L,576), iq (B,64,128), ik (B,L,128) fp16 (or all four bf16), w (B,64) fp32, lens
     (B,) int32 or None -> (B,128,512) of the same 16-bit type.  With return_selection=True also returns (idx (B,2048) int32 ascending,
     cnt (B,) int32), the integer stage's result.  Inputs are not modified; host tensors are copied in
@@ -50,7 +50,11 @@ def kernel(q, kv, iq, ik, w, lens=None, return_selection=False):
 
     A page-locked host `kv` is NOT copied whole: the index keys go to the device, stages 1 and 2 run there,
     and stage 3 is fed by `gather`, which reads only the selected rows out of host memory (2048 of L rows per
-    request over the link).  The result is bit-identical to the all-on-device call."""
+    request over the link).  The result is bit-identical to the all-on-device call.
+
+    Device status: calls with host tensors synchronise and raise VmkDeviceStatusError when a kernel reported a
+    bounded wait that ran out (the output is then invalid) or a clamped index; device-resident calls do so only
+    with check=True (otherwise call check_status(device) after synchronising)."""
     if (HOST_CACHE_IN_PLACE and isinstance(kv, torch.Tensor) and not kv.is_cuda and kv.is_pinned() and kv.dim() == 3 and kv.shape[1] > TOPK
             and kv.dtype in (torch.float16, torch.bfloat16) and kv.is_contiguous()):
         return _kernel_host_cache(q, kv, iq, ik, w, lens, return_selection)
@@ -69,12 +73,11 @@ def kernel(q, kv, iq, ik, w, lens=None, return_selection=False):
                                 _lib.ptr(out), _lib.ptr(idx), _lib.ptr(cnt), B, L, _lib.ptr(ws), ws.numel(),
                                 _lib.ptr(_lib.status_word(dev)), stream.cuda_stream)
     _lib.check(rc, "vmk_dsa_decode")
-    if host:
-        out = out.cpu()
+    out = _lib.finish(out, host, check, dev, "vmk_dsa_decode")
     return (out, idx, cnt) if return_selection else out
 
 
-def kernel_paged(q, kv_pages, iq, ik_pages, w, page_table, lens, return_selection=False):
+def kernel_paged(q, kv_pages, iq, ik_pages, w, page_table, lens, return_selection=False, check=False):
     """`dsa` over a paged cache: kv_pages (pages,page_size,576) and ik_pages (pages,page_size,128) are pools paged
     alike, page_table (B,T) int32 maps positions [i * page_size, (i + 1) * page_size) of request b to page
     page_table[b, i]; lens (B,) int32 are the cache lengths (required); page_size a multiple of 128 and
@@ -110,6 +113,7 @@ def kernel_paged(q, kv_pages, iq, ik_pages, w, page_table, lens, return_selectio
                                       _lib.ptr(idx), _lib.ptr(cnt), B, L, 1 if dt == torch.bfloat16 else 0,
                                       _lib.ptr(ws), ws.numel(), _lib.ptr(_lib.status_word(dev)), stream.cuda_stream)
     _lib.check(rc, "vmk_dsa_decode_paged")
+    out = _lib.finish(out, False, check, dev, "vmk_dsa_decode_paged")
     return (out, idx, cnt) if return_selection else out
 
 
@@ -123,7 +127,7 @@ def _kernel_host_cache(q, kv, iq, ik, w, lens, return_selection):
     scores, hist = indexer_hist(iq, ik, w, lens)
     idx, cnt = select(scores, lens, hist)
     kv_sel, idx_sel = gather(kv, idx, cnt)
-    out = attend(q, kv_sel, idx_sel, cnt).cpu()
+    out = _lib.finish(attend(q, kv_sel, idx_sel, cnt), True, True, q.device, "dsa (host-resident cache)")
     return (out, idx, cnt) if return_selection else out
 
 

@@ -9,13 +9,18 @@ from .. import _lib
 from ._common import need, stage_in
 
 
-def kernel(q, kp, vp, ks, vs, slens=None):
+def kernel(q, kp, vp, ks, vs, slens=None, check=False):
     """q (N,Hq,D), kp/vp (Hkv,P,D), ks/vs (N,Hkv,S,D) fp16 (or all bf16) -> (N,Hq,D) of the same type on the
     inputs' device.
 
     `slens` (N,) int32, optional: true suffix length per request.  Inputs are not modified.  Host (CPU)
     tensors are accepted: they are copied to the current CUDA device first and the result is returned
-    on the host, which is the end-to-end path measured by bench.py."""
+    on the host, which is the end-to-end path measured by bench.py.
+
+    Device status: a call with host tensors synchronises anyway and raises VmkDeviceStatusError if a kernel
+    reported a bounded wait that ran out (the output is then invalid) or a clamped index.  A device-resident call
+    returns without synchronising; pass check=True to synchronise and check here, or call
+    verified_metal_kernels_b200.check_status(device) after synchronising."""
     (q, kp, vp, ks, vs, slens), host = stage_in([q, kp, vp, ks, vs, slens])
     if not isinstance(q, torch.Tensor) or q.dtype not in (torch.float16, torch.bfloat16):
         raise TypeError("q: expected a float16 or bfloat16 tensor")
@@ -44,10 +49,10 @@ def kernel(q, kp, vp, ks, vs, slens=None):
                                  _lib.ptr(vs) if S > 0 else None, _lib.ptr(slens), _lib.ptr(out), N, Hq, Hkv, D, P, S,
                                  _lib.ptr(ws), ws.numel(), _lib.ptr(_lib.status_word(dev)), stream.cuda_stream)
     _lib.check(rc, "vmk_prefix_decode")
-    return out.cpu() if host else out
+    return _lib.finish(out, host, check, dev, "vmk_prefix_decode")
 
 
-def kernel_paged(q, k_pages, v_pages, prefix_table, P, suffix_table=None, slens=None):
+def kernel_paged(q, k_pages, v_pages, prefix_table, P, suffix_table=None, slens=None, check=False):
     """`prefix` over a paged cache: k_pages / v_pages (pages, Hkv, page_size, D) fp16 are one pool; the shared
     prefix is P keys in pages prefix_table (T_p,) int32; request n's private suffix is slens[n] keys in pages
     suffix_table[n] ((N, T_s) int32).  page_size a multiple of 64.  Returns (N,Hq,D) fp16, equal to kernel() on
@@ -87,4 +92,4 @@ def kernel_paged(q, k_pages, v_pages, prefix_table, P, suffix_table=None, slens=
                                          _lib.ptr(ws), ws.numel(),
                                          _lib.ptr(_lib.status_word(dev)), stream.cuda_stream)
     _lib.check(rc, "vmk_prefix_decode_paged")
-    return out
+    return _lib.finish(out, False, check, dev, "vmk_prefix_decode_paged")

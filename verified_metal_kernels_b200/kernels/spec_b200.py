@@ -8,11 +8,12 @@ from .. import _lib
 from ._common import need, stage_in
 
 
-def kernel(q, k, v, bits):
+def kernel(q, k, v, bits, check=False):
     """q (B,kd,Hq,D), k/v (B,Hkv,L,D) fp16 (or all bf16), bits (B,kd) int32 -- or (B,kd,W) int32 words for kd > 32 --
     -> (B,kd,Hq,D) fp16.  The drafts are the last kd cache positions; bit j of bits[b,i] set means
     draft i attends draft j.  Inputs are not modified; host tensors are copied in and the result is
-    returned on the host."""
+    returned on the host (that path synchronises and raises VmkDeviceStatusError on a non-zero device status
+    word; a device-resident call checks only with check=True, else use check_status(device) after synchronising)."""
     (q, k, v, bits), host = stage_in([q, k, v, bits])
     if not isinstance(q, torch.Tensor) or q.dtype not in (torch.float16, torch.bfloat16):
         raise TypeError("q: expected a float16 or bfloat16 tensor")
@@ -45,10 +46,10 @@ def kernel(q, k, v, bits):
                                Hkv, D, Lk, _lib.ptr(ws), ws.numel(), _lib.ptr(_lib.status_word(dev)),
                                stream.cuda_stream)
     _lib.check(rc, "vmk_spec_verify")
-    return out.cpu() if host else out
+    return _lib.finish(out, host, check, dev, "vmk_spec_verify")
 
 
-def kernel_paged(q, k_pages, v_pages, page_table, L, bits):
+def kernel_paged(q, k_pages, v_pages, page_table, L, bits, check=False):
     """`spec` over a paged cache: k_pages / v_pages (pages, Hkv, page_size, D) fp16 are one pool for every
     request, page_table (B, T) int32 maps keys [i * page_size, (i + 1) * page_size) of request b to page
     page_table[b, i]; L is the (common) cache length, T * page_size >= L, page_size a multiple of 64.
@@ -85,4 +86,4 @@ def kernel_paged(q, k_pages, v_pages, page_table, L, bits):
                                        1 if dt == torch.bfloat16 else 0,
                                        _lib.ptr(ws), ws.numel(), _lib.ptr(_lib.status_word(dev)), stream.cuda_stream)
     _lib.check(rc, "vmk_spec_verify_paged")
-    return out
+    return _lib.finish(out, False, check, dev, "vmk_spec_verify_paged")
