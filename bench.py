@@ -1,24 +1,28 @@
 """Benchmark of the B200 decode kernels on the multi-GPU sweep workload.
 
-    python bench.py                                   # 1 GPU, dsa B=128 L=131072 (+ prefix / spec side lines)
+    python bench.py                                   # 1 GPU, dsa B=128 L=131072 (+ per-op lines with opponents)
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port P \
-        bench.py --gpus 8 --steps 20 --warmup 3       # every rank its own batch of 128 requests (weak scaling)
-    ... bench.py --gpus 8 --scaling strong            # ONE batch of 128 requests cut over the ranks
+        bench.py --gpus 8 --steps 20 --warmup 3       # ONE batch of 128 requests cut over the ranks (strong scaling)
+    ... bench.py --gpus 8 --scaling weak              # headline = every rank its own batch of 128 instead
     python bench.py --impl reference                  # the float64 NumPy truth timed on the host cores
 
 A step is one pass of the op over the whole batch.  The headline op is `dsa` on the sweep configuration
 (batch 128, cache 131072): rows/s where a row is one request's complete output.  Requests are independent
-units: they are spread over the ranks with no collective on the data path.  By default every rank holds
-the configuration's 128 requests (weak scaling: the global batch is 128 x N); `--scaling strong` cuts one
-batch of 128 over the ranks instead (16 per GPU at N=8, where the fixed latencies of the three stages weigh
-more).
-Inputs are synthetic (seeded N(0,1) rounded to fp16, head weights N(0,1)/sqrt(64*128), as the op's
-generator draws them) and far larger than the 126 MB L2, so no flush is needed between steps.
+units: they are spread over the ranks with no collective on the data path.  On more than one GPU the headline is
+the STRONG scaling of that one batch (16 requests per GPU at N=8, where the fixed latencies of the three stages
+weigh more); the line's `weak` object carries the same measurement with 128 requests per rank.  The `ops` object
+holds the other configurations: on one GPU every configuration of the op list with its library opponents timed
+in the same shuffled rounds; on N GPUs the `prefix` sweep under hybrid sharding (suffixes by request, the shared
+prefix by kv head, one all-to-all of packed partials) and the speculative tree (by batch element, beyond four
+ranks with every cache split in two).
+Inputs are synthetic (seeded N(0,1) rounded to fp16, head weights N(0,1)/sqrt(64*128), as the op's generator
+draws them).  The dsa inputs are far larger than the 126 MB L2; every other timing flushes L2 first.
 
-Rank 0 prints one JSON line.  `value` is timed with inputs resident in HBM; `e2e` is timed through the
-kernel module's public call with pinned HOST tensors (host->device copies and the device->host read of
-the result inside the timed region); `roofline` is for the dominant kernel (the indexer) from CUDA
-events inside this run; `cpu_baseline` is the float64 oracle on a bounded sample on the host cores."""
+Before any timing every rank checks one of its own requests against the float64 oracle and its inputs for
+modification afterwards (`output_ok`).  Rank 0 prints one JSON line.  `value` is timed with inputs resident in
+HBM; `e2e` through the kernel module's public call with pinned HOST tensors (copies inside the timed region);
+`roofline` is for the dominant kernel (the indexer) from CUDA events inside this run; `cpu_baseline` is the
+float64 oracle on a bounded sample on the host cores.  A non-zero device status word makes the run exit 1."""
 import argparse
 import json
 import os
@@ -37,10 +41,12 @@ if ROOT not in sys.path:
 METRIC = "dsa decode rows/s (batch 128, cache 131072)"
 UNIT = "rows/s"
 DSA = dict(B=128, L=131072)
-PREFIX = dict(N=256, P=32768, S=2048)
-SPEC = dict(B=4, L=32768, k=64)
+PREFIX = dict(N=256, P=32768, S=2048, ragged=True)
+SPEC = dict(B=4, L=32768, k=64, max_depth=8)
 FALLBACK_HBM_GBS = 6650.0
+NOMINAL_HBM_GBS = 8000.0           # the figure the metric is quoted against
 E2E_MAX = 32
+DELAY_BYTES = 1 << 30              # a 1 GiB fill ahead of each multi-GPU side step: flushes L2 and lets the host run ahead
 
 
 def peaks():
@@ -143,22 +149,8 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------------ inputs
 def dsa_inputs(B, L, device, seed):
     """Synthetic dsa inputs on the device with the generator's distributions (chunked to bound memory)."""
-    import torch
-    g = torch.Generator(device=device)
-    g.manual_seed(seed)
-
-    def randn16(*shape):
-        out = torch.empty(*shape, dtype=torch.float16, device=device)
-        flat = out.view(-1)
-        step = 1 << 28
-        for i in range(0, flat.numel(), step):
-            n = min(step, flat.numel() - i)
-            flat[i:i + n] = torch.randn(n, generator=g, device=device, dtype=torch.float32).half()
-        return out
-
-    return dict(q=randn16(B, 128, 576), kv=randn16(B, L, 576), iq=randn16(B, 64, 128), ik=randn16(B, L, 128),
-                w=torch.randn(B, 64, generator=g, device=device, dtype=torch.float32) * (64 ** -0.5 * 128 ** -0.5),
-                lens=None)
+    from verified_metal_kernels_b200 import abbench
+    return abbench.device_inputs("dsa", dict(B=B, L=L), seed, device)
 
 
 def timed_steps(fn, steps, warmup, dist, torch, sampler=None):
@@ -217,8 +209,6 @@ def stage_times(inp, steps, torch):
     B, Lk = inp["ik"].shape[0], inp["ik"].shape[1]
     st = torch.cuda.current_stream().cuda_stream
     status = _lib.status_word(inp["ik"].device)
-    out["indexer_ms"] = avg(lambda: L.vmk_dsa_indexer(inp["iq"].data_ptr(), inp["ik"].data_ptr(), inp["w"].data_ptr(),
-                                                      None, scores.data_ptr(), B, Lk, status.data_ptr(), st))
     hist = torch.empty(B, 2048, dtype=torch.int32, device=scores.device)
     out["indexer_ms"] = avg(lambda: L.vmk_dsa_indexer_hist(inp["iq"].data_ptr(), inp["ik"].data_ptr(),
                                                            inp["w"].data_ptr(), None, scores.data_ptr(), hist.data_ptr(),
@@ -227,11 +217,7 @@ def stage_times(inp, steps, torch):
                                                          cnt.data_ptr(), B, Lk, st))
     out["attend_ms"] = avg(lambda: dsa_b200.attend(inp["q"], inp["kv"], idx, cnt))
     # stage 1 on fp8 index queries and keys (a different input format, reported beside the fp16 stage)
-    iq8, iqs = dsa_b200.quantize_e4m3(inp["iq"])
-    ik8 = torch.empty(B, Lk, 128, dtype=torch.uint8, device=scores.device)
-    iks = torch.empty(B, Lk, dtype=torch.float32, device=scores.device)
-    for b0 in range(0, B, 8):                              # in pieces: the float copy of ik is 4 x its size
-        ik8[b0:b0 + 8], iks[b0:b0 + 8] = dsa_b200.quantize_e4m3(inp["ik"][b0:b0 + 8])
+    iq8, iqs, ik8, iks = fp8_index(inp, torch)
     out["indexer_fp8_ms"] = avg(lambda: L.vmk_dsa_indexer_hist_fp8(iq8.data_ptr(), iqs.data_ptr(), ik8.data_ptr(),
                                                                    iks.data_ptr(), inp["w"].data_ptr(), None,
                                                                    scores.data_ptr(), hist.data_ptr(), B, Lk,
@@ -239,51 +225,123 @@ def stage_times(inp, steps, torch):
     return out
 
 
+def fp8_index(inp, torch):
+    """The index queries and keys of `inp` quantised to e4m3 bytes with positive fp32 scales (per head / per position)."""
+    from verified_metal_kernels_b200.kernels import dsa_b200
+    B, Lk = inp["ik"].shape[0], inp["ik"].shape[1]
+    iq8, iqs = dsa_b200.quantize_e4m3(inp["iq"])
+    ik8 = torch.empty(B, Lk, 128, dtype=torch.uint8, device=inp["ik"].device)
+    iks = torch.empty(B, Lk, dtype=torch.float32, device=inp["ik"].device)
+    for b0 in range(0, B, 8):                              # in pieces: the float copy of ik is 4 x its size
+        ik8[b0:b0 + 8], iks[b0:b0 + 8] = dsa_b200.quantize_e4m3(inp["ik"][b0:b0 + 8])
+    return iq8, iqs, ik8, iks
+
+
+# ------------------------------------------------------------------------------------------------ output checks
+def _host(t):
+    return None if t is None else t.detach().cpu().numpy()
+
+
+def check_dsa_request(inp, out, idx, cnt, b):
+    """Request b of a dsa call against the float64 oracle: the selected set (exact wherever the float64 scores
+    are separated by more than fp32 accumulation error) and the output (normalised max error <= 1e-2)."""
+    from oracle import judge, ref64
+    one = {k: _host(v[b:b + 1]) for k, v in inp.items() if v is not None}
+    L = one["ik"].shape[1]
+    s64 = ref64.dsa_scores64(one["iq"], one["ik"], one["w"])
+    sel_rep = judge.select_check(_host(idx[b]), int(cnt[b]), s64[0], L)
+    sel = [_host(idx[b, :int(cnt[b])]).astype(np.int64)]
+    truth = ref64.dsa_ref64(one["q"], one["kv"], one["iq"], one["ik"], one["w"], None, sel=sel)
+    rep = judge.judge_l2(_host(out[b:b + 1].float()), truth, half=True)
+    return bool(sel_rep["ok"] and rep["ok"]), dict(selection_exact=sel_rep.get("exact"), err_max=rep.get("err_max"))
+
+
+def all_ranks_ok(ok, dist, torch):
+    if dist is None:
+        return bool(ok)
+    t = torch.tensor([1 if ok else 0], device="cuda", dtype=torch.int32)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return bool(int(t.item()))
+
+
+# ------------------------------------------------------------------------------------------------ one-GPU op lines
+def ab_line(opname, name, shape, torch, rounds, mask="tree", opponents=True, std_name=None):
+    """One configuration on one GPU through the interleaved A/B method (verified_metal_kernels_b200/abbench.py):
+    per-layer time of a 16-layer CUDA-graph chain with L2 flushed, the library opponents in the same shuffled
+    rounds, plus the time of one plain kernel(...) call (host launch overhead included)."""
+    from verified_metal_kernels_b200 import abbench, load_kernel, ops
+    op = ops.load_op(opname)
+    fn = load_kernel(opname)
+    flush = torch.empty(abbench.L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda")
+    row = abbench.bench_config(opname, shape, fn, rounds=rounds, mask=mask, opponents=opponents, flush=flush,
+                               std_name=std_name)
+    inp = abbench.device_inputs(opname, shape, 0, mask=mask)
+    sl = _host(inp.get("slens")) if opname == "prefix" and inp.get("slens") is not None else None
+    nbytes = op.algorithmic_bytes(shape, sl) if opname == "prefix" else op.algorithmic_bytes(shape)
+    keys = ops.KEYS[opname]
+    times = []
+    for i in range(8):
+        flush.fill_(i & 0xff)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn(**{k: inp.get(k) for k in keys})
+        b.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            times.append(a.elapsed_time(b))
+    ms_call = statistics.median(times)
+    if opname == "prefix":
+        flops = 4.0 * shape["N"] * 32 * 128 * (shape["P"] + (float(sl.mean()) if sl is not None else shape["S"]))
+    elif opname == "spec":
+        flops = 4.0 * shape["B"] * shape["k"] * 32 * 128 * shape["L"]
+    else:
+        flops = 2.0 * 64 * 128 * shape["L"] * shape["B"] + 2.0 * 128 * (576 + 512) * min(2048, shape["L"]) * shape["B"]
+    peak, kind = peaks()
+    ms = row["median_us"] * 1e-3
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    line = dict(workload=name, algorithmic_mb=nbytes / 1e6, peak=f"of {kind}", l2="flushed before every timed chain",
+                timing=row["timing"], ms=ms, p10_ms=row["p10_us"] * 1e-3, p90_ms=row["p90_us"] * 1e-3,
+                rows_per_s=op.rows(shape) / (ms * 1e-3), hbm_gbs=gbs, hbm_frac=gbs / peak,
+                hbm_frac_of_8tbs=gbs / NOMINAL_HBM_GBS, tflops=flops / (ms * 1e-3) / 1e12,
+                ms_single_call=ms_call, single_call_hbm_frac=nbytes / (ms_call * 1e-3) / 1e9 / peak,
+                output_ok=bool(row["output_ok"] and row["inputs_unmodified"]), n_distinct=row["n_distinct"])
+    for k in ("vs_torch", "opponents_us", "strongest_ref", "speedup", "skipped", "timed_eagerly"):
+        if k in row:
+            line[k] = row[k]
+    return line, row
+
+
 def side_line(config, torch, steps):
-    """rows/s and HBM fraction of one named configuration on one GPU, L2 flushed between iterations.
-    Configurations: prefix_small, spec_chain, spec_tree, spec_tree_paged, dsa_small (the single-GPU ones),
-    prefix_sweep and decode (the extension op)."""
-    from verified_metal_kernels_b200 import load_kernel, ops
+    """rows/s and HBM fraction of the two extension configurations on one GPU (`decode`, `spec_tree_paged`), and of
+    any named configuration for profiling (`--side-only`): L2 flushed between iterations, one call and a chain."""
+    from verified_metal_kernels_b200 import abbench, ops
     g = torch.Generator(device="cuda")
     g.manual_seed(1)
     r16 = lambda *s: torch.randn(*s, generator=g, device="cuda", dtype=torch.float32).half()
-    if config in ("prefix_small", "prefix_sweep"):
-        opname = "prefix"
-        op = ops.load_op(opname)
-        shape = dict(N=8, P=4096, S=256) if config == "prefix_small" else PREFIX
-        N, P, S = shape["N"], shape["P"], shape["S"]
-        inp = dict(q=r16(N, 32, 128), kp=r16(8, P, 128), vp=r16(8, P, 128), ks=r16(N, 8, S, 128), vs=r16(N, 8, S, 128))
-        sl = None
-        if config == "prefix_sweep":
-            inp["slens"] = torch.randint(0, S + 1, (N,), generator=g, device="cuda", dtype=torch.int32)
-            sl = inp["slens"].cpu().numpy()
-        nbytes = op.algorithmic_bytes(shape, sl)
-        rows = N
-        name = f"prefix N={N} P={P} " + (f"S~U[0,{S}]" if sl is not None else f"S={S}")
-        flops = 4.0 * N * 32 * 128 * (P + (float(sl.mean()) if sl is not None else S))
-    elif config in ("spec_chain", "spec_tree", "spec_tree_paged"):
-        opname = "spec"
-        op = ops.load_op(opname)
-        shape = dict(B=1, L=8192, k=8) if config == "spec_chain" else SPEC
+    named = dict(prefix_small=("prefix", dict(N=8, P=4096, S=256), "tree"), prefix_sweep=("prefix", PREFIX, "tree"),
+                 spec_chain=("spec", dict(B=1, L=8192, k=8), "chain"), spec_tree=("spec", SPEC, "tree"),
+                 dsa_small=("dsa", dict(B=8, L=32768), "tree"))
+    if config in named:
+        opname, shape, mask = named[config]
+        return ab_line(opname, config, shape, torch, max(steps, 3), mask=mask, opponents=False)[0]
+    if config == "spec_tree_paged":
+        from verified_metal_kernels_b200.kernels import spec_b200
+        op = ops.load_op("spec")
+        shape = SPEC
         B, L, kd = shape["B"], shape["L"], shape["k"]
-        rng = np.random.default_rng(0)
-        masks = [op.chain_bits(kd) if config == "spec_chain" else op.tree_bits(kd, rng, 8) for _ in range(B)]
-        inp = dict(q=r16(B, kd, 32, 128), k=r16(B, 8, L, 128), v=r16(B, 8, L, 128),
-                   bits=torch.from_numpy(op.pack_bits(masks, kd)).cuda())
-        nbytes = op.algorithmic_bytes(shape)
-        rows = B * kd
-        name = f"spec {'chain' if config == 'spec_chain' else 'tree depth<=8'} B={B} k={kd} L={L}"
+        base = abbench.device_inputs("spec", shape, 0)
+        # the same cache as a shuffled pool of 64-key pages (the smallest page the kernels take)
+        page = 64
+        T = L // page
+        perm = torch.randperm(B * T + 7, generator=g, device="cuda")[:B * T].to(torch.int32).reshape(B, T)
+        inp = dict(q=base["q"], k_pages=r16(B * T + 7, 8, page, 128), v_pages=r16(B * T + 7, 8, page, 128),
+                   page_table=perm.contiguous(), L=L, bits=base["bits"])
+        nbytes, rows, fn, opname = op.algorithmic_bytes(shape), B * kd, spec_b200.kernel_paged, "spec"
+        name = f"spec tree depth<=8 B={B} k={kd} L={L}, paged cache (page {page})"
         flops = 4.0 * B * kd * 32 * 128 * L
-        if config == "spec_tree_paged":
-            # the same cache as a shuffled pool of 64-key pages (the smallest page the kernels take)
-            page = 64
-            T = L // page
-            perm = torch.randperm(B * T + 7, generator=g, device="cuda")[:B * T].to(torch.int32).reshape(B, T)
-            inp = dict(q=inp["q"], k_pages=r16(B * T + 7, 8, page, 128), v_pages=r16(B * T + 7, 8, page, 128),
-                       page_table=perm.contiguous(), L=L, bits=inp["bits"])
-            name += f", paged cache (page {page})"
     elif config in ("decode", "decode_small"):
         # plain single-token decode (extension op): 64 requests with caches of 16k..32k keys
+        from verified_metal_kernels_b200.kernels import decode_b200
         from verified_metal_kernels_b200.ops import decode as op
         opname = "decode"
         shape = op.CONFIG_BENCH if config == "decode" else dict(B=8, L=16384)     # the small one is for profiling
@@ -291,24 +349,10 @@ def side_line(config, torch, steps):
         lens = torch.randint(L // 2, L + 1, (B,), generator=g, device="cuda", dtype=torch.int32)
         inp = dict(q=r16(B, 32, 128), k=r16(B, 8, L, 128), v=r16(B, 8, L, 128), lens=lens)
         nbytes = op.algorithmic_bytes(shape, lens.cpu().numpy())
-        rows, name = B, f"decode B={B} L~U[{L // 2},{L}]"
+        rows, name, fn = B, f"decode B={B} L~U[{L // 2},{L}]", decode_b200.kernel
         flops = 4.0 * 32 * 128 * float(lens.sum())
     else:
-        opname = "dsa"
-        op = ops.load_op(opname)
-        shape = dict(B=8, L=32768)
-        inp = dsa_inputs(shape["B"], shape["L"], "cuda", seed=5)
-        nbytes = op.algorithmic_bytes(shape)
-        rows, name = shape["B"], "dsa B=8 L=32768"
-        flops = 2.0 * 64 * 128 * shape["L"] * shape["B"] + 2.0 * 128 * (576 + 512) * 2048 * shape["B"]
-    if opname == "decode":
-        from verified_metal_kernels_b200.kernels import decode_b200
-        fn = decode_b200.kernel
-    else:
-        fn = load_kernel(opname)
-    if config == "spec_tree_paged":
-        from verified_metal_kernels_b200.kernels import spec_b200
-        fn = spec_b200.kernel_paged
+        raise SystemExit(f"unknown configuration {config!r}")
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     times = []
     for i in range(steps + 3):
@@ -321,12 +365,9 @@ def side_line(config, torch, steps):
         if i >= 3:
             times.append(a.elapsed_time(b))
     ms_call = statistics.median(times)
-    # The reference's timing method (bench.py:61-76 there): a chain of 16 "layers" on distinct input sets, each
-    # layer's query being the previous layer's output, here captured once in a CUDA graph and replayed after an
-    # L2 flush, so that host launch overhead is off the clock.
     ms = None
     try:
-        ms = chain_time(opname, fn, inp, flush, torch, steps)
+        ms = chain_time(fn, inp, flush, torch, steps)
     except Exception as e:                        # a capture problem must not lose the per-call number
         chain_err = f"{type(e).__name__}: {str(e)[:200]}"
     peak, kind = peaks()
@@ -338,11 +379,12 @@ def side_line(config, torch, steps):
     else:
         line["timing"] = "per layer of a 16-layer chain (output -> next query) replayed as a CUDA graph"
     line.update(rows_per_s=rows / (ms * 1e-3), ms=ms, hbm_gbs=nbytes / (ms * 1e-3) / 1e9,
-                hbm_frac=nbytes / (ms * 1e-3) / 1e9 / peak, tflops=flops / (ms * 1e-3) / 1e12)
+                hbm_frac=nbytes / (ms * 1e-3) / 1e9 / peak, hbm_frac_of_8tbs=nbytes / (ms * 1e-3) / 1e9 / NOMINAL_HBM_GBS,
+                tflops=flops / (ms * 1e-3) / 1e12)
     return line
 
 
-def chain_time(opname, fn, inp, flush, torch, rounds, layers=16):
+def chain_time(fn, inp, flush, torch, rounds, layers=16):
     """Median time per layer of a `layers`-long chain over up to 8 distinct copies of the inputs (within
     1.5 GiB), replayed from a CUDA graph; the L2 is flushed before every replay."""
     per_set = sum(v.numel() * v.element_size() for v in inp.values() if isinstance(v, torch.Tensor))
@@ -353,7 +395,7 @@ def chain_time(opname, fn, inp, flush, torch, rounds, layers=16):
     for _ in range(1, n_distinct):
         cp = {}
         for k, v in inp.items():
-            if not isinstance(v, torch.Tensor) or not v.is_floating_point() or k in ("w",):
+            if not isinstance(v, torch.Tensor) or not v.is_floating_point():
                 cp[k] = v
             else:
                 cp[k] = torch.randn(v.shape, generator=g, device="cuda", dtype=torch.float32).to(v.dtype)
@@ -364,8 +406,7 @@ def chain_time(opname, fn, inp, flush, torch, rounds, layers=16):
         for i in range(layers):
             kw = dict(sets[i % n_distinct])
             kw["q"] = q
-            out = fn(**kw)
-            q = torch.cat([out, kw["q"][..., 512:]], dim=-1) if opname == "dsa" else out
+            q = fn(**kw)
         return q
 
     run_chain()
@@ -386,9 +427,236 @@ def chain_time(opname, fn, inp, flush, torch, rounds, layers=16):
     return statistics.median(times)
 
 
+def single_gpu_ops(torch, rounds):
+    """Every configuration of the op list on one GPU: the five named ones (C1-C4 and the prefix sweep), the two
+    extension lines, and the reference's own benchmark shapes (its ops/<op>.py: BENCH_SHAPES) with the geometric
+    mean of the speed-up over the strongest library opponent per op, as the reference reports it."""
+    from verified_metal_kernels_b200 import abbench, ops
+    out, saved = {}, {"prefix": [], "spec": [], "dsa": []}
+    # (the sweep's per-request caches for the non-sharing opponent would be 36 GB: its standard op for the output
+    # check is the library cascade, and the opponents that need those layouts are skipped by the memory budget)
+    named = [("prefix_small", "prefix", dict(N=8, P=4096, S=256), "tree", None),
+             ("spec_chain", "spec", dict(B=1, L=8192, k=8), "chain", None),
+             ("spec_tree", "spec", SPEC, "tree", None),
+             ("dsa_small", "dsa", dict(B=8, L=32768), "tree", None),
+             ("prefix_sweep", "prefix", PREFIX, "tree", "torch_cascade")]
+    for key, opname, shape, mask, std_name in named:
+        try:
+            out[key], row = ab_line(opname, f"{opname} {json.dumps(shape)}", shape, torch, rounds, mask=mask,
+                                    std_name=std_name)
+            saved[opname].append(row)
+        except Exception as e:
+            out[key] = dict(error=f"{type(e).__name__}: {str(e)[:300]}")
+            torch.cuda.synchronize()
+    for c in ("spec_tree_paged", "decode"):
+        out[c] = side_line(c, torch, 10)
+    ref = {}
+    for opname in ("prefix", "spec", "dsa"):
+        rows_ = []
+        for shape in ops.load_op(opname).BENCH_SHAPES:
+            try:
+                line, row = ab_line(opname, f"{opname} {json.dumps(shape)}", shape, torch, rounds)
+                saved[opname].append(row)
+                rows_.append({k: line.get(k) for k in ("workload", "ms", "p10_ms", "p90_ms", "rows_per_s", "hbm_frac",
+                                                       "hbm_frac_of_8tbs", "vs_torch", "strongest_ref", "speedup",
+                                                       "output_ok", "skipped")})
+            except Exception as e:
+                rows_.append(dict(workload=f"{opname} {json.dumps(shape)}", error=f"{type(e).__name__}: {str(e)[:300]}"))
+                torch.cuda.synchronize()
+        sp = [r.get("speedup") for r in rows_ if r.get("speedup")]
+        ref[opname] = dict(shapes=rows_, geomean_speedup_vs_strongest_torch_ref=abbench.geomean(sp),
+                           min=min(sp) if sp else None, max=max(sp) if sp else None)
+    out["reference_bench_shapes"] = ref
+    try:
+        for opname, rows_ in saved.items():
+            abbench.save_samples(opname, rows_, ROOT)
+        out["samples_saved_to"] = "results/bench_<op>.json"
+    except Exception as e:
+        out["samples_saved_to"] = f"not saved: {type(e).__name__}"
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ multi-GPU op lines
+def timed_side_steps(step, steps, dist, torch, delay):
+    """Per-step device time of a multi-GPU side configuration: before each step a 1 GiB fill (flushes L2 and gives
+    the host time to enqueue the whole step, so that launch overhead is off the clock) and a tiny all-reduce (the
+    ranks start together); CUDA events around the step; per step the MAX over ranks; returns the median in ms."""
+    tiny = torch.zeros(1, device="cuda")
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ev = []
+    for i in range(steps):
+        delay.fill_(i & 0xff)
+        dist.all_reduce(tiny)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        step()
+        b.record()
+        ev.append((a, b))
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b) for a, b in ev], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.median().item()), [float(x) for x in t.tolist()]
+
+
+def multi_prefix(torch, dist, rank, world, steps, delay):
+    """The prefix sweep under hybrid sharding: suffixes by request, the shared prefix by kv head (by key range when
+    the head count does not divide), one all-to-all of packed partials, local merge."""
+    from oracle import judge, ref64
+    from verified_metal_kernels_b200 import abbench, ops, shard
+    op = ops.load_op("prefix")
+    N, P, S, Hq, Hkv, D = PREFIX["N"], PREFIX["P"], PREFIX["S"], op.HQ, op.HKV, op.D
+    plan = shard.PrefixHybridPlan(N, Hq, Hkv, P, world)
+    lo, hi = plan.req[rank]
+    g = torch.Generator(device="cuda")
+
+    def r16(seed, *dims):
+        g.manual_seed(seed)
+        return torch.randn(*dims, generator=g, device="cuda", dtype=torch.float32).half()
+
+    q_all = r16(11, N, Hq, D)                                                     # the same on every rank
+    slens_all = np.random.default_rng(1).integers(0, S + 1, (N,)).astype(np.int32)
+    (h0, h1), (k0, k1) = plan.heads[rank], plan.keys[rank]
+    # the shared prefix is generated head by head from per-head seeds, so any rank can rebuild any slice
+    kp = torch.stack([r16(1000 + h, P, D) for h in range(h0, h1)])[:, k0:k1].contiguous()
+    vp = torch.stack([r16(2000 + h, P, D) for h in range(h0, h1)])[:, k0:k1].contiguous()
+    ks, vs = r16(3000 + rank, hi - lo, Hkv, S, D), r16(4000 + rank, hi - lo, Hkv, S, D)
+    slens = torch.from_numpy(slens_all[lo:hi]).cuda()
+    side = torch.cuda.Stream()
+    comp = shard.CudaPartials()
+
+    def step(ss=side):
+        return shard.prefix_hybrid(q_all, kp, vp, ks, vs, slens, plan, compute=comp, side_stream=ss)
+
+    # output check: this rank's first request against the float64 oracle on the full prefix (rebuilt here)
+    ok, err = True, None
+    before = abbench.checksum(dict(q=q_all, kp=kp, vp=vp, ks=ks, vs=vs))
+    out = step()
+    torch.cuda.synchronize()
+    if hi > lo:
+        kp_full = np.stack([_host(r16(1000 + h, P, D)) for h in range(Hkv)])
+        vp_full = np.stack([_host(r16(2000 + h, P, D)) for h in range(Hkv)])
+        truth = ref64.prefix_ref64(_host(q_all[lo:lo + 1]), kp_full, vp_full, _host(ks[:1]), _host(vs[:1]), slens_all[lo:lo + 1])
+        rep = judge.judge_l2(_host(out[:1].float()), truth, half=True)
+        ok, err = bool(rep["ok"]), rep.get("err_max")
+        del kp_full, vp_full
+    t_side, _ = timed_side_steps(step, steps, dist, torch, delay)
+    t_one, _ = timed_side_steps(lambda: step(None), steps, dist, torch, delay)
+    ok = ok and abbench.checksum(dict(q=q_all, kp=kp, vp=vp, ks=ks, vs=vs)) == before
+    ok = all_ranks_ok(ok, dist, torch)
+    ms = min(t_side, t_one)
+    nbytes = op.algorithmic_bytes(PREFIX, slens_all)
+    per_rank = max(plan.bytes_read(r, slens_all, S) for r in range(world))
+    peak, kind = peaks()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return dict(workload=f"prefix N={N} P={P} S~U[0,{S}]", sharding=f"hybrid: suffixes by request, prefix by {plan.mode} x{world}, "
+                "one all-to-all of packed (m,l,o) records", ms=ms, ms_suffix_on_side_stream=t_side, ms_single_stream=t_one,
+                rows_per_s=N / (ms * 1e-3), algorithmic_mb=nbytes / 1e6, max_bytes_per_gpu_mb=per_rank / 1e6,
+                hbm_gbs_aggregate=gbs, hbm_frac=gbs / (peak * world), hbm_frac_of_8tbs=gbs / (NOMINAL_HBM_GBS * world),
+                peak=f"of {kind}", timing="median over steps of the max over ranks; CUDA events; 1 GiB fill + tiny all-reduce before each step",
+                exchange_bytes_per_rank=int(sum(plan.send_rows(rank)) * shard.RECORD * 4), output_ok=ok, err_max=err)
+
+
+def multi_spec(torch, dist, rank, world, steps, delay):
+    """The speculative tree: batch elements over the ranks; with more ranks than elements each cache is split by
+    position inside a group of ranks (one all-to-all of packed partials inside the group)."""
+    from oracle import judge, ref64
+    from verified_metal_kernels_b200 import abbench, load_kernel, ops, shard
+    op = ops.load_op("spec")
+    B, L, kd, Hq, Hkv, D = SPEC["B"], SPEC["L"], SPEC["k"], op.HQ, op.HKV, op.D
+    plan = shard.SpecSplitPlan(B, kd * Hq, L, world)
+    rng = np.random.default_rng(0)
+    bits_all = op.pack_bits([op.tree_bits(kd, rng, SPEC["max_depth"]) for _ in range(B)], kd)
+    g = torch.Generator(device="cuda")
+
+    def r16(seed, *dims):
+        g.manual_seed(seed)
+        return torch.randn(*dims, generator=g, device="cuda", dtype=torch.float32).half()
+
+    # element b: q from seed 100 + b; its cache from per-head seeds, so that any rank can rebuild any element
+    def elem_q(b):
+        return r16(100 + b, 1, kd, Hq, D)
+
+    def elem_kv(b, which, lo, hi):
+        return torch.stack([r16(1000 * which + 16 * b + h, L, D) for h in range(Hkv)])[None, :, lo:hi].contiguous()
+
+    comp = shard.CudaPartials()
+    ok, err = True, None
+    if plan.split:
+        b = plan.elem[rank]
+        lo, hi = plan.keys[rank]
+        q, bits = elem_q(b), torch.from_numpy(bits_all[b:b + 1]).cuda()
+        k, v = elem_kv(b, 1, lo, hi), elem_kv(b, 2, lo, hi)
+        step = lambda: shard.spec_split(q, k, v, bits, plan, compute=comp)
+        inputs = dict(q=q, k=k, v=v)
+        out, (r0, r1) = step()
+        torch.cuda.synchronize()
+        # check the first draft row this rank owns (all its heads in the range) against the full cache
+        i0 = r0 // Hq
+        kf, vf = _host(elem_kv(b, 1, 0, L)), _host(elem_kv(b, 2, 0, L))
+        truth = ref64.spec_ref64(_host(q), kf, vf, bits_all[b:b + 1])[0].reshape(kd * Hq, D)
+        r_hi = min(r1, (i0 + 2) * Hq)
+        rep = judge.judge_l2(_host(out[:r_hi - r0].float()), truth[r0:r_hi], half=True)
+        ok, err = bool(rep["ok"]), rep.get("err_max")
+        del kf, vf
+        mode = f"cache split in {world // B} by position inside groups of ranks, one all-to-all of packed (m,l,o) records per group"
+        xbytes = int(sum(plan.send_rows(rank)) * shard.RECORD * 4)
+    else:
+        lo, hi = plan.elems[rank]
+        fn = load_kernel("spec")
+        xbytes = 0
+        mode = f"batch elements x{world}, no exchange"
+        if hi > lo:
+            q = torch.cat([elem_q(b) for b in range(lo, hi)])
+            k = torch.cat([elem_kv(b, 1, 0, L) for b in range(lo, hi)])
+            v = torch.cat([elem_kv(b, 2, 0, L) for b in range(lo, hi)])
+            bits = torch.from_numpy(bits_all[lo:hi]).cuda()
+            step = lambda: fn(q=q, k=k, v=v, bits=bits)
+            inputs = dict(q=q, k=k, v=v)
+            out = step()
+            torch.cuda.synchronize()
+            # the first two draft rows of this rank's first element against the float64 oracle
+            full = ref64.spec_ref64(_host(q[:1]), _host(k[:1]), _host(v[:1]), bits_all[lo:lo + 1])[:, :2]
+            rep = judge.judge_l2(_host(out[:1, :2].float()), full, half=True)
+            ok, err = bool(rep["ok"]), rep.get("err_max")
+            del full
+        else:
+            step, inputs = (lambda: None), {}
+    before = abbench.checksum(inputs)
+    ms, _ = timed_side_steps(step, steps, dist, torch, delay)
+    ok = ok and abbench.checksum(inputs) == before
+    ok = all_ranks_ok(ok, dist, torch)
+    nbytes = op.algorithmic_bytes(SPEC)
+    flops = 4.0 * B * kd * Hq * D * L
+    peak, kind = peaks()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    used = min(world, max(B, world if plan.split else B))
+    return dict(workload=f"spec tree depth<=8 B={B} k={kd} L={L}", sharding=mode, ms=ms, rows_per_s=B * kd / (ms * 1e-3),
+                algorithmic_mb=nbytes / 1e6, hbm_gbs_aggregate=gbs, hbm_frac=gbs / (peak * world),
+                hbm_frac_of_8tbs=gbs / (NOMINAL_HBM_GBS * world), tflops_aggregate=flops / (ms * 1e-3) / 1e12,
+                gpus_with_work=used if not plan.split else world, peak=f"of {kind}",
+                timing="median over steps of the max over ranks; CUDA events; 1 GiB fill + tiny all-reduce before each step",
+                exchange_bytes_per_rank=xbytes, output_ok=ok, err_max=err)
+
+
 # ------------------------------------------------------------------------------------------------ CPU arm
+def blas_threads(n=None):
+    """Sets (when n is given) and returns the BLAS thread count NumPy's matmuls use.  A launcher that starts one
+    process per GPU exports OMP_NUM_THREADS=1; the CPU arm runs on one rank alone and takes every core it may."""
+    try:
+        import threadpoolctl
+        if n is not None:
+            threadpoolctl.threadpool_limits(limits=int(n))
+        info = [p for p in threadpoolctl.threadpool_info() if p.get("user_api") == "blas"]
+        return max([int(p.get("num_threads", 1)) for p in info] or [1])
+    except Exception:
+        return None
+
+
 def cpu_sample(n_requests, L):
-    """Float64 oracle on `n_requests` requests of the dsa workload; returns (seconds, cores used)."""
+    """Float64 oracle on `n_requests` requests of the dsa workload; returns seconds."""
     from oracle import ref64
     from verified_metal_kernels_b200 import ops
     op = ops.load_op("dsa")
@@ -406,27 +674,73 @@ def host_cores():
 
 
 def reference_arm(a):
-    """The reference's CPU implementation of the path: its float64 NumPy truth, restated in oracle/ (the
-    reference is a Python package that cannot travel to the GPU box).  One request per step."""
+    """The reference's CPU implementation of the path: its float64 NumPy truth as restated in oracle/ (the
+    reference is a Python package that cannot travel to the GPU box; the restatement replaces its einsum
+    contractions by BLAS matmuls of the same float64 arithmetic, which is faster, so the ratio against it is
+    conservative).  One request per step, on every host core the process may use."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
+    cores = host_cores()
+    threads = blas_threads(cores)
     for _ in range(min(a.warmup, 1)):
         cpu_sample(1, DSA["L"])
     t = [cpu_sample(1, DSA["L"]) for _ in range(a.steps)]
     sec = sum(t) / len(t)
     v = 1.0 / sec
     line = dict(metric=METRIC, value=v, unit=UNIT, impl="reference", n_gpus=a.gpus, steps=a.steps, warmup=min(a.warmup, 1),
-                ms_per_step=sec * 1e3, higher_is_better=True, scaling=a.scaling, vs_baseline=None, dtype="f64",
-                data="synthetic", config=dict(workload="dsa B=128 L=131072 (sample: 1 request per step)"),
-                cpu_baseline=dict(value=v, unit=UNIT, cores=host_cores(), kind="port",
-                                  sample="1 of 128 requests (B=1, L=131072) per step, NumPy float64, BLAS threads"),
+                ms_per_step=sec * 1e3, higher_is_better=True, scaling=a.scaling or ("weak" if a.gpus == 1 else "strong"),
+                vs_baseline=None, dtype="f64", data="synthetic",
+                config=dict(workload="dsa B=128 L=131072 (sample: 1 request per step)"),
+                cpu_baseline=dict(value=v, unit=UNIT, cores=cores, blas_threads=threads, kind="port",
+                                  sample="1 of 128 requests (B=1, L=131072) per step, float64 NumPy oracle, BLAS matmuls"),
                 e2e=dict(value=v, unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
     print(json.dumps(line))
     return 0
 
 
 # ------------------------------------------------------------------------------------------------ main
+def e2e_leg(fn, inp, Bl, L, world, steps, dist, torch):
+    """The same op through the public kernel(...) call with pinned HOST tensors (at most E2E_MAX requests per call)."""
+    from verified_metal_kernels_b200.kernels import dsa_b200
+    Be = min(max(Bl, 1), E2E_MAX)
+    host = {}
+    for k, v in inp.items():
+        if v is not None:
+            host[k] = torch.empty(v[:Be].shape, dtype=v.dtype, pin_memory=True)
+            host[k].copy_(v[:Be])
+        else:
+            host[k] = None
+    torch.cuda.synchronize()
+    all_bytes = sum(v.numel() * v.element_size() for v in host.values() if v is not None)
+    kv_bytes = host["kv"].numel() * host["kv"].element_size()
+    # the kernel module leaves a page-locked latent cache on the host and reads only the selected rows
+    in_place = dsa_b200.HOST_CACHE_IN_PLACE and L > 2048
+    h2d = all_bytes - kv_bytes + Be * min(L, 2048) * 576 * 2 if in_place else all_bytes
+    d2h = Be * 128 * 512 * 2
+    e_steps = min(steps, 5)
+    run_h = (lambda: fn(**host)) if Bl > 0 else (lambda: None)
+    esec, _, _ = timed_steps(run_h, e_steps, 1, dist, torch)
+    e_rows = Be
+    if dist is not None:
+        t = torch.tensor([Be if Bl > 0 else 0], device="cuda", dtype=torch.int64)
+        dist.all_reduce(t)
+        e_rows = int(t.item())
+    e2e = dict(value=e_rows * e_steps / esec, unit=UNIT, h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
+               steps=e_steps, sample=f"{Be} requests per call per rank (of {Bl}), pinned host tensors in, host tensor out"
+               + ("; the latent cache stays in host memory and stage 3 reads its 2048 selected rows per request "
+                  "from there, every other input is copied" if in_place else ""))
+    if in_place:
+        # the same call with the cache copied to the device whole, for comparison
+        dsa_b200.HOST_CACHE_IN_PLACE = False
+        try:
+            fsec, _, _ = timed_steps(run_h, e_steps, 1, dist, torch)
+        finally:
+            dsa_b200.HOST_CACHE_IN_PLACE = True
+        e2e["copy_everything"] = dict(value=e_rows * e_steps / fsec, unit=UNIT, h2d_bytes_per_step=all_bytes)
+    return e2e
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -435,128 +749,170 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=DSA["B"], help="total dsa batch (default: the sweep's 128)")
     ap.add_argument("--cache", type=int, default=DSA["L"], help="dsa cache length (default: the sweep's 131072)")
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
-                    help="N>1: weak = --batch requests per rank (default), strong = --batch requests in total")
+    ap.add_argument("--scaling", default=None, choices=["weak", "strong"],
+                    help="N>1: strong = --batch requests in total, cut over the ranks (default); weak = --batch "
+                         "requests per rank as the headline.  Both are measured and printed either way")
     ap.add_argument("--batch-invariant", action="store_true",
                     help="time the library with vmk_set_batch_invariant(1) (fixed kernels and cut points)")
-    ap.add_argument("--no-side", action="store_true", help="skip the prefix / spec side lines")
+    ap.add_argument("--no-side", action="store_true", help="skip the per-op lines (`ops`)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
-    ap.add_argument("--side-only", default=None, help="time only one side configuration (prefix_small, spec_chain, "
-                    "spec_tree, dsa_small, prefix_sweep) on one GPU and print its line; used for profiling")
+    ap.add_argument("--rounds", type=int, default=30, help="shuffled rounds per configuration of the per-op lines")
+    ap.add_argument("--side-only", default=None, help="time only one configuration (prefix_small, spec_chain, "
+                    "spec_tree, dsa_small, prefix_sweep, decode, decode_small, spec_tree_paged) on one GPU and print "
+                    "its line; used for profiling")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3) if a.impl == "ours" else a.warmup
     if a.impl == "reference":
         return reference_arm(a)
 
     import torch
-    from verified_metal_kernels_b200 import _lib, build, load_kernel, ops, shard
+    from verified_metal_kernels_b200 import _lib, abbench, build, load_kernel, ops, shard
+    from verified_metal_kernels_b200.kernels import dsa_b200
     rank, local_rank, world = shard.world()
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU path")
     torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist.init_process_group("nccl", device_id=dev)
     build.build()
     if a.batch_invariant:
         _lib.lib().vmk_set_batch_invariant(1)
     if a.side_only:
         print(json.dumps(side_line(a.side_only, torch, a.steps)))
         return 0
+    scaling = a.scaling or ("weak" if world == 1 else "strong")
     fn = load_kernel("dsa")
     op = ops.load_op("dsa")
     B, L = a.batch, a.cache
-    if a.scaling == "weak":
-        Bl, B_total = B, B * world                       # this rank's own requests; global batch grows with N
-    else:
-        lo, hi = shard.unit_range(B, rank, world)
-        Bl, B_total = hi - lo, B
-    inp = dsa_inputs(max(Bl, 1), L, "cuda", seed=1000 + rank)
-    run = (lambda: fn(**inp)) if Bl > 0 else (lambda: None)
+    lo, hi = shard.unit_range(B, rank, world)
+    inp_full = dsa_inputs(B, L, "cuda", seed=1000 + rank)          # this rank's own 128 requests (the weak batch)
+    n_strong = hi - lo
+    inp_strong = {k: (None if v is None else v[:max(n_strong, 1)]) for k, v in inp_full.items()}   # its share of ONE batch
+
+    # ---- output check before any timing: one request of this rank against the float64 oracle
+    before = abbench.checksum({k: v for k, v in inp_strong.items() if v is not None})
+    out, idx, cnt = dsa_b200.kernel(**inp_strong, return_selection=True)
+    torch.cuda.synchronize()
+    ok, detail = check_dsa_request(inp_strong, out, idx, cnt, 0)
+    del out, idx, cnt
+
+    def timed(inp_, n_local, sampler=None):
+        run = (lambda: fn(**inp_)) if n_local > 0 else (lambda: None)
+        return timed_steps(run, a.steps, a.warmup, dist, torch, sampler)
 
     sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
-    sec, per, clocks = timed_steps(run, a.steps, a.warmup, dist, torch, sampler)
-    status = _lib.read_status(torch.device("cuda", torch.cuda.current_device()))
-    value = B_total * a.steps / sec
-
-    # end to end: pinned host tensors in, host tensor out, through the public kernel(...) call
-    e2e = None
-    if not a.no_e2e:
-        # Pinned host copies of (a bounded slice of) this rank's batch: at most E2E_MAX requests per call, so
-        # that host memory and the pinning time stay modest; rows/s is per-request work either way.
-        Be = min(max(Bl, 1), E2E_MAX)
-        host = {}
-        for k, v in inp.items():
-            if v is not None:
-                host[k] = torch.empty(v[:Be].shape, dtype=v.dtype, pin_memory=True)
-                host[k].copy_(v[:Be])
+    results = {}
+    if world == 1:
+        results["weak"] = timed(inp_full, B, sampler) + (B, B)
+    else:
+        order = ["strong", "weak"] if scaling == "strong" else ["weak", "strong"]
+        for i, kind in enumerate(order):
+            if kind == "strong":
+                results[kind] = timed(inp_strong, n_strong, sampler if i == 0 else None) + (B, n_strong)
             else:
-                host[k] = None
-        torch.cuda.synchronize()
-        from verified_metal_kernels_b200.kernels import dsa_b200
-        all_bytes = sum(v.numel() * v.element_size() for v in host.values() if v is not None)
-        kv_bytes = host["kv"].numel() * host["kv"].element_size()
-        # the kernel module leaves a page-locked latent cache on the host and reads only the selected rows
-        in_place = dsa_b200.HOST_CACHE_IN_PLACE and L > 2048
-        h2d = all_bytes - kv_bytes + Be * min(L, 2048) * 576 * 2 if in_place else all_bytes
-        d2h = Be * 128 * 512 * 2
-        e_steps = min(a.steps, 5)
-        run_h = (lambda: fn(**host)) if Bl > 0 else (lambda: None)
-        esec, _, _ = timed_steps(run_h, e_steps, 1, dist, torch)
-        e_rows = Be * world if Bl > 0 else 0
-        e2e = dict(value=e_rows * e_steps / esec, unit=UNIT, h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
-                   steps=e_steps, sample=f"{Be} requests per call per rank (of {Bl}), pinned host tensors in, host tensor out"
-                   + ("; the latent cache stays in host memory and stage 3 reads its 2048 selected rows per request "
-                      "from there, every other input is copied" if in_place else ""))
-        if in_place:
-            # the same call with the cache copied to the device whole, for comparison
-            dsa_b200.HOST_CACHE_IN_PLACE = False
-            try:
-                fsec, _, _ = timed_steps(run_h, e_steps, 1, dist, torch)
-            finally:
-                dsa_b200.HOST_CACHE_IN_PLACE = True
-            e2e["copy_everything"] = dict(value=e_rows * e_steps / fsec, unit=UNIT, h2d_bytes_per_step=all_bytes)
-        del host
+                results[kind] = timed(inp_full, B, sampler if i == 0 else None) + (B * world, B)
+    status = _lib.read_status(dev)
+    ok = ok and abbench.checksum({k: v for k, v in inp_strong.items() if v is not None}) == before
+    ok = all_ranks_ok(ok, dist, torch)
+    head = "weak" if world == 1 else scaling
+    sec, per, clocks, B_total, Bl = results[head]
+    value = B_total * a.steps / sec
+    inp = inp_full if head == "weak" else inp_strong
+
+    e2e = None if a.no_e2e else e2e_leg(fn, inp, Bl, L, world, a.steps, dist, torch)
+    status |= _lib.read_status(dev)
 
     launches = 3 + (1 if _lib.lib().vmk_dsa_attend_workspace_bytes(max(Bl, 1)) > 256 else 0)
     metric = METRIC if (B, L) == (DSA["B"], DSA["L"]) else f"dsa decode rows/s (batch {B}, cache {L})"
     line = dict(metric=metric, value=value, unit=UNIT, n_gpus=world, steps=a.steps, warmup=a.warmup,
-                ms_per_step=sec * 1e3 / a.steps, higher_is_better=True, scaling=a.scaling, vs_baseline=None, dtype="f16",
+                ms_per_step=sec * 1e3 / a.steps, higher_is_better=True, scaling=head, vs_baseline=None, dtype="f16",
                 data="synthetic",
-                config=dict(workload=f"dsa B={B} L={L}" + (" (8-GPU sweep configuration)" if (B, L) == (DSA["B"], DSA["L"]) else ""), parallelism=f"batch-sharded x{world}",
-                            global_batch=B_total, per_rank_batch=Bl, l2="inputs (GBs per rank) far larger than the 126 MB L2; no flush"),
-                clocks=clocks, e2e=e2e, gpu_launches=launches * a.steps, device_status=status)
+                config=dict(workload=f"dsa B={B} L={L}" + (" (8-GPU sweep configuration)" if (B, L) == (DSA["B"], DSA["L"]) else ""),
+                            parallelism=f"batch-sharded x{world}", global_batch=B_total, per_rank_batch=Bl,
+                            l2="inputs (GBs per rank) far larger than the 126 MB L2; no flush"),
+                clocks=clocks, e2e=e2e, gpu_launches=launches * a.steps, device_status=status,
+                output_ok=ok, output_check=dict(what="request 0 of every rank against the float64 oracle (selection + output), "
+                                                "inputs unmodified after the run", rank0=detail))
+    for kind, (s_, _, _, bt, bl) in results.items():
+        if kind != head or world > 1:
+            line[kind] = dict(value=bt * a.steps / s_, unit=UNIT, ms_per_step=s_ * 1e3 / a.steps, global_batch=bt,
+                              per_rank_batch=bl, scaling=kind)
+
+    side_ops = None
+    if world > 1 and not a.no_side:
+        # side configurations on all ranks (collectives inside): the big dsa inputs go first
+        del inp, inp_strong
+        keep = {k: (None if v is None else v[:max(n_strong, 1)].clone()) for k, v in inp_full.items()}
+        del inp_full
+        torch.cuda.empty_cache()
+        delay = torch.empty(DELAY_BYTES, dtype=torch.uint8, device="cuda")
+        side_ops = {}
+        for key, f in (("prefix_sweep", multi_prefix), ("spec_tree", multi_spec)):
+            try:
+                side_ops[key] = f(torch, dist, rank, world, max(a.steps, 10), delay)
+            except Exception as e:                 # every rank raises or none does (same code path), so no rank is left waiting
+                side_ops[key] = dict(error=f"{type(e).__name__}: {str(e)[:300]}")
+        del delay
+        status |= _lib.read_status(dev)
+        line["device_status"] = status
+        inp_full = keep
+        inp = keep
 
     if rank == 0:
-        st = stage_times(inp, min(a.steps, 10), torch)
+        st_inp = inp if world > 1 else inp
+        st = stage_times(st_inp, min(a.steps, 10), torch)
+        Bs = st_inp["ik"].shape[0]
         peak, kind = peaks()
-        alg = Bl * L * 128 * 2                       # the ik stream: every byte once
+        alg = Bs * L * 128 * 2                       # the ik stream: every byte once
         ach = alg / (st["indexer_ms"] * 1e-3) / 1e9
         tr = ncu_traffic()
         line["roofline"] = dict(kernel="dsa indexer", bound="hbm", achieved=ach, peak=peak, unit="GB/s", frac=ach / peak,
-                                peak_source=f"of {kind}", traffic=(tr["indexer_bytes_per_position"] * Bl * L if tr else None),
+                                frac_of_8tbs=ach / NOMINAL_HBM_GBS, batch=Bs,
+                                peak_source=f"of {kind}", traffic=(tr["indexer_bytes_per_position"] * Bs * L if tr else None),
                                 algorithmic_bytes=alg, launch_ms=st["indexer_ms"])
-        total_alg = op.algorithmic_bytes(dict(B=Bl, L=L))
-        line["stages_ms"] = st
-        line["op_hbm"] = dict(algorithmic_bytes=total_alg, gbs=total_alg / (sec / a.steps) / 1e9,
-                              frac=total_alg / (sec / a.steps) / 1e9 / peak)
-        if not a.no_side and world == 1:
-            del inp
+        total_alg = op.algorithmic_bytes(dict(B=B_total, L=L))
+        gbs = total_alg / (sec / a.steps) / 1e9
+        line["stages_ms"] = dict(st, batch=Bs)
+        line["op_hbm"] = dict(algorithmic_bytes=total_alg, gbs=gbs, frac=gbs / (peak * world),
+                              frac_of_8tbs=gbs / (NOMINAL_HBM_GBS * world), gpus=world)
+        if world == 1 and not a.no_side:
+            # the whole op with fp8 index keys (a different input format: reported beside the headline)
+            try:
+                iq8, iqs, ik8, iks = fp8_index(inp, torch)
+                f8 = lambda: dsa_b200.kernel_fp8_index(inp["q"], inp["kv"], iq8, iqs, ik8, iks, inp["w"])
+                fsec, _, _ = timed_steps(f8, min(a.steps, 10), 3, None, torch)
+                n8 = min(a.steps, 10)
+                alg8 = total_alg - B * L * 128 + B * L * 4
+                line["fp8_index"] = dict(value=B * n8 / fsec, unit=UNIT, ms_per_step=fsec * 1e3 / n8,
+                                         algorithmic_bytes=alg8, hbm_frac=alg8 / (fsec / n8) / 1e9 / peak,
+                                         note="index queries and keys as e4m3 bytes + fp32 scales; q, kv fp16")
+                del iq8, iqs, ik8, iks
+            except Exception as e:
+                line["fp8_index"] = dict(error=f"{type(e).__name__}: {str(e)[:200]}")
+            del inp, inp_full, inp_strong, st_inp
             torch.cuda.empty_cache()
-            line["ops"] = {c: side_line(c, torch, 10)
-                           for c in ("prefix_small", "spec_chain", "spec_tree", "spec_tree_paged", "dsa_small", "prefix_sweep", "decode")}
+            line["ops"] = single_gpu_ops(torch, a.rounds)
+        elif side_ops is not None:
+            line["ops"] = side_ops
         if not a.no_cpu and world == 1:
             n = 2
+            threads = blas_threads(host_cores())
             t = cpu_sample(n, L)
-            line["cpu_baseline"] = dict(value=n / t, unit=UNIT, cores=host_cores(), kind="port",
+            line["cpu_baseline"] = dict(value=n / t, unit=UNIT, cores=host_cores(), blas_threads=threads, kind="port",
                                         sample=f"{n} of {B} requests (L={L}), float64 NumPy oracle, {t:.1f} s")
+        line["device_status"] |= _lib.read_status(dev)
         print(json.dumps(line))
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
-    return 0
+    bad = line["device_status"] != 0 or not line["output_ok"]
+    if bad and rank == 0:
+        sys.stderr.write(f"bench.py: INVALID run (device_status={line['device_status']}, output_ok={line['output_ok']})\n")
+    return 1 if bad else 0
 
 
 if __name__ == "__main__":

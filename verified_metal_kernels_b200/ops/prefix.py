@@ -57,18 +57,23 @@ def make_inputs(shape, seed=0, dist="randn", with_ref_layouts=False):
 
 
 def build_layouts(kp, vp, ks, vs):
-    """Per-request full caches kf, vf (N,Hkv,P+S,D) for the non-sharing standard op
-    (reference ops/prefix.py:47-54).  Works on NumPy arrays or torch tensors."""
+    """Layouts the standard ops read, never passed to kernel() (reference ops/prefix.py:47-54): per-request full
+    caches kf, vf (N,Hkv,P+S,D) for the non-sharing op, and the unified caches ku, vu (1,Hkv,P+N*S,D) -- the
+    shared prefix once, then every request's suffix in turn -- for the block-masked op.  NumPy arrays or torch
+    tensors."""
+    N, Hkv, S, d = ks.shape
     if isinstance(kp, np.ndarray):
-        N = ks.shape[0]
         kf = np.concatenate([np.broadcast_to(kp[None], (N,) + kp.shape), ks], axis=2)
         vf = np.concatenate([np.broadcast_to(vp[None], (N,) + vp.shape), vs], axis=2)
-        return dict(kf=kf, vf=vf)
+        ku = np.concatenate([kp, ks.transpose(1, 0, 2, 3).reshape(Hkv, N * S, d)], axis=1)[None]
+        vu = np.concatenate([vp, vs.transpose(1, 0, 2, 3).reshape(Hkv, N * S, d)], axis=1)[None]
+        return dict(kf=kf, vf=vf, ku=ku, vu=vu)
     import torch
-    N = ks.shape[0]
     kf = torch.cat([kp[None].expand(N, *kp.shape), ks], dim=2)
     vf = torch.cat([vp[None].expand(N, *vp.shape), vs], dim=2)
-    return dict(kf=kf, vf=vf)
+    ku = torch.cat([kp, ks.permute(1, 0, 2, 3).reshape(Hkv, N * S, d)], dim=1)[None]
+    vu = torch.cat([vp, vs.permute(1, 0, 2, 3).reshape(Hkv, N * S, d)], dim=1)[None]
+    return dict(kf=kf, vf=vf, ku=ku, vu=vu)
 
 
 # ------------------------------------------------------------------ standard ops (torch; opponents, not product)
@@ -87,7 +92,59 @@ def torch_naive(q, kp, vp, ks, vs, slens=None, kf=None, vf=None, **_):
     return F.scaled_dot_product_attention(q[:, :, None, :], kf, vf, attn_mask=mask, enable_gqa=True)[:, :, 0, :]
 
 
-TORCH_REFS = dict(torch_naive=torch_naive)
+def torch_unified(q, kp, vp, ks, vs, slens=None, ku=None, vu=None, **_):
+    """One fused SDPA call over the unified cache with a block mask: the N*G stacked rows of a kv head all see
+    the shared prefix, and row (n, g) sees only request n's suffix block (reference ops/prefix.py:126-138, its
+    strongest library opponent on this op).  The prefix is read once per kv head."""
+    import torch
+    import torch.nn.functional as F
+    N, Hq, d = q.shape
+    Hkv, P = kp.shape[0], kp.shape[1]
+    S, G = ks.shape[2], Hq // kp.shape[0]
+    if ku is None:
+        lay = build_layouts(kp, vp, ks, vs)
+        ku, vu = lay["ku"], lay["vu"]
+    owner = torch.arange(N * G, device=q.device)[:, None] // G           # request of each stacked row
+    col = torch.arange(P + N * S, device=q.device)[None, :]
+    end = (owner + 1) * S if slens is None else owner * S + slens.to(q.device).long()[owner[:, 0]][:, None]
+    mask = (col < P) | ((col >= P + owner * S) & (col < P + end))
+    stacked = q.reshape(N, Hkv, G, d).permute(1, 0, 2, 3).reshape(1, Hkv, N * G, d)
+    o = F.scaled_dot_product_attention(stacked, ku, vu, attn_mask=mask)
+    return o.reshape(Hkv, N, G, d).permute(1, 0, 2, 3).reshape(N, Hq, d)
+
+
+def torch_cascade(q, kp, vp, ks, vs, slens=None, **_):
+    """The sharing algorithm written with library matmuls: prefix scores for all stacked rows at once, suffix
+    scores per request, two fp32 softmax partials merged by log-sum-exp (the reference's `mlx_cascade`,
+    ops/prefix.py:100-118, in torch).  Reads every byte once, like kernel(); P and the scores round-trip HBM."""
+    import torch
+    N, Hq, d = q.shape
+    Hkv, S = kp.shape[0], ks.shape[2]
+    G = Hq // Hkv
+    sc = d ** -0.5
+    qh = q.reshape(N, Hkv, G, d)
+    qs = qh.permute(1, 0, 2, 3).reshape(Hkv, N * G, d)
+    s1 = torch.matmul(qs, kp.transpose(1, 2)).float() * sc                   # (Hkv, N*G, P)
+    m1 = s1.amax(-1, keepdim=True)
+    p1 = torch.exp(s1 - m1)
+    l1 = p1.sum(-1, keepdim=True)
+    o1 = torch.matmul(p1.to(q.dtype), vp).float()
+    to_req = lambda t: t.reshape(Hkv, N, G, -1).permute(1, 0, 2, 3)
+    o1, m1, l1 = to_req(o1), to_req(m1), to_req(l1)
+    s2 = torch.matmul(qh, ks.transpose(2, 3)).float() * sc                   # (N, Hkv, G, S)
+    if slens is not None:
+        dead = torch.arange(S, device=q.device)[None, :] >= slens.to(q.device).long()[:, None]
+        s2 = s2.masked_fill(dead[:, None, None, :], float("-inf"))
+    m2 = s2.amax(-1, keepdim=True)
+    p2 = torch.exp(s2 - torch.where(torch.isinf(m2), torch.zeros_like(m2), m2))
+    l2 = p2.sum(-1, keepdim=True)
+    o2 = torch.matmul(p2.to(q.dtype), vs).float()
+    m = torch.maximum(m1, m2)
+    a, b = torch.exp(m1 - m), torch.exp(m2 - m)
+    return ((o1 * a + o2 * b) / (l1 * a + l2 * b)).to(q.dtype).reshape(N, Hq, d)
+
+
+TORCH_REFS = dict(torch_naive=torch_naive, torch_unified=torch_unified, torch_cascade=torch_cascade)
 L1_REF = "torch_naive"
 L3_REF = "torch_naive"
 
