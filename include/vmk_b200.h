@@ -288,7 +288,9 @@ VMK_API int vmk_lse_merge_packed(const float* records, int parts, int rows, int 
  *   vmk_attn_set_tc(0): prefix / spec row tiles of more than 64 rows use the warp-level kernel instead of
  *   the tcgen05 one (1, the default).
  *   vmk_dsa_set_indexer_variant(v), vmk_dsa_set_attend_variant(v): 1 = tcgen05 kernels (default), 0 = the
- *   warp-level mma.sync kernels kept as cross-checks (fp16, contiguous caches only); other values are refused. */
+ *   warp-level mma.sync kernels kept as cross-checks (fp16, contiguous caches only).  The attend stage also
+ *   takes 2 = the tcgen05 kernel with its rows gathered by TMA (tile::gather4) instead of cp.async; the result has
+ *   the same bits.  Other values are refused. */
 VMK_API int vmk_attn_set_tc(int on);
 VMK_API int vmk_dsa_set_indexer_variant(int variant);
 VMK_API int vmk_dsa_set_attend_variant(int variant);

@@ -3,6 +3,7 @@
 #include <cudaTypedefs.h>
 
 #include "common.cuh"
+#include "dsa_mla_tc.cuh"
 
 namespace vmk {
 
@@ -43,6 +44,21 @@ int make_tmap_3d(CUtensorMap* tm, const void* base, uint64_t width, uint64_t row
   cuuint32_t box[3] = {box_w, box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? VMK_OK : VMK_E_DRIVER;
+}
+
+int make_tmap_rows(CUtensorMap* tm, const void* base, uint64_t width, uint64_t rows) {
+  auto fn = encode_fn();
+  if (fn == nullptr) return VMK_E_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (width * 2) % 16 != 0 || rows == 0 || rows > 0x7fffffffull)
+    return VMK_E_BADARG;
+  cuuint64_t dims[2] = {width, rows};
+  cuuint64_t strides[1] = {width * 2};
+  cuuint32_t box[2] = {64, 1};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? VMK_OK : VMK_E_DRIVER;

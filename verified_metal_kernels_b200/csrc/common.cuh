@@ -96,12 +96,30 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* tm, in
       : "memory");
 }
 
+// Row gather: four rows y0..y3 of a 2-D tensor (box (64 x 16-bit, 1)), columns [x, x + 64), land as four
+// consecutive 128-byte rows at dst (512-byte aligned, swizzled by address like any other TMA tile); a row
+// coordinate outside the tensor is filled with zeros.  x * 2 must be a multiple of 16 bytes: callers pass
+// multiples of 64.  No cluster multicast.
+__device__ __forceinline__ void tma_gather4(void* dst, const CUtensorMap* tm, int x, int y0, int y1, int y2, int y3,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(tm), "r"(smem_u32(bar)), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3)
+      : "memory");
+}
+
 // ------------------------------------------------------------------------------------------------
 // cp.async (16-byte, zero-fill when src_bytes == 0), ldmatrix, mma.sync
 // ------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(src_bytes)
                : "memory");
+}
+// This thread's arrival on `bar` happens when all its cp.async copies so far have landed (the arrival is one of the
+// barrier's expected ones: .noinc).
+__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>

@@ -1,6 +1,7 @@
 // `dsa`: indexer (stage 1), sparse absorbed-MLA attention (stage 3) and the fused entry point.
 // Stage 2 (top-2048 select) lives in dsa_select.cu, the tcgen05 indexer in dsa_indexer_tc.cu.
 #include "common.cuh"
+#include "dsa_mla_tc.cuh"
 
 namespace vmk {
 
@@ -15,23 +16,7 @@ int indexer_tc_launch(const CUtensorMap& tmIK, const CUtensorMap& tmIQ, const fl
                       float* scores, uint32_t* hist, int B, int L, int32_t* status, cudaStream_t stream, int bf16,
                       const int32_t* page_table, int page_size, int table_stride, int pages, const float* iq_scale,
                       const float* ik_scale);
-struct MlaTcParams {
-  const __half* q;
-  const __half* kv;
-  const int32_t* idx;
-  const int32_t* cnt;
-  __half* out;
-  float* part_o;
-  float* part_ml;
-  int B, L, ncta;
-  float sc;
-  int32_t* status;
-  int bf16;
-  const int32_t* page_table;
-  int page_size, table_stride, pages;
-};
-int mla_tc_launch(const MlaTcParams& p, float* workspace, cudaStream_t stream);   // dsa_mla_tc.cu
-size_t mla_tc_workspace(int B);
+
 int select_launch(const float* scores, const uint32_t* hist, const int32_t* lens, int32_t* idx, int32_t* cnt, int B,
                   int L, cudaStream_t stream);
 
@@ -472,7 +457,7 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const __half* __restri
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-static int g_attend_variant = 1;    // 0 = warp-level mma.sync kernel, 1 = tcgen05 kernel (default)
+static int g_attend_variant = 1;    // 0 = warp-level mma.sync kernel, 1 = tcgen05 kernel (default), 2 = the same with a TMA row gather
 
 // Key splits of the warp-level kernel.
 static int mla_splits(int B) {
@@ -576,7 +561,7 @@ static int attend_impl(const void* q, const void* kv, const int32_t* idx, const 
                        int L, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream, int bf16 = 0,
                        DsaPages pg = DsaPages{nullptr, 0, 0, 0}) {
   if (!q || !kv || !idx || !cnt || !out || B <= 0 || L <= 0) return VMK_E_BADARG;
-  if ((bf16 || pg.pages > 0) && g_attend_variant != 1) return VMK_E_UNSUPPORTED;
+  if ((bf16 || pg.pages > 0) && g_attend_variant == 0) return VMK_E_UNSUPPORTED;
   if (!aligned16(q) || !aligned16(kv) || !aligned16(out) || B > 65535) return VMK_E_BADARG;
   const int ns = mla_splits(B);
   if (!ws || ws_bytes < attend_ws(B) || (reinterpret_cast<uintptr_t>(ws) & 255)) return VMK_E_WORKSPACE;
@@ -594,8 +579,21 @@ static int attend_impl(const void* q, const void* kv, const int32_t* idx, const 
     p.part_o = static_cast<float*>(ws);
     p.part_ml = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + align_up((size_t)B * ns * kMH * kDV * 4, 256));
   }
-  if (g_attend_variant == 1) {
+  if (g_attend_variant >= 1) {
     MlaTcParams t;
+    memset(&t, 0, sizeof(t));
+    t.gather_tma = g_attend_variant == 2 ? 1 : 0;
+    t.rows_total = pg.pages > 0 ? pg.pages * pg.page_size : B * L;
+    if ((long long)t.rows_total != (pg.pages > 0 ? (long long)pg.pages * pg.page_size : (long long)B * L))
+      return VMK_E_UNSUPPORTED;                        // row coordinates are 32-bit
+    if (t.gather_tma) {
+      const int rc = make_tmap_rows(&t.tmKV, kv, kDK, (uint64_t)t.rows_total);
+      if (rc) return rc;
+    }
+    {
+      const int rc = make_tmap_3d(&t.tmQ, q, kDK, kMH, (uint64_t)B, 64, 64);
+      if (rc) return rc;
+    }
     t.q = p.q; t.kv = p.kv; t.idx = p.idx; t.cnt = p.cnt; t.out = p.out; t.part_o = nullptr; t.part_ml = nullptr;
     t.B = B; t.L = L; t.ncta = 0; t.sc = p.sc; t.status = status; t.bf16 = bf16;
     t.page_table = pg.pages > 0 ? pg.table : nullptr;
@@ -623,9 +621,10 @@ static int g_indexer_variant = 1;   // 0 = mma.sync (warp-level), 1 = tcgen05 + 
 
 using namespace vmk;
 
-// Test hook: chooses the stage-3 implementation (0 = warp-level mma.sync, 1 = tcgen05).
+// Test hook: chooses the stage-3 implementation (0 = warp-level mma.sync, 1 = tcgen05 with the rows gathered by
+// cp.async from four warps (default), 2 = tcgen05 with the rows gathered by TMA tile::gather4).
 extern "C" VMK_API int vmk_dsa_set_attend_variant(int v) {
-  if (v != 0 && v != 1) return VMK_E_BADARG;
+  if (v < 0 || v > 2) return VMK_E_BADARG;
   g_attend_variant = v;
   return VMK_OK;
 }

@@ -270,6 +270,7 @@ def set_indexer_variant(name):
 
 
 def set_attend_variant(name):
-    """Chooses the stage-3 implementation: "mma" (warp-level mma.sync) or "tcgen05" (tensor memory)."""
-    rc = _lib.lib().vmk_dsa_set_attend_variant({"mma": 0, "tcgen05": 1}[name])
+    """Chooses the stage-3 implementation: "mma" (warp-level mma.sync), "tcgen05" (tensor memory, rows gathered by
+    cp.async from four warps: the default) or "tcgen05_tma" (the same with the rows gathered by TMA tile::gather4)."""
+    rc = _lib.lib().vmk_dsa_set_attend_variant({"mma": 0, "tcgen05": 1, "tcgen05_tma": 2}[name])
     _lib.check(rc, "vmk_dsa_set_attend_variant")
