@@ -757,6 +757,8 @@ def main():
     ap.add_argument("--no-side", action="store_true", help="skip the per-op lines (`ops`)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--spec-batch", type=int, default=SPEC["B"], help="batch elements of the speculative-tree line (default: "
+                    "the configuration's 4; with fewer elements than ranks the caches are split by position)")
     ap.add_argument("--rounds", type=int, default=30, help="shuffled rounds per configuration of the per-op lines")
     ap.add_argument("--side-only", default=None, help="time only one configuration (prefix_small, spec_chain, "
                     "spec_tree, dsa_small, prefix_sweep, decode, decode_small, spec_tree_paged) on one GPU and print "
@@ -765,6 +767,7 @@ def main():
     a.warmup = max(a.warmup, 3) if a.impl == "ours" else a.warmup
     if a.impl == "reference":
         return reference_arm(a)
+    SPEC["B"] = a.spec_batch
 
     import torch
     from verified_metal_kernels_b200 import _lib, abbench, build, load_kernel, ops, shard

@@ -42,6 +42,7 @@ extern "C" {
 #define VMK_E_LAUNCH (-4)       /* the CUDA runtime rejected a launch */
 #define VMK_E_DRIVER (-5)       /* tensor-map encoding failed / driver entry point missing */
 #define VMK_E_TOO_LARGE (-6)    /* the problem needs more scratch than a built-in static buffer holds */
+#define VMK_E_NOMEM (-7)        /* the device had no room left for the library's static device buffers */
 
 #define VMK_DSA_TOPK 2048
 #define VMK_SPEC_MAX_DRAFTS 128
@@ -112,7 +113,14 @@ VMK_API int vmk_spec_verify_paged(const void* q, const void* k_pages, const void
  * so there is neither `ws` nor `ws_bytes`; inputs and output are still the caller's.
  *   - A shape whose partials would not fit is refused with VMK_E_TOO_LARGE before anything is launched;
  *     vmk_spec_workspace_bytes(...) <= VMK_SPEC_NOALLOC_SCRATCH_BYTES tells in advance.
- *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress); make
+ *   - The array becomes resident when the CUDA module that holds it is loaded on a device, which under the
+ *     runtime's default lazy loading is the first use of a kernel or symbol of that module -- typically the
+ *     first call of this entry point, not the loading of the library.  A host that claims all remaining
+ *     device memory for its own pools must therefore make one warm-up call on each device BEFORE it does so
+ *     (or run with CUDA_MODULE_LOADING=EAGER, which reserves the bytes when the library's context is set up);
+ *     otherwise that first call can fail with VMK_E_NOMEM, or take the bytes out of memory the host thinks it
+ *     owns.
+ *   - The first call on each device also looks up the array's device address (cudaGetSymbolAddress); make
  *     that first call before any stream capture begins on that device.
  *   - All calls on a device share the one array and it keeps the previous call's contents.  Nothing in
  *     it needs clearing, but calls whose kernels overlap on the GPU (different streams) race on it:

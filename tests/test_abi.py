@@ -82,6 +82,12 @@ def test_bad_arguments_are_rejected_before_any_launch(lib):
                                        None, None) == -1
     # misaligned pointer
     assert lib.vmk_prefix_decode(8, 16, 16, 16, 16, None, 16, 1, 32, 8, 128, 8, 8, 256, 1 << 20, None, None) == -1
+    # dsa: a bad LATE argument (the output pointer of stage 3) is refused before stage 1 enqueues anything -- here,
+    # without a GPU, an enqueue would come back as a launch failure (-4) instead
+    assert lib.vmk_dsa_decode(256, 256, 256, 256, 256, None, 8, None, None, 2, 4096, 256, 1 << 30, None, None) == -1
+    assert lib.vmk_dsa_decode(256, 256, 256, 256, 256, None, None, None, None, 2, 4096, 256, 1 << 30, None, None) == -1
+    assert lib.vmk_dsa_indexer_hist(256, 256, 256, None, 256, 256, 0, 4096, None, None) == -1          # B = 0
+    assert lib.vmk_dsa_indexer_hist(256, 256, 256, None, 256, 256, 70000, 4096, None, None) == -1      # B > 65535
 
 
 def test_kernel_modules_refuse_cpu_only_use():

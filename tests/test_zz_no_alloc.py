@@ -6,6 +6,7 @@ import numpy as np
 import pytest
 import torch
 
+from oracle import judge, ref64
 from verified_metal_kernels_b200 import _lib, ops
 
 pytestmark = pytest.mark.gpu
@@ -14,7 +15,8 @@ SCRATCH = 32 << 20
 
 def _run_pair(L, shape, seed, dist):
     op = ops.load_op("spec")
-    inp = ops.to_torch(op.make_inputs(shape, seed=seed, dist=dist), "cuda")
+    host = op.make_inputs(shape, seed=seed, dist=dist)
+    inp = ops.to_torch(host, "cuda")
     q, k, v, bits = inp["q"], inp["k"], inp["v"], inp["bits"]
     B, kd, Hq, D = q.shape
     Hkv, Lk = k.shape[1], k.shape[2]
@@ -34,6 +36,9 @@ def _run_pair(L, shape, seed, dist):
     assert rc == 0, _lib.error_string(rc)
     torch.cuda.synchronize()
     assert int(status.item()) == 0
+    # and directly against the float64 truth, with the acceptance criterion of the parity tests
+    rep = judge.judge_l2(out.float().cpu().numpy(), ref64.spec_ref64(**host), half=True)
+    assert rep["ok"], rep
     return out, ref
 
 

@@ -92,6 +92,7 @@ extern "C" const char* vmk_error_string(int code) {
     case VMK_E_LAUNCH: return "CUDA launch failed";
     case VMK_E_DRIVER: return "tensor-map encoding failed or the driver entry point is missing";
     case VMK_E_TOO_LARGE: return "the problem needs more scratch than the library's built-in static buffer holds";
+    case VMK_E_NOMEM: return "no device memory left for the library's static device buffers (load them before the host claims the rest)";
     default: return "unknown error code";
   }
 }

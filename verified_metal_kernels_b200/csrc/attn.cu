@@ -46,7 +46,12 @@ constexpr int kMaxParts = 640;     // upper bound of splits merged into one row 
 __global__ void __launch_bounds__(128) combine_kernel(const CombineParams p) {
   __shared__ float s_w[kMaxParts], s_l[kMaxParts];
   __shared__ const float* s_o[kMaxParts];
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (blockIdx.x == 0) ATTN_M(1024, 0);
+  // the next call's split kernel (a programmatic dependent of this grid) may be scheduled from here on: it sets
+  // itself up and waits for this grid to finish before it reads anything
+  pdl_release();
+  pdl_wait();
+  if (blockIdx.x == 0) ATTN_M(1024, 1);
   const int row = blockIdx.x;
   const int d = threadIdx.x;
   const int outer = row / p.Hq, hq = row % p.Hq;
@@ -80,6 +85,7 @@ __global__ void __launch_bounds__(128) combine_kernel(const CombineParams p) {
     acc += w * s_o[t][d];
     lsum += w * s_l[t];
   }
+  if (blockIdx.x == 0) ATTN_M(1024, 2);
   if (p.out != nullptr) {
     store16(&p.out[(size_t)row * kHD + d], acc / lsum, p.bf16);
   } else {
@@ -323,8 +329,18 @@ static int launch_attn_inst(const AttnParams& p, int n_cta, cudaStream_t stream)
     configured = true;
     configured_dev = dev;
   }
-  kern<<<n_cta, 256, smem, stream>>>(p);
-  return check_launch(cudaGetLastError());
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(n_cta);
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return check_launch(cudaLaunchKernelEx(&cfg, kern, p));
 }
 
 template <bool HAS_B, bool BF>
@@ -549,6 +565,13 @@ static int spec_impl(const void* q, const void* k, const void* v, const uint32_t
 // ------------------------------------------------------------------------------------------------
 using namespace vmk;
 
+#ifdef VMK_ATTN_TIMING
+extern "C" VMK_API int vmk_debug_attn_marks(long long* out) {
+  cudaDeviceSynchronize();
+  return (int)cudaMemcpyFromSymbol(out, g_attn_marks, sizeof(g_attn_marks));
+}
+#endif
+
 // 1: results of a row (a request's output) are bit-identical whatever else is in the batch, for every op of the
 // library, at the price of speed (fixed kernels, layouts and cut points instead of ones chosen for the batch).
 extern "C" VMK_API int vmk_set_batch_invariant(int on) {
@@ -657,8 +680,9 @@ extern "C" int vmk_spec_partial_packed(const void* q, const void* k, const void*
 // vmk_spec_verify_noalloc: the same kernels, with the split partials in a buffer that is part of the
 // library image instead of caller-provided scratch.
 //
-// g_spec_scratch is a file-scope device array: every GPU that loads the library reserves these bytes
-// until the process exits.  In host code the name is only a handle; the device address comes from
+// g_spec_scratch is a file-scope device array: every GPU on which this module gets loaded (at the first use of
+// one of its kernels or symbols, under the runtime's default lazy loading) reserves these bytes until the
+// process exits.  In host code the name is only a handle; the device address comes from
 // cudaGetSymbolAddress, taken once per device with that device current.  Every call on a device uses
 // the same bytes, which still hold the previous call's partials: the kernels write each partial before
 // the combine pass reads it, so nothing has to be cleared -- but two calls whose kernels overlap on the
@@ -673,7 +697,13 @@ static int spec_scratch_address(void** out) {
   void* ptr = __atomic_load_n(&cached[dev], __ATOMIC_ACQUIRE);
   if (ptr == nullptr) {
     // first call on this device: resolve the array's device address (not to be done during stream capture)
-    if (cudaGetSymbolAddress(&ptr, g_spec_scratch) != cudaSuccess || ptr == nullptr) return VMK_E_LAUNCH;
+    // (this is also what loads the module, and with it reserves the array, under lazy module loading)
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_spec_scratch);
+    if (e == cudaErrorMemoryAllocation) {
+      cudaGetLastError();                               // the failure is reported through the return code
+      return VMK_E_NOMEM;
+    }
+    if (e != cudaSuccess || ptr == nullptr) return VMK_E_LAUNCH;
     __atomic_store_n(&cached[dev], ptr, __ATOMIC_RELEASE);
   }
   *out = ptr;

@@ -60,6 +60,16 @@ struct AttnParams {
   int bf16;                 // q, K, V and out are bf16 instead of fp16
 };
 
+#ifdef VMK_ATTN_TIMING
+// Debug build only.  Global-timer stamps of every CTA of the last split-KV launch: [cta][mark], and of the
+// combine pass: [8 * 1024 + mark].
+__device__ long long g_attn_marks[8 * 1024 + 8];
+#define ATTN_M(cta, k) do { if (threadIdx.x == 0 && (cta) <= 1024) { long long _t; \
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); g_attn_marks[(cta) * 8 + (k)] = _t; } } while (0)
+#else
+#define ATTN_M(cta, k) do {} while (0)
+#endif
+
 template <int RT, int STAGES>
 constexpr int attn_smem_bytes() {
   return STAGES * kStageBytes + RT * 16 * kQStride + STAGES * 8 + 1024 /* alignment slack */;
@@ -81,6 +91,7 @@ __device__ __forceinline__ void attn_core(const AttnRole& R, float sc, int32_t* 
   const int nthreads = blockDim.x;
   const bool active = warp < NW;
   const int rt = warp / KS, ks = warp % KS;
+  ATTN_M(blockIdx.x, 0);
 
   // ---- which piece of work --------------------------------------------------------------------
   const int split = cta % R.nsplit;
@@ -90,6 +101,64 @@ __device__ __forceinline__ void attn_core(const AttnRole& R, float sc, int32_t* 
   const int zg = z / R.Hkv, h = z % R.Hkv;
   const int rows = R.rows_outer * R.G;
   const int row0 = tile * MT;
+  // Set-up that reads nothing a kernel before this one could have written: the barriers, the tensor-map
+  // descriptors, and L2 prefetches of the first key blocks of the range (hints: they need no shared memory, and
+  // a block beyond the group's true length is merely fetched for nothing).  The kernel is launched as a
+  // programmatic dependent, so in a chain of calls all this overlaps the tail of the call before; every read of
+  // the call's inputs stands after pdl_wait.
+  uint8_t* stage0 = smem;
+  uint8_t* sQ = smem + STAGES * kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sQ + MT * kQStride);
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) mbar_init(&bars[s], 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&R.tmK);
+    tma_prefetch_desc(&R.tmV);
+    if (R.page_table == nullptr) {
+      const int kb0 = R.key_lo + split * R.split_len;
+      const int ke0 = min(kb0 + R.split_len, R.key_hi);
+      for (int j = 0; j < STAGES && kb0 + j * kBK < ke0; ++j) {
+        tma_prefetch_3d(&R.tmK, 0, kb0 + j * kBK, z);
+        tma_prefetch_3d(&R.tmK, 64, kb0 + j * kBK, z);
+        tma_prefetch_3d(&R.tmV, 0, kb0 + j * kBK, z);
+        tma_prefetch_3d(&R.tmV, 64, kb0 + j * kBK, z);
+      }
+    }
+  }
+  pdl_wait();
+
+  // Every global load of the set-up is requested before any of them is waited for (on a cold cache each is a
+  // round trip to DRAM: taken one after the other they used to be most of a small call's time): this thread's
+  // part of the query tile, its draft-visibility words and the group's key count.
+  constexpr int kQPer = (MT * 16 + 255) / 256;          // 16-byte chunks of the query tile per thread (256 threads)
+  uint4 qreg[kQPer];
+#pragma unroll
+  for (int u = 0; u < kQPer; ++u) {
+    const int i = tid + u * nthreads;
+    const int r = i >> 4, c = i & 15;
+    const int row = row0 + r;
+    qreg[u] = make_uint4(0u, 0u, 0u, 0u);
+    if (i < MT * 16 && row < rows) {
+      const size_t outer = (size_t)zg * R.rows_outer + row / R.G;
+      const int head = h * R.G + row % R.G;
+      qreg[u] = *reinterpret_cast<const uint4*>(R.q + (outer * R.Hq + head) * kHD + c * 8);
+    }
+  }
+  // The two rows this thread owns in its warp's 16-row tile, and their draft-visibility words.
+  const int r_lo = row0 + rt * 16 + (lane >> 2), r_hi = r_lo + 8;
+  uint32_t mw_lo[kMaxMaskWords], mw_hi[kMaxMaskWords];
+#pragma unroll
+  for (int w = 0; w < kMaxMaskWords; ++w) mw_lo[w] = mw_hi[w] = 0xffffffffu;
+  if (R.bits != nullptr && active) {
+#pragma unroll
+    for (int w = 0; w < kMaxMaskWords; ++w) {
+      if (w < R.bits_words) {
+        if (r_lo < rows) mw_lo[w] = R.bits[((size_t)zg * R.rows_outer + r_lo / R.G) * R.bits_words + w];
+        if (r_hi < rows) mw_hi[w] = R.bits[((size_t)zg * R.rows_outer + r_hi / R.G) * R.bits_words + w];
+      }
+    }
+  }
+
   const int kbeg = R.key_lo + split * R.split_len;
   int kend = min(kbeg + R.split_len, R.key_hi);
   if (R.klens != nullptr) {
@@ -101,16 +170,7 @@ __device__ __forceinline__ void attn_core(const AttnRole& R, float sc, int32_t* 
     kend = min(kend, kv);
   }
   const int nblk = kend > kbeg ? (kend - kbeg + kBK - 1) / kBK : 0;
-
-  uint8_t* stage0 = smem;
-  uint8_t* sQ = smem + STAGES * kStageBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sQ + MT * kQStride);
-
-  if (tid == 0) {
-    for (int s = 0; s < STAGES; ++s) mbar_init(&bars[s], 1);
-    fence_mbar_init();
-  }
-  __syncthreads();
+  __syncthreads();                                      // the barriers are initialised
 
   auto issue = [&](int j) {
     const int s = j % STAGES;
@@ -135,16 +195,10 @@ __device__ __forceinline__ void attn_core(const AttnRole& R, float sc, int32_t* 
   }
 
   // ---- query tile -> shared memory -> A fragments ------------------------------------------------
-  for (int i = tid; i < MT * 16; i += nthreads) {
-    const int r = i >> 4, c = i & 15;
-    const int row = row0 + r;
-    uint4 val = make_uint4(0u, 0u, 0u, 0u);
-    if (row < rows) {
-      const size_t outer = (size_t)zg * R.rows_outer + row / R.G;
-      const int head = h * R.G + row % R.G;
-      val = *reinterpret_cast<const uint4*>(R.q + (outer * R.Hq + head) * kHD + c * 8);
-    }
-    *reinterpret_cast<uint4*>(sQ + r * kQStride + c * 16) = val;
+#pragma unroll
+  for (int u = 0; u < kQPer; ++u) {
+    const int i = tid + u * nthreads;
+    if (i < MT * 16) *reinterpret_cast<uint4*>(sQ + (i >> 4) * kQStride + (i & 15) * 16) = qreg[u];
   }
   __syncthreads();
 
@@ -155,20 +209,6 @@ __device__ __forceinline__ void attn_core(const AttnRole& R, float sc, int32_t* 
       ldsm_x4(qf[kk], smem_u32(sQ + (rt * 16 + (lane & 15)) * kQStride + (kk * 2 + (lane >> 4)) * 16));
   }
 
-  // The two rows this thread owns in its warp's 16-row tile, and their draft-visibility words.
-  const int r_lo = row0 + rt * 16 + (lane >> 2), r_hi = r_lo + 8;
-  uint32_t mw_lo[kMaxMaskWords], mw_hi[kMaxMaskWords];
-#pragma unroll
-  for (int w = 0; w < kMaxMaskWords; ++w) mw_lo[w] = mw_hi[w] = 0xffffffffu;
-  if (R.bits != nullptr && active) {
-#pragma unroll
-    for (int w = 0; w < kMaxMaskWords; ++w) {
-      if (w < R.bits_words) {
-        if (r_lo < rows) mw_lo[w] = R.bits[((size_t)zg * R.rows_outer + r_lo / R.G) * R.bits_words + w];
-        if (r_hi < rows) mw_hi[w] = R.bits[((size_t)zg * R.rows_outer + r_hi / R.G) * R.bits_words + w];
-      }
-    }
-  }
   auto visible = [&](const uint32_t (&mw)[kMaxMaskWords], int j) -> bool {
     uint32_t word = mw[0];
 #pragma unroll
@@ -176,6 +216,7 @@ __device__ __forceinline__ void attn_core(const AttnRole& R, float sc, int32_t* 
     return (word >> (j & 31)) & 1u;
   };
 
+  ATTN_M(blockIdx.x, 1);
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
   float oacc[16][4];
 #pragma unroll
@@ -186,10 +227,19 @@ __device__ __forceinline__ void attn_core(const AttnRole& R, float sc, int32_t* 
     const int s = j % STAGES;
     const bool arrived = mbar_wait(&bars[s], (uint32_t)((j / STAGES) & 1));
     if (__syncthreads_or(!arrived)) {   // also: every warp is done with block j-1
-      if (tid == 0) report(status, kStatusTimeout);
+      // Give up.  The loads already requested (blocks j .. j + STAGES - 2, or the first STAGES blocks) may still be
+      // landing in this CTA's shared memory: wait for them, with the same bound, so that the SM cannot hand the
+      // memory to another CTA under them.  The whole call's output is invalid once the status bit is set.
+      if (tid == 0) {
+        report(status, kStatusTimeout);
+        const int issued = min(nblk, j == 0 ? STAGES : j + STAGES - 1);
+        for (int b = j; b < issued; ++b) mbar_wait(&bars[b % STAGES], (uint32_t)((b / STAGES) & 1));
+      }
+      __syncthreads();
       return;
     }
     if (tid == 0 && j >= 1 && j - 1 + STAGES < nblk) issue(j - 1 + STAGES);
+    if (j == 0) ATTN_M(blockIdx.x, 2);
 
     uint8_t* st = stage0 + s * kStageBytes;
     const int kb = kbeg + j * kBK;
@@ -304,6 +354,7 @@ __device__ __forceinline__ void attn_core(const AttnRole& R, float sc, int32_t* 
 
   // ---- merge the KS key slices of each row tile, emit ------------------------------------------
   __syncthreads();   // every stage has been consumed; the ring is reused as the merge buffer
+  ATTN_M(blockIdx.x, 3);
   float* mo = reinterpret_cast<float*>(stage0);                      // [NW][16][kMergeStride]
   float* ml = mo + NW * 16 * kMergeStride;                           // [NW][16][2]
   if (active) {
@@ -326,35 +377,58 @@ __device__ __forceinline__ void attn_core(const AttnRole& R, float sc, int32_t* 
     }
   }
   __syncthreads();
-  const size_t slot = (size_t)z * R.nsplit + split;
-  for (int i = tid; i < MT * kHD; i += nthreads) {
-    const int row = i >> 7, d = i & 127;
-    const int grow = row0 + row;
-    if (grow >= rows) continue;
+  ATTN_M(blockIdx.x, 5);
+  // per row: the common maximum of its KS slices, their weights 2^(m_k - M) and the merged row sum, computed
+  // once (one thread per row) instead of once per output element
+  float* wts = ml + NW * 16 * 2;                                     // [MT][KS]
+  float* rowM = wts + MT * KS;                                       // [MT]
+  float* rowL = rowM + MT;                                           // [MT]
+  for (int row = tid; row < MT; row += nthreads) {
     const int wr = (row >> 4) * KS, rr = row & 15;
     float M = -INFINITY;
 #pragma unroll
     for (int k = 0; k < KS; ++k) M = fmaxf(M, ml[((wr + k) * 16 + rr) * 2]);
-    float acc = 0.f, lsum = 0.f;
+    float lsum = 0.f;
 #pragma unroll
     for (int k = 0; k < KS; ++k) {
       const float mk = ml[((wr + k) * 16 + rr) * 2];
       const float wgt = (mk == -INFINITY) ? 0.f : exp2f(mk - M);
-      acc += wgt * mo[((wr + k) * 16 + rr) * kMergeStride + d];
+      wts[row * KS + k] = wgt;
       lsum += wgt * ml[((wr + k) * 16 + rr) * 2 + 1];
+    }
+    rowM[row] = M;
+    rowL[row] = lsum;
+  }
+  __syncthreads();
+  const size_t slot = (size_t)z * R.nsplit + split;
+  for (int i = tid; i < MT * (kHD / 4); i += nthreads) {             // four columns per thread and step
+    const int row = i >> 5, d = (i & 31) * 4;
+    const int grow = row0 + row;
+    if (grow >= rows) continue;
+    const int wr = (row >> 4) * KS, rr = row & 15;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < KS; ++k) {
+      const float wgt = wts[row * KS + k];
+      const float4 v = *reinterpret_cast<const float4*>(mo + ((wr + k) * 16 + rr) * kMergeStride + d);
+      acc.x += wgt * v.x; acc.y += wgt * v.y; acc.z += wgt * v.z; acc.w += wgt * v.w;
     }
     if (R.direct) {
       const size_t outer = (size_t)zg * R.rows_outer + grow / R.G;
       const int head = h * R.G + grow % R.G;
-      store16(&R.out[(outer * R.Hq + head) * kHD + d], acc / lsum, BF);
+      const float lsum = rowL[row];
+      uint2 pk;
+      pk.x = pack2(acc.x / lsum, acc.y / lsum, BF);
+      pk.y = pack2(acc.z / lsum, acc.w / lsum, BF);
+      *reinterpret_cast<uint2*>(&R.out[(outer * R.Hq + head) * kHD + d]) = pk;
     } else {
-      R.part_o[(slot * R.MP + grow) * kHD + d] = acc;
-      if (d == 0) {
-        R.part_ml[(slot * R.MP + grow) * 2] = M;
-        R.part_ml[(slot * R.MP + grow) * 2 + 1] = lsum;
-      }
+      *reinterpret_cast<float4*>(R.part_o + (slot * R.MP + grow) * kHD + d) = acc;
+      if (d == 0) *reinterpret_cast<float2*>(R.part_ml + (slot * R.MP + grow) * 2) = make_float2(rowM[row], rowL[row]);
     }
   }
+  ATTN_M(blockIdx.x, 6);
+  __syncthreads();
+  ATTN_M(blockIdx.x, 4);
 }
 
 }  // namespace vmk

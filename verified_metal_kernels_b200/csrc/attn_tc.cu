@@ -88,9 +88,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
   const int row0 = tile * kTcRows;
   const bool has_b = row0 + 128 < rows;                 // tile B holds at least one real row
   const int kbeg = R.key_lo + split * R.split_len;
-  int kend = min(kbeg + R.split_len, R.key_hi);
-  if (R.klens != nullptr) kend = min(kend, max(0, min(R.klens[zg], R.klen)));
-  const int nblk = kend > kbeg ? (kend - kbeg + kTcBK - 1) / kTcBK : 0;
 
   if (tid == 0) {
     for (int s = 0; s < kTcSlots; ++s) {
@@ -106,21 +103,46 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
     fence_mbar_init();
   }
   if (warp == 1) tmem_alloc(tmem_slot, kTcCols);
+  if (warp == 0 && lane == 0) {
+    // hints that start the HBM reads of the first tiles early (no shared memory, no barrier); like the barrier
+    // and tensor-memory set-up above they touch nothing a kernel before this one could have written
+    tma_prefetch_desc(&R.tmK);
+    tma_prefetch_desc(&R.tmV);
+    if (R.page_table == nullptr) {
+      const int ke0 = min(kbeg + R.split_len, R.key_hi);
+      for (int j = 0; j < 2 && kbeg + j * kTcBK < ke0; ++j) {
+        for (int y = 0; y < kTcBK; y += 64) {
+          tma_prefetch_3d(&R.tmK, 0, kbeg + j * kTcBK + y, z);
+          tma_prefetch_3d(&R.tmK, 64, kbeg + j * kTcBK + y, z);
+          tma_prefetch_3d(&R.tmV, 0, kbeg + j * kTcBK + y, z);
+          tma_prefetch_3d(&R.tmV, 64, kbeg + j * kTcBK + y, z);
+        }
+      }
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // launched as a programmatic dependent: in a chain of calls everything above overlaps the tail of the call
+  // before; the inputs are read only below this line
+  pdl_wait();
+  int kend = min(kbeg + R.split_len, R.key_hi);
+  if (R.klens != nullptr) kend = min(kend, max(0, min(R.klens[zg], R.klen)));
+  const int nblk = kend > kbeg ? (kend - kbeg + kTcBK - 1) / kTcBK : 0;
 
   bool timed_out = false;
   if (warp == 0) {
     // ------------------------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      int issued = 0;                                     // tiles requested so far
       for (int i = 0; i < 2 * nblk; ++i) {
         const int s = i % kTcSlots;
         if (i >= kTcSlots && !mbar_wait(&empty[s], (uint32_t)(((i / kTcSlots) - 1) & 1))) {
           timed_out = true;
           break;
         }
+        issued = i + 1;
         const CUtensorMap* tm = (i & 1) ? &R.tmV : &R.tmK;
         const int kb = kbeg + (i >> 1) * kTcBK;
         uint8_t* dst = sKV + s * kKvTile;
@@ -143,6 +165,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) attn_tc_kernel(const __grid_con
         tma_load_3d(dst + kKvHalf, tm, 64, y0, z0, &full[s]);
         tma_load_3d(dst + kKvHalf + kKvHalf / 2, tm, 64, y1, z1, &full[s]);
       }
+      // No load outlives the CTA: the newest tile of every slot has landed before this warp goes to the exit.  In a
+      // run without a timeout the consumers have waited for all of them already and these return at once; when a
+      // consumer gave up, this keeps the SM from handing the shared memory to another CTA under a late load.
+      for (int i = max(0, issued - kTcSlots); i < issued; ++i)
+        mbar_wait(&full[i % kTcSlots], (uint32_t)((i / kTcSlots) & 1));
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------------------ Q.K^T issuer
@@ -448,8 +475,18 @@ int launch_attn_tc(const AttnParams& p, int n_cta, cudaStream_t stream) {
     if (e != cudaSuccess) return check_launch(e);
     configured_dev = dev;
   }
-  attn_tc_kernel<<<n_cta, kTcThreads, kAttnTcSmem, stream>>>(p);
-  return check_launch(cudaGetLastError());
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(n_cta);
+  cfg.blockDim = dim3(kTcThreads);
+  cfg.dynamicSmemBytes = kAttnTcSmem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return check_launch(cudaLaunchKernelEx(&cfg, attn_tc_kernel, p));
 }
 
 }  // namespace vmk

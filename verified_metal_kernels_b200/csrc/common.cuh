@@ -89,6 +89,18 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* tm, in
       : "memory");
 }
 
+// Prefetch of one box into L2 (no shared memory, no barrier): a hint that starts the HBM read early.
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* tm, int x, int y, int z) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(tm), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+
+// Programmatic dependent launch.  pdl_wait: block until every grid this one depends on has completed and its
+// writes are visible (returns at once when the launch was an ordinary one).  pdl_release: allow the grid
+// launched after this one with programmatic stream serialisation to start being scheduled.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* tm, int x, int y, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"

@@ -523,15 +523,24 @@ struct DsaPages {
 
 // bf16 = 1: the 16-bit tensors of the call are bf16 (only the tcgen05 implementations take them, and only they
 // take a paged cache).
-static int indexer_impl(const void* iq, const void* ik, const float* w, const int32_t* lens, float* scores,
-                        uint32_t* hist, int B, int L, int32_t* status, cudaStream_t stream, int variant, int bf16 = 0,
-                        DsaPages pg = DsaPages{nullptr, 0, 0, 0}) {
+// Argument checks of stage 1, separate from the launch so that the entry points can run every check of a call
+// before they enqueue anything (a refused call leaves the stream and the outputs untouched).
+static int indexer_check(const void* iq, const void* ik, const float* w, const float* scores, int B, int L, int variant,
+                         int bf16, const DsaPages& pg) {
   if (!iq || !ik || !w || !scores || B <= 0 || L <= 0) return VMK_E_BADARG;
   if ((bf16 || pg.pages > 0) && variant != 1) return VMK_E_UNSUPPORTED;
   if (pg.pages > 0 && (!pg.table || pg.page_size < kIdxTile || pg.page_size % kIdxTile != 0 || pg.table_stride <= 0 ||
                        (long long)pg.table_stride * pg.page_size < L))
     return VMK_E_BADARG;
   if (!aligned16(iq) || !aligned16(ik) || B > 65535) return VMK_E_BADARG;
+  return VMK_OK;
+}
+
+static int indexer_impl(const void* iq, const void* ik, const float* w, const int32_t* lens, float* scores,
+                        uint32_t* hist, int B, int L, int32_t* status, cudaStream_t stream, int variant, int bf16 = 0,
+                        DsaPages pg = DsaPages{nullptr, 0, 0, 0}) {
+  const int bad = indexer_check(iq, ik, w, scores, B, L, variant, bf16, pg);
+  if (bad) return bad;
   if (L <= kTopK) return VMK_OK;                        // nothing to rank
   IndexerParams p;
   memset(&p, 0, sizeof(p));
@@ -557,14 +566,21 @@ static int indexer_impl(const void* iq, const void* ik, const float* w, const in
   return check_launch(cudaGetLastError());
 }
 
-static int attend_impl(const void* q, const void* kv, const int32_t* idx, const int32_t* cnt, void* out, int B,
-                       int L, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream, int bf16 = 0,
-                       DsaPages pg = DsaPages{nullptr, 0, 0, 0}) {
+static int attend_check(const void* q, const void* kv, const int32_t* idx, const int32_t* cnt, const void* out, int B,
+                        int L, const void* ws, size_t ws_bytes, int bf16, const DsaPages& pg) {
   if (!q || !kv || !idx || !cnt || !out || B <= 0 || L <= 0) return VMK_E_BADARG;
   if ((bf16 || pg.pages > 0) && g_attend_variant == 0) return VMK_E_UNSUPPORTED;
   if (!aligned16(q) || !aligned16(kv) || !aligned16(out) || B > 65535) return VMK_E_BADARG;
-  const int ns = mla_splits(B);
   if (!ws || ws_bytes < attend_ws(B) || (reinterpret_cast<uintptr_t>(ws) & 255)) return VMK_E_WORKSPACE;
+  return VMK_OK;
+}
+
+static int attend_impl(const void* q, const void* kv, const int32_t* idx, const int32_t* cnt, void* out, int B,
+                       int L, void* ws, size_t ws_bytes, int32_t* status, cudaStream_t stream, int bf16 = 0,
+                       DsaPages pg = DsaPages{nullptr, 0, 0, 0}) {
+  const int bad = attend_check(q, kv, idx, cnt, out, B, L, ws, ws_bytes, bf16, pg);
+  if (bad) return bad;
+  const int ns = mla_splits(B);
   MlaParams p;
   memset(&p, 0, sizeof(p));
   p.q = static_cast<const __half*>(q);
@@ -645,6 +661,8 @@ extern "C" int vmk_dsa_indexer(const void* iq, const void* ik, const float* w, c
 extern "C" int vmk_dsa_indexer_hist(const void* iq, const void* ik, const float* w, const int32_t* lens, float* scores,
                                     uint32_t* hist, int B, int L, int32_t* status, void* stream) {
   if (!hist) return VMK_E_BADARG;
+  const int bad = indexer_check(iq, ik, w, scores, B, L, 1, 0, DsaPages{nullptr, 0, 0, 0});
+  if (bad) return bad;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(hist, 0, (size_t)B * kSelBins * 4, st) != cudaSuccess) return VMK_E_LAUNCH;
   return indexer_impl(iq, ik, w, lens, scores, hist, B, L, status, st, 1);
@@ -685,6 +703,10 @@ static int decode_impl(const void* q, const void* kv, const void* iq, const void
   float* scores = reinterpret_cast<float*>(base + pl.off_scores);
   int32_t* idx = idx_out ? idx_out : reinterpret_cast<int32_t*>(base + pl.off_idx);
   int32_t* cnt = cnt_out ? cnt_out : reinterpret_cast<int32_t*>(base + pl.off_cnt);
+  // every argument check of the three stages before the first thing is enqueued
+  int bad = indexer_check(iq, ik, w, scores, B, L, g_indexer_variant, bf16, pg);
+  if (!bad) bad = attend_check(q, kv, idx, cnt, out, B, L, base + pl.off_attend, attend_ws(B), bf16, pg);
+  if (bad) return bad;
   // The tcgen05 indexer also accumulates the first radix level of the select (a 2048-bin histogram per
   // request); the mma.sync variant does not, and the select then builds it in a pass of its own.
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -716,7 +738,9 @@ extern "C" int vmk_dsa_decode_bf16(const void* q, const void* kv, const void* iq
 
 extern "C" int vmk_dsa_indexer_hist_bf16(const void* iq, const void* ik, const float* w, const int32_t* lens,
                                          float* scores, uint32_t* hist, int B, int L, int32_t* status, void* stream) {
-  if (!hist || B <= 0) return VMK_E_BADARG;
+  if (!hist) return VMK_E_BADARG;
+  const int bad = indexer_check(iq, ik, w, scores, B, L, 1, 1, DsaPages{nullptr, 0, 0, 0});
+  if (bad) return bad;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(hist, 0, (size_t)B * kSelBins * 4, st) != cudaSuccess) return VMK_E_LAUNCH;
   return indexer_impl(iq, ik, w, lens, scores, hist, B, L, status, st, 1, 1);
