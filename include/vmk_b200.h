@@ -300,6 +300,13 @@ VMK_API int vmk_lse_merge_packed(const float* records, int parts, int rows, int 
  *   takes 2 = the tcgen05 kernel with its rows gathered by TMA (tile::gather4) instead of cp.async; the result has
  *   the same bits.  Other values are refused. */
 VMK_API int vmk_attn_set_tc(int on);
+/*   vmk_prefix_set_side_by_side(0): a prefix call with 512 or more private suffixes (requests x kv heads) and more
+ *   than 64 stacked rows runs its tensor-bound prefix kernel and its HBM-bound suffix kernel one after the other on the caller's
+ *   stream, instead of side by side (1, the default: the prefix kernel takes one wave on two thirds of the SMs and
+ *   the suffix kernel runs on a second stream the library creates per device, forked from and joined to the
+ *   caller's stream by events; the results have the same bits unless the prefix is cut into a different number
+ *   of splits). */
+VMK_API int vmk_prefix_set_side_by_side(int on);
 VMK_API int vmk_dsa_set_indexer_variant(int variant);
 VMK_API int vmk_dsa_set_attend_variant(int variant);
 

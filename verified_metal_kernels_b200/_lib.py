@@ -49,6 +49,7 @@ SIGNATURES = {
     "vmk_spec_partial_packed": (_i, [_vp] * 4 + [_i] * 11 + [_vp, _vp, _sz, _vp, _vp]),
     "vmk_lse_merge_packed": (_i, [_vp] + [_i] * 4 + [_vp, _vp]),
     "vmk_attn_set_tc": (_i, [_i]),
+    "vmk_prefix_set_side_by_side": (_i, [_i]),
     "vmk_dsa_set_indexer_variant": (_i, [_i]),
     "vmk_dsa_set_attend_variant": (_i, [_i]),
 }

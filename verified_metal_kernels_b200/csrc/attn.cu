@@ -160,6 +160,7 @@ int launch_attn_tc(const AttnParams& p, int n_cta, cudaStream_t stream);   // at
 int g_batch_invariant = 0;
 
 static int g_attn_tc = 1;   // 1: row tiles of 128 run on tcgen05 (attn_tc.cu); 0: always the warp-level kernel
+static int g_side_by_side = 1;   // 1: big prefix calls run their two kernels at the same time (see PrefixPlan)
 constexpr int kTcRowsMin = 65;     // stacked rows from which the tensor-memory kernel is used
 constexpr int kTcSplitCap = 32;
 
@@ -193,7 +194,9 @@ static int tc_split_cap(int units) {
 // tcgen05 path: one CTA per SM, 256-row tiles, 128-key blocks.  The split count minimises
 // waves x (blocks per CTA + a fixed per-CTA overhead of about three blocks), which avoids a mostly empty
 // last wave.
-static void plan_role_tc(RolePlan* r, int groups, int rows, int keys) {
+// one_wave_on > 0: the CTAs must fit ONE wave on that many SMs (the rest of the GPU is left to a kernel that runs
+// beside this one); the largest split count that does is taken.
+static void plan_role_tc(RolePlan* r, int groups, int rows, int keys, int one_wave_on = 0) {
   constexpr int kTcBlock = 128;      // keys per block of the tensor-memory kernel
   r->tc = true;
   r->rt = 8; r->ks = 1;
@@ -208,6 +211,10 @@ static void plan_role_tc(RolePlan* r, int groups, int rows, int keys) {
   for (int ns = 1; ns <= cap && ns <= blocks; ++ns) {
     const int per = cdiv(blocks, ns);
     const int real = cdiv(blocks, per);
+    if (one_wave_on > 0) {
+      if (units * real <= one_wave_on || real == 1) best = real;      // ascending: ends at the largest that fits
+      continue;
+    }
     const long long cost = (long long)cdiv(units * real, sms) * (per + 3);
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = real; }
   }
@@ -229,10 +236,10 @@ static void plan_role_invariant(RolePlan* r, int groups, int rows, int keys, boo
   r->n_cta = groups * r->row_tiles * r->nsplit;
 }
 
-static void plan_role(RolePlan* r, int groups, int rows, int keys, int target, bool fixed_small) {
+static void plan_role(RolePlan* r, int groups, int rows, int keys, int target, bool fixed_small, int one_wave_on = 0) {
   r->tc = false;
   if (g_batch_invariant) { plan_role_invariant(r, groups, rows, keys, fixed_small); return; }
-  if (!fixed_small && g_attn_tc && rows >= kTcRowsMin) { plan_role_tc(r, groups, rows, keys); return; }
+  if (!fixed_small && g_attn_tc && rows >= kTcRowsMin) { plan_role_tc(r, groups, rows, keys, one_wave_on); return; }
   if (fixed_small) { r->rt = 1; r->ks = 4; } else pick_layout(rows, &r->rt, &r->ks);
   const int mt = r->rt * 16;
   r->row_tiles = cdiv(rows, mt);
@@ -262,8 +269,15 @@ static size_t place(RolePlan* r, int groups, size_t off, int cap) {
 struct PrefixPlan {
   RolePlan a, b;
   bool has_a, has_b;       // shared-prefix role (keys [key_lo, key_hi) not empty), private-suffix role
+  bool side_by_side;       // the tensor-bound prefix tiles and the HBM-bound suffix streams run at the same time
   size_t ws_bytes;
 };
+
+// From this many private suffixes (request x kv head) on, a call whose shared prefix runs on the tensor-memory
+// kernel gives that kernel one wave on about two thirds of the SMs and streams the suffixes beside it on a second
+// stream.  The rule looks at the number of suffixes, not at their length: the length bound S of a paged call is
+// rounded up to whole pages, and the paged and the contiguous call must cut the work alike.
+constexpr int kSideBySideGroups = 512;
 
 static PrefixPlan plan_prefix(int N, int Hq, int Hkv, int P, int S, int key_lo, int key_hi, bool with_suffix) {
   PrefixPlan pl;
@@ -285,10 +299,14 @@ static PrefixPlan plan_prefix(int N, int Hq, int Hkv, int P, int S, int key_lo, 
     pl.b = RolePlan{};
   }
   size_t off = 0;
+  pl.side_by_side = false;
   if (pl.has_a) {
     int target_a = 2 * sms - target_b;
     if (target_a < sms) target_a = sms;
-    plan_role(&pl.a, Hkv, N * G, key_hi - key_lo, target_a, false);
+    const bool big_suffix = pl.has_b && (long long)N * Hkv >= kSideBySideGroups;
+    const bool tc_rows = !g_batch_invariant && g_attn_tc && N * G >= kTcRowsMin;
+    pl.side_by_side = big_suffix && tc_rows && g_side_by_side;
+    plan_role(&pl.a, Hkv, N * G, key_hi - key_lo, target_a, false, pl.side_by_side ? (2 * sms) / 3 : 0);
     off = place(&pl.a, Hkv, 0, pl.a.tc ? tc_split_cap(Hkv * pl.a.row_tiles) : cdiv(2 * sms, Hkv * pl.a.row_tiles));
   } else {
     pl.a = RolePlan{};
@@ -416,6 +434,34 @@ static int role_tmaps(AttnRole* r, const void* k, const void* v, int keys, uint6
 
 // pg_a / pg_b: page tables of the shared prefix (one row) and of the private suffixes (one row per request);
 // with pages > 0, kp/vp and ks/vs all point at the page pool.
+// The library's second stream of a device and the two events that fork it from, and join it to, the caller's
+// stream.  Created at the first call that needs them (no device memory involved); calls on one device share
+// them, which is correct for any order of calls (every use is bracketed by its own fork and join) but makes the
+// suffix kernels of concurrent calls queue behind one another.  Works under stream capture: the fork pulls the
+// second stream into the capture and the join hands it back.
+struct SideStream {
+  cudaStream_t stream;
+  cudaEvent_t fork, join;
+};
+static SideStream* side_stream() {
+  static SideStream made[64];
+  static bool ready[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!ready[dev]) {
+    SideStream s;
+    if (cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;                                   // the call then runs its kernels one after the other
+    }
+    made[dev] = s;
+    ready[dev] = true;
+  }
+  return &made[dev];
+}
+
 // q_heads: heads per request in q's memory (the distance between two requests' rows, in heads); Hq when the
 // call covers every head, larger when q points at a slice of heads [h0, h0 + Hq) of a wider tensor.
 static int prefix_impl(const void* q, const void* kp, const void* vp, const void* ks, const void* vs,
@@ -470,11 +516,24 @@ static int prefix_impl(const void* q, const void* kp, const void* vp, const void
   if (pl.has_a && pl.has_b) {
     if (pl.a.tc) {
       // shared prefix on the tensor-memory kernel, private suffixes on the warp-level kernel
-      rc = launch_attn_tc(p, pl.a.n_cta, stream);
-      if (rc) return rc;
       AttnParams ps = p;
       ps.a = p.b;
-      rc = launch_attn<false>(ps, 1, pl.b.n_cta, stream);
+      SideStream* side = pl.side_by_side ? side_stream() : nullptr;
+      if (side != nullptr) {
+        // fork: the suffix streams go to the library's second stream and fill whatever SMs the prefix tiles leave
+        if (cudaEventRecord(side->fork, stream) != cudaSuccess || cudaStreamWaitEvent(side->stream, side->fork, 0) != cudaSuccess)
+          return check_launch(cudaGetLastError());
+        rc = launch_attn_tc(p, pl.a.n_cta, stream);
+        if (rc) return rc;
+        rc = launch_attn<false>(ps, 1, pl.b.n_cta, side->stream);
+        if (rc) return rc;
+        if (cudaEventRecord(side->join, side->stream) != cudaSuccess || cudaStreamWaitEvent(stream, side->join, 0) != cudaSuccess)
+          return check_launch(cudaGetLastError());
+      } else {
+        rc = launch_attn_tc(p, pl.a.n_cta, stream);
+        if (rc) return rc;
+        rc = launch_attn<false>(ps, 1, pl.b.n_cta, stream);
+      }
     } else {
       rc = launch_attn<true>(p, pl.a.rt, pl.a.n_cta + pl.b.n_cta, stream);
     }
@@ -576,6 +635,13 @@ extern "C" VMK_API int vmk_debug_attn_marks(long long* out) {
 // library, at the price of speed (fixed kernels, layouts and cut points instead of ones chosen for the batch).
 extern "C" VMK_API int vmk_set_batch_invariant(int on) {
   g_batch_invariant = on ? 1 : 0;
+  return VMK_OK;
+}
+
+// A/B switch: 1 = a prefix call with a large suffix volume runs its prefix tiles (one wave on two thirds of the
+// SMs) and its suffix streams at the same time on two streams (default), 0 = one after the other.
+extern "C" VMK_API int vmk_prefix_set_side_by_side(int on) {
+  g_side_by_side = on ? 1 : 0;
   return VMK_OK;
 }
 
