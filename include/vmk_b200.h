@@ -249,6 +249,18 @@ VMK_API int vmk_dsa_indexer_hist_fp8(const void* iq8, const float* iq_scale, con
                                      const float* w, const int32_t* lens, float* scores, uint32_t* hist, int B, int L,
                                      int32_t* status, void* stream);
 
+/* The step before stage 1: the projection that produces the indexer's queries and head weights, which the
+ * reference keeps outside its op (ops/dsa.py:8-9 names the projections that produce q / iq / w as not part of it;
+ * there is no reference kernel or truth for it: the float64 statement lives in oracle/ref64.py).
+ *   x (B, Dx) activation; wq (8192, Dx), ww (64, Dx): weights stored (out features, in features) as a linear layer
+ *   keeps them; all three fp16 (bf16 = 0) or bf16 (1); Dx a multiple of 8.
+ *   iq_out (B, 64, 128), same 16-bit type: iq[b, h, d] = sum_k x[b, k] * wq[h * 128 + d, k], fp32 accumulation,
+ *   rounded once.  w_out (B, 64) fp32: w[b, h] = w_scale * sum_k x[b, k] * ww[h, k].
+ * Both outputs are what vmk_dsa_decode / vmk_dsa_indexer_hist take as iq and w.  Positional encodings, if the model
+ * applies any to its index queries, are the caller's to apply between the two calls. */
+VMK_API int vmk_dsa_index_project(const void* x, const void* wq, const void* ww, float w_scale, void* iq_out,
+                                  float* w_out, int B, int Dx, int bf16, int32_t* status, void* stream);
+
 /* ---- merge of split partials -------------------------------------------------------------------
  * Log-sum-exp merge used after a KV split across GPUs (the reference merges its in-GPU splits the
  * same way, kernels/prefix_opus55_v8.py:211-261).  m, l (parts,rows) and o (parts,rows,D) fp32 with m

@@ -133,6 +133,15 @@ def dsa_ref64(q, kv, iq, ik, w, lens=None, sel=None, **_):
     return out
 
 
+def dsa_index_project64(x, wq, ww, w_scale=1.0):
+    """The projection in front of the indexer, which the reference keeps outside its op (ops/dsa.py:8-9) and has no
+    truth for: iq (B,64,128) = x @ wq^T and w (B,64) = w_scale * x @ ww^T in float64, unrounded.  x (B,Dx);
+    wq (8192,Dx), ww (64,Dx) stored (out features, in features)."""
+    x, wq, ww = _f64(x), _f64(wq), _f64(ww)
+    iq = (x @ wq.T).reshape(x.shape[0], 64, 128)
+    return iq, float(w_scale) * (x @ ww.T)
+
+
 REF64 = dict(prefix=prefix_ref64, spec=spec_ref64, dsa=dsa_ref64)
 
 

@@ -42,6 +42,7 @@ SIGNATURES = {
     "vmk_dsa_attend": (_i, [_vp] * 5 + [_i] * 2 + [_vp, _sz, _vp, _vp]),
     "vmk_dsa_attend_bf16": (_i, [_vp] * 5 + [_i] * 2 + [_vp, _sz, _vp, _vp]),
     "vmk_dsa_gather": (_i, [_vp] * 5 + [_i] * 2 + [_vp, _vp]),
+    "vmk_dsa_index_project": (_i, [_vp] * 3 + [_c.c_float] + [_vp] * 2 + [_i] * 3 + [_vp, _vp]),
     "vmk_lse_merge": (_i, [_vp] * 3 + [_i] * 3 + [_vp, _vp]),
     "vmk_prefix_partial": (_i, [_vp] * 6 + [_i] * 9 + [_vp] * 3 + [_vp, _sz, _vp, _vp]),
     "vmk_spec_partial": (_i, [_vp] * 4 + [_i] + [_i] * 8 + [_vp] * 3 + [_vp, _sz, _vp, _vp]),

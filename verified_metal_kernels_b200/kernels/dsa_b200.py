@@ -216,6 +216,35 @@ def indexer_hist_fp8(iq8, iq_scale, ik8, ik_scale, w, lens=None):
     return scores, hist
 
 
+def index_project(x, wq, ww, w_scale=1.0):
+    """The projection in front of stage 1 (outside the reference's op, ops/dsa.py:8-9): x (B,Dx) activation,
+    wq (8192,Dx) and ww (64,Dx) weights stored (out, in), all fp16 or all bf16 -> (iq (B,64,128) of the same type,
+    w (B,64) fp32 = w_scale * x @ ww^T), the `iq` and `w` inputs of kernel()."""
+    dt = _half(x, "x")
+    need(x, "x", dt, dims=2)
+    B, Dx = x.shape
+    need(wq, "wq", dt, shape=(HI * DI, Dx))
+    need(ww, "ww", dt, shape=(HI, Dx))
+    if Dx % 8 != 0:
+        raise ValueError("Dx must be a multiple of 8")
+    dev = x.device
+    with torch.cuda.device(dev):
+        iq = torch.empty(B, HI, DI, dtype=dt, device=dev)
+        w = torch.empty(B, HI, dtype=torch.float32, device=dev)
+        rc = _lib.lib().vmk_dsa_index_project(_lib.ptr(x), _lib.ptr(wq), _lib.ptr(ww), float(w_scale), _lib.ptr(iq),
+                                              _lib.ptr(w), B, Dx, 1 if dt == torch.bfloat16 else 0,
+                                              _lib.ptr(_lib.status_word(dev)), torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "vmk_dsa_index_project")
+    return iq, w
+
+
+def kernel_projected(q, kv, x, wq, ww, ik, w_scale=1.0, lens=None, return_selection=False, check=False):
+    """The op with the indexer's queries and head weights computed here from the activation x (B,Dx) and the
+    projection weights (see index_project), then the usual three stages."""
+    iq, w = index_project(x, wq, ww, w_scale)
+    return kernel(q, kv, iq, ik, w, lens, return_selection=return_selection, check=check)
+
+
 def kernel_fp8_index(q, kv, iq8, iq_scale, ik8, ik_scale, w, lens=None, return_selection=False):
     """The op with the index queries and keys in fp8 (q and kv stay fp16 or bf16): stage 1 on fp8, then the
     usual select and sparse attention."""
