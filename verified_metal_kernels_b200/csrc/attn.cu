@@ -39,13 +39,18 @@ struct CombineParams {
 
 constexpr int kMaxParts = 640;     // upper bound of splits merged into one row (both sides together)
 
-// One CTA of 128 threads per output row (outer, head).  The (m, l) pairs of every split are fetched in
-// parallel (one per thread) into shared memory, turned into weights 2^(m - M), and thread d then merges
-// column d with independent loads.  Launched with programmatic stream serialisation: the grid may be
-// scheduled while the split kernel is still running and waits here for its results.
-__global__ void __launch_bounds__(128) combine_kernel(const CombineParams p) {
-  __shared__ float s_w[kMaxParts], s_l[kMaxParts];
-  __shared__ const float* s_o[kMaxParts];
+// One CTA of NG x 32 threads per output row (outer, head): NG groups of 32 lanes; group g merges the splits
+// t = g, g + NG, g + 2 NG, ... and lane l owns columns [4 l, 4 l + 4).  Every thread requests its first four
+// partial rows (4 NG splits per CTA) at once, before the (m, l) pairs that give them their weights have even
+// arrived, so that a row of the usual 9-37 splits costs one round trip to L2 instead of one per eight splits;
+// the group sums meet in shared memory.  NG = 8 for decode-sized calls (few rows, many splits: latency is all
+// there is), NG = 4 when there are thousands of rows.  Launched with programmatic stream serialisation: the grid
+// may be scheduled while the split kernel is still running and waits here for its results.
+template <int NG>
+__global__ void __launch_bounds__(NG * 32) combine_kernel(const CombineParams p) {
+  __shared__ float s_m[kMaxParts], s_l[kMaxParts];
+  __shared__ float4 s_red[NG][32];
+  __shared__ float s_lred[NG];
   if (blockIdx.x == 0) ATTN_M(1024, 0);
   // the next call's split kernel (a programmatic dependent of this grid) may be scheduled from here on: it sets
   // itself up and waits for this grid to finish before it reads anything
@@ -53,64 +58,109 @@ __global__ void __launch_bounds__(128) combine_kernel(const CombineParams p) {
   pdl_wait();
   if (blockIdx.x == 0) ATTN_M(1024, 1);
   const int row = blockIdx.x;
-  const int d = threadIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, grp = tid >> 5;
   const int outer = row / p.Hq, hq = row % p.Hq;
   const int h = hq / p.G, g = hq % p.G;
   const int nA = p.a.nsplit, nB = p.has_b ? p.b.nsplit : 0;
   const int total = min(nA + nB, kMaxParts);
-  for (int t = d; t < total; t += 128) {
+  // index of split t's record of this row in its side's partial arrays
+  auto record = [&](int t, const CombineSide** side) -> size_t {
     const CombineSide& sd = t < nA ? p.a : p.b;
     const int s = t < nA ? t : t - nA;
     const int z = (outer / sd.rows_outer) * p.Hkv + h;
     const int r = (outer % sd.rows_outer) * p.G + g;
-    const size_t i = ((size_t)z * sd.nsplit + s) * sd.MP + r;
-    const float2 ml = *reinterpret_cast<const float2*>(sd.part_ml + i * 2);
-    s_w[t] = ml.x;
+    *side = &sd;
+    return ((size_t)z * sd.nsplit + s) * sd.MP + r;
+  };
+  float4 o[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int t = grp + NG * k;
+    o[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (t < total) {
+      const CombineSide* sd;
+      const size_t i = record(t, &sd);
+      o[k] = *reinterpret_cast<const float4*>(sd->part_o + i * kHD + lane * 4);
+    }
+  }
+  for (int t = tid; t < total; t += NG * 32) {
+    const CombineSide* sd;
+    const size_t i = record(t, &sd);
+    const float2 ml = *reinterpret_cast<const float2*>(sd->part_ml + i * 2);
+    s_m[t] = ml.x;
     s_l[t] = ml.y;
-    s_o[t] = sd.part_o + i * kHD;
   }
   __syncthreads();
   float M = -INFINITY;
-  for (int t = 0; t < total; ++t) M = fmaxf(M, s_w[t]);
-  __syncthreads();
-  for (int t = d; t < total; t += 128) {
-    const float m = s_w[t];
-    s_w[t] = (m == -INFINITY) ? 0.f : exp2f(m - M);
+  for (int t = 0; t < total; ++t) M = fmaxf(M, s_m[t]);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float lsum = 0.f;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int t = grp + NG * k;
+    if (t < total) {
+      const float m = s_m[t];
+      const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
+      acc.x += w * o[k].x; acc.y += w * o[k].y; acc.z += w * o[k].z; acc.w += w * o[k].w;
+      lsum += w * s_l[t];
+    }
   }
-  __syncthreads();
-  float acc = 0.f, lsum = 0.f;
-#pragma unroll 8
-  for (int t = 0; t < total; ++t) {
-    const float w = s_w[t];
-    acc += w * s_o[t][d];
+  for (int t = grp + 4 * NG; t < total; t += NG) {        // rows with more than 4 NG splits: the rest, one by one
+    const CombineSide* sd;
+    const size_t i = record(t, &sd);
+    const float4 v = *reinterpret_cast<const float4*>(sd->part_o + i * kHD + lane * 4);
+    const float m = s_m[t];
+    const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
+    acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
     lsum += w * s_l[t];
   }
+  s_red[grp][lane] = acc;
+  if (lane == 0) s_lred[grp] = lsum;
+  __syncthreads();
+  if (tid >= 32) return;
+  acc = s_red[0][lane];
+  lsum = s_lred[0];
+#pragma unroll
+  for (int q = 1; q < NG; ++q) {
+    const float4 v = s_red[q][lane];
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    lsum += s_lred[q];
+  }
   if (blockIdx.x == 0) ATTN_M(1024, 2);
+  const int d = lane * 4;
   if (p.out != nullptr) {
-    store16(&p.out[(size_t)row * kHD + d], acc / lsum, p.bf16);
+    uint2 pk;
+    pk.x = pack2(acc.x / lsum, acc.y / lsum, p.bf16);
+    pk.y = pack2(acc.z / lsum, acc.w / lsum, p.bf16);
+    *reinterpret_cast<uint2*>(&p.out[(size_t)row * kHD + d]) = pk;
   } else {
-    p.po[(size_t)row * p.o_stride + d] = acc;
-    if (d == 0) {
+    float* po = p.po + (size_t)row * p.o_stride + d;      // packed records start 8 bytes into the row: scalar stores
+    po[0] = acc.x; po[1] = acc.y; po[2] = acc.z; po[3] = acc.w;
+    if (lane == 0) {
       p.pm[(size_t)row * p.ml_stride] = M;
       p.pl[(size_t)row * p.ml_stride] = lsum;
     }
   }
 }
 
+int g_batch_invariant = 0;
+
 // Launch of the combine pass as a programmatic dependent of the kernel enqueued just before it.
 static int launch_combine(const CombineParams& c, int rows, cudaStream_t stream) {
   if (c.a.nsplit + (c.has_b ? c.b.nsplit : 0) > kMaxParts) return VMK_E_UNSUPPORTED;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
+  // (batch-invariant mode: one fixed variant, so that a row's sum order does not depend on the row count)
+  const bool few_rows = g_batch_invariant || rows <= 2048;
   cfg.gridDim = dim3(rows);
-  cfg.blockDim = dim3(128);
+  cfg.blockDim = dim3(few_rows ? 256 : 128);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return check_launch(cudaLaunchKernelEx(&cfg, combine_kernel, c));
+  return check_launch(few_rows ? cudaLaunchKernelEx(&cfg, combine_kernel<8>, c) : cudaLaunchKernelEx(&cfg, combine_kernel<4>, c));
 }
 
 // Merge of `parts` partials per row (used after an exchange between GPUs).
@@ -157,7 +207,6 @@ __global__ void __launch_bounds__(128) lse_merge_packed_kernel(const float* __re
 // ------------------------------------------------------------------------------------------------
 int launch_attn_tc(const AttnParams& p, int n_cta, cudaStream_t stream);   // attn_tc.cu
 
-int g_batch_invariant = 0;
 
 static int g_attn_tc = 1;   // 1: row tiles of 128 run on tcgen05 (attn_tc.cu); 0: always the warp-level kernel
 static int g_side_by_side = 1;   // 1: big prefix calls run their two kernels at the same time (see PrefixPlan)

@@ -62,10 +62,10 @@ struct AttnParams {
 
 #ifdef VMK_ATTN_TIMING
 // Debug build only.  Global-timer stamps of every CTA of the last split-KV launch: [cta][mark], and of the
-// combine pass: [8 * 1024 + mark].
-__device__ long long g_attn_marks[8 * 1024 + 8];
+// combine pass: [16 * 1024 + mark].
+__device__ long long g_attn_marks[16 * 1025];
 #define ATTN_M(cta, k) do { if (threadIdx.x == 0 && (cta) <= 1024) { long long _t; \
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); g_attn_marks[(cta) * 8 + (k)] = _t; } } while (0)
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); g_attn_marks[(cta) * 16 + (k)] = _t; } } while (0)
 #else
 #define ATTN_M(cta, k) do {} while (0)
 #endif
@@ -126,6 +126,7 @@ __device__ __forceinline__ void attn_core(const AttnRole& R, float sc, int32_t* 
     }
   }
   pdl_wait();
+  ATTN_M(blockIdx.x, 8);
 
   // Every global load of the set-up is requested before any of them is waited for (on a cold cache each is a
   // round trip to DRAM: taken one after the other they used to be most of a small call's time): this thread's
@@ -170,7 +171,9 @@ __device__ __forceinline__ void attn_core(const AttnRole& R, float sc, int32_t* 
     kend = min(kend, kv);
   }
   const int nblk = kend > kbeg ? (kend - kbeg + kBK - 1) / kBK : 0;
+  ATTN_M(blockIdx.x, 9);
   __syncthreads();                                      // the barriers are initialised
+  ATTN_M(blockIdx.x, 10);
 
   auto issue = [&](int j) {
     const int s = j % STAGES;
@@ -193,6 +196,7 @@ __device__ __forceinline__ void attn_core(const AttnRole& R, float sc, int32_t* 
   if (tid == 0) {
     for (int j = 0; j < STAGES && j < nblk; ++j) issue(j);
   }
+  ATTN_M(blockIdx.x, 11);
 
   // ---- query tile -> shared memory -> A fragments ------------------------------------------------
 #pragma unroll
@@ -201,6 +205,7 @@ __device__ __forceinline__ void attn_core(const AttnRole& R, float sc, int32_t* 
     if (i < MT * 16) *reinterpret_cast<uint4*>(sQ + (i >> 4) * kQStride + (i & 15) * 16) = qreg[u];
   }
   __syncthreads();
+  ATTN_M(blockIdx.x, 12);
 
   uint32_t qf[8][4];
   if (active) {
