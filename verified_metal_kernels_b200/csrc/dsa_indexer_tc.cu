@@ -68,6 +68,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int b = blockIdx.y;
+  // the top-k selection is launched as a programmatic dependent of this grid: it may set itself up from here on,
+  // and waits for this grid to finish before it reads the scores
+  pdl_release();
   int n = p.L;
   if (p.lens != nullptr) n = max(0, min(p.lens[b], p.L));
   if (n <= kTopK) return;                                   // uniform: nothing to rank for this request

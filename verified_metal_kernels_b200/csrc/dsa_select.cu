@@ -302,12 +302,23 @@ __global__ void __launch_bounds__(kSelThreads, 1) select_kernel(const float* __r
   const int b = CLUSTER ? blockIdx.x / csize : blockIdx.x;
   const int crank = CLUSTER ? blockIdx.x % csize : 0;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // Set-up that reads nothing the indexer writes: this kernel is itself a programmatic dependent of it, so the
+  // shared-memory clearing and the first cluster barrier overlap the indexer's tail.
+  if (tid == 0) {
+    sh.overflow = 0u;
+    sh.total = 0u;
+  }
+  for (int i = tid; i < kSelBins; i += kSelThreads) sh.acc2[i] = sh.acc3[i] = 0u;
+  __syncthreads();
+  if (CLUSTER) cg::this_cluster().sync();         // rank 0's accumulators are clear before any peer adds to them
+  pdl_wait();                                     // scores, histogram and lengths are read below this line
+
   int n = L;
   if (lens != nullptr) n = max(0, min(lens[b], L));
   const float* s = scores + (size_t)b * L;
   int32_t* out = idx + (size_t)b * kTopK;
 
-  if (n <= kTopK) {                            // uniform across the cluster: nobody reaches a cluster barrier
+  if (n <= kTopK) {                            // uniform across the cluster: nobody reaches a later cluster barrier
     if (crank == 0) {
       for (int i = tid; i < kTopK; i += kSelThreads) out[i] = i < n ? i : 0;
       if (tid == 0) cnt[b] = n;
@@ -319,13 +330,6 @@ __global__ void __launch_bounds__(kSelThreads, 1) select_kernel(const float* __r
   const int pbeg = min(n, crank * part), pend = min(n, pbeg + part);
   const int span = ((pend - pbeg + 31) / 32 + 3) & ~3;
   const int beg = min(pend, pbeg + warp * span), end = min(pend, beg + span);
-  if (tid == 0) {
-    sh.overflow = 0u;
-    sh.total = 0u;
-  }
-  for (int i = tid; i < kSelBins; i += kSelThreads) sh.acc2[i] = sh.acc3[i] = 0u;
-  __syncthreads();
-  if (CLUSTER) cg::this_cluster().sync();         // rank 0's accumulators are clear before any peer adds to them
 
 #ifdef VMK_SEL_TIMING
   long long _t0 = clock64();
@@ -535,17 +539,29 @@ static int launch_select(const float* scores, const uint32_t* hist, const int32_
     cfg.blockDim = dim3(kSelThreads);
     cfg.dynamicSmemBytes = kSelSmem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = kSelCluster;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     return check_launch(cudaLaunchKernelEx(&cfg, select_kernel<EPL, true>, scores, hist, lens, idx, cnt, L, kSelCluster));
   }
-  select_kernel<EPL, false><<<B, kSelThreads, kSelSmem, stream>>>(scores, hist, lens, idx, cnt, L, 1);
-  return check_launch(cudaGetLastError());
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)B);
+  cfg.blockDim = dim3(kSelThreads);
+  cfg.dynamicSmemBytes = kSelSmem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return check_launch(cudaLaunchKernelEx(&cfg, select_kernel<EPL, false>, scores, hist, lens, idx, cnt, L, 1));
 }
 
 int select_launch(const float* scores, const uint32_t* hist, const int32_t* lens, int32_t* idx, int32_t* cnt, int B,
