@@ -307,10 +307,11 @@ VMK_API int vmk_lse_merge_packed(const float* records, int parts, int rows, int 
  * No counterpart in the reference (its variants are separate kernel files).  Each returns VMK_OK.
  *   vmk_attn_set_tc(0): prefix / spec row tiles of more than 64 rows use the warp-level kernel instead of
  *   the tcgen05 one (1, the default).
- *   vmk_dsa_set_indexer_variant(v), vmk_dsa_set_attend_variant(v): 1 = tcgen05 kernels (default), 0 = the
- *   warp-level mma.sync kernels kept as cross-checks (fp16, contiguous caches only).  The attend stage also
- *   takes 2 = the tcgen05 kernel with its rows gathered by TMA (tile::gather4) instead of cp.async; the result has
- *   the same bits.  Other values are refused. */
+ *   vmk_dsa_set_indexer_variant(v), vmk_dsa_set_attend_variant(v): 1 = tcgen05 kernels (the indexer's default),
+ *   0 = the warp-level mma.sync kernels kept as cross-checks (fp16, contiguous caches only).  The attend stage
+ *   also takes 2 = the tcgen05 kernel of 1 with its rows gathered by TMA (tile::gather4) instead of cp.async (the
+ *   result has the same bits) and 3 = the tcgen05 kernel that gives a request to a cluster of two CTAs which
+ *   share the score product (its default).  Other values are refused. */
 VMK_API int vmk_attn_set_tc(int on);
 /*   vmk_prefix_set_side_by_side(0): a prefix call with 512 or more private suffixes (requests x kv heads) and more
  *   than 64 stacked rows runs its tensor-bound prefix kernel and its HBM-bound suffix kernel one after the other on the caller's

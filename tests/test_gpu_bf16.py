@@ -60,7 +60,7 @@ def test_dsa_bf16_needs_the_tensor_memory_kernels():
             dsa_b200.kernel(**d)
         assert e.value.code == -2
     finally:
-        dsa_b200.set_attend_variant("tcgen05")
+        dsa_b200.set_attend_variant(dsa_b200.DEFAULT_ATTEND_VARIANT)
 
 
 prefix = ops.load_op("prefix")

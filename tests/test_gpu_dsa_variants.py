@@ -53,8 +53,9 @@ def test_ragged_and_full_op(variant):
 
 @pytest.mark.parametrize("B,dist", [(1, "randn"), (3, "large"), (8, "randn"), (40, "needle")])
 def test_attend_variants_agree(B, dist):
-    """Stage 3 on tcgen05 (Q in tensor memory, output accumulated in registers) against the warp-level
-    kernel and the oracle, on random selections with short and full counts."""
+    """Stage 3 on tcgen05 (Q in tensor memory, output accumulated in registers; one CTA per request and value
+    half, or a cluster of two per request) against the warp-level kernel and the oracle, on random selections
+    with short and full counts."""
     L = 3000
     rng = np.random.default_rng(100 + B)
     inp = op.make_inputs(dict(B=B, L=L), seed=43, dist=dist)
@@ -72,17 +73,18 @@ def test_attend_variants_agree(B, dist):
     d = _verify.device_inputs("dsa", inp)
     ti, tc_ = torch.from_numpy(idx).cuda(), torch.from_numpy(cnt).cuda()
     outs = {}
-    for v in ("tcgen05", "tcgen05_tma", "mma"):
+    for v in ("tcgen05_pair", "tcgen05", "tcgen05_tma", "mma"):
         dsa_b200.set_attend_variant(v)
         try:
             outs[v] = dsa_b200.attend(d["q"], d["kv"], ti, tc_).float().cpu().numpy()
         finally:
-            dsa_b200.set_attend_variant("tcgen05")
+            dsa_b200.set_attend_variant(dsa_b200.DEFAULT_ATTEND_VARIANT)
     _verify.assert_clean_status()
     t = ref64.dsa_ref64(inp["q"], inp["kv"], None, None, None, sel=sel)
     for v, o in outs.items():
         rep = judge.judge_l2(o, t, half=True, dist=dist)
         assert rep["ok"] and rep["err_max"] <= 2e-3, (v, rep)
     assert judge.nerr(outs["tcgen05"], outs["mma"])[0] <= 2e-3
+    assert judge.nerr(outs["tcgen05_pair"], outs["tcgen05"])[0] <= 2e-3
     # the two gathers fill the same shared-memory tiles, so everything after them sees the same bits
     assert np.array_equal(outs["tcgen05"], outs["tcgen05_tma"], equal_nan=True)

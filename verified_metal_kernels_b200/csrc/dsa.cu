@@ -457,7 +457,9 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const __half* __restri
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-static int g_attend_variant = 1;    // 0 = warp-level mma.sync kernel, 1 = tcgen05 kernel (default), 2 = the same with a TMA row gather
+// 0 = warp-level mma.sync kernel, 1 = tcgen05 kernel, one CTA per (request, value half), 2 = the same with a TMA row
+// gather, 3 = tcgen05 kernel, a cluster of two CTAs per request (default)
+static int g_attend_variant = 3;
 
 // Key splits of the warp-level kernel.
 static int mla_splits(int B) {
@@ -477,7 +479,9 @@ static size_t attend_ws(int B) {
   const int ns = mla_splits(B);
   const size_t warp_level =
       ns == 1 ? 256 : align_up((size_t)B * ns * kMH * kDV * 4, 256) + align_up((size_t)B * ns * kMH * 2 * 4, 256);
-  const size_t tc = mla_tc_workspace(B);
+  size_t tc = mla_tc_workspace(B);
+  const size_t pair = mla_pair_workspace(B);
+  if (pair > tc) tc = pair;
   return warp_level > tc ? warp_level : tc;
 }
 
@@ -614,6 +618,10 @@ static int attend_impl(const void* q, const void* kv, const int32_t* idx, const 
     t.B = B; t.L = L; t.ncta = 0; t.sc = p.sc; t.status = status; t.bf16 = bf16;
     t.page_table = pg.pages > 0 ? pg.table : nullptr;
     t.page_size = pg.page_size; t.table_stride = pg.table_stride; t.pages = pg.pages;
+    if (g_attend_variant >= 3) {
+      t.gather_tma = g_attend_variant == 4 ? 1 : 0;
+      return mla_pair_launch(t, static_cast<float*>(ws), stream);
+    }
     return mla_tc_launch(t, static_cast<float*>(ws), stream);
   }
   static int configured_dev = -1;
@@ -637,10 +645,11 @@ static int g_indexer_variant = 1;   // 0 = mma.sync (warp-level), 1 = tcgen05 + 
 
 using namespace vmk;
 
-// Test hook: chooses the stage-3 implementation (0 = warp-level mma.sync, 1 = tcgen05 with the rows gathered by
-// cp.async from four warps (default), 2 = tcgen05 with the rows gathered by TMA tile::gather4).
+// Test hook: chooses the stage-3 implementation (0 = warp-level mma.sync, 1 = tcgen05, one CTA per (request, value
+// half), rows gathered by cp.async from four warps, 2 = the same with the rows gathered by TMA tile::gather4,
+// 3 = tcgen05, a cluster of two CTAs per request that share the score product (default)).
 extern "C" VMK_API int vmk_dsa_set_attend_variant(int v) {
-  if (v < 0 || v > 2) return VMK_E_BADARG;
+  if (v < 0 || v > 4) return VMK_E_BADARG;
   g_attend_variant = v;
   return VMK_OK;
 }

@@ -7,7 +7,7 @@
 // may cross from one request into the next: the index queries are double-buffered in shared memory, the head
 // weights and the histogram are switched between requests by the epilogue warps.  Warp-specialised:
 //   warp 0     TMA producer: a request's 16 KiB of index queries, then its 32 KiB ik tiles into a 5-deep
-//              shared-memory ring (128-byte swizzle)
+//              shared-memory ring (128-byte swizzle; ten 16 KiB slots with fp8 keys)
 //   warp 1     (and warp 10 for fp8 keys) allocates tensor memory, issues 8 tcgen05.mma (M128 N64 K16) per tile
 //              into one of four accumulator buffers, commits the ring slot back to the producer and the
 //              accumulator to the epilogue
@@ -32,7 +32,7 @@ constexpr int kTmemCols = kAccs * kHI;                 // 256
 constexpr int kTcThreads = 352;
 // ring | iq x 2 | w | histogram | barriers | tmem base
 constexpr int kTcSmem =
-    kStages * kTileBytes + 2 * kIqBytes + kHI * 4 + kSelBins * 4 + (2 * kStages + 2 * kAccs + 4) * 8 + 16 + 1024;
+    kStages * kTileBytes + 2 * kIqBytes + kHI * 4 + kSelBins * 4 + (4 * kStages + 2 * kAccs + 4) * 8 + 16 + 1024;
 
 struct TcParams {
   CUtensorMap tmIK;      // (B, L, 128) box (64, 128, 1), 128-byte swizzle
@@ -84,7 +84,10 @@ __device__ __forceinline__ bool next_run(const TcParams& p, RunWalk& w, int g0, 
 template <bool FP8>
 __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_constant__ TcParams p) {
   constexpr int kTileLoad = FP8 ? kTileBytes / 2 : kTileBytes;   // bytes one tile brings in = size of a ring slot
-  constexpr int kSt = kStages;                                   // ring slots (twice as many fp8 slots were no faster)
+  // Ring slots.  With fp8 keys there are two issuing threads on alternate tiles, and the number of slots must be
+  // EVEN so that a slot always comes back to the same thread: a thread that ran ahead and asked for a slot that still
+  // holds the other thread's earlier tile would see the parity of the phase before and take the old tile for its own.
+  constexpr int kSt = FP8 ? 2 * kStages : kStages;
   constexpr int kIqLoad = FP8 ? kIqBytes / 2 : kIqBytes;
   constexpr int kIssuers = FP8 ? 2 : 1;
   constexpr int kSets = FP8 ? 2 : 1;

@@ -30,6 +30,11 @@ struct MlaTcParams {
 int mla_tc_launch(const MlaTcParams& p, float* workspace, cudaStream_t stream);
 size_t mla_tc_workspace(int B);
 
+// The same stage by clusters of two CTAs per request that share the score product (dsa_mla_pair.cu).  Uses q, kv,
+// idx, cnt, out, tmQ and the paging fields; part_o is then (((cluster * 2 + k) * 128 + column / 4) * 128 + head) * 4.
+int mla_pair_launch(const MlaTcParams& p, float* workspace, cudaStream_t stream);
+size_t mla_pair_workspace(int B);
+
 // Tiled tensor map over a 16-bit tensor viewed as (rows, width) with `width` contiguous, box (64, 1), 128-byte
 // swizzle: rows are fetched four at a time by cp.async.bulk.tensor ... tile::gather4.  Returns 0 or a VMK_E_* code.
 int make_tmap_rows(CUtensorMap* tm, const void* base, uint64_t width, uint64_t rows);

@@ -298,8 +298,14 @@ def set_indexer_variant(name):
     _lib.check(rc, "vmk_dsa_set_indexer_variant")
 
 
+ATTEND_VARIANTS = {"mma": 0, "tcgen05": 1, "tcgen05_tma": 2, "tcgen05_pair": 3, "tcgen05_pair_n128": 4}
+DEFAULT_ATTEND_VARIANT = "tcgen05_pair"
+
+
 def set_attend_variant(name):
-    """Chooses the stage-3 implementation: "mma" (warp-level mma.sync), "tcgen05" (tensor memory, rows gathered by
-    cp.async from four warps: the default) or "tcgen05_tma" (the same with the rows gathered by TMA tile::gather4)."""
-    rc = _lib.lib().vmk_dsa_set_attend_variant({"mma": 0, "tcgen05": 1, "tcgen05_tma": 2}[name])
+    """Chooses the stage-3 implementation: "mma" (warp-level mma.sync), "tcgen05" (tensor memory, one CTA per
+    request and value half, rows gathered by cp.async from four warps), "tcgen05_tma" (the same with the rows
+    gathered by TMA tile::gather4) or "tcgen05_pair" (tensor memory, a cluster of two CTAs per request that share
+    the score product: the default)."""
+    rc = _lib.lib().vmk_dsa_set_attend_variant(ATTEND_VARIANTS[name])
     _lib.check(rc, "vmk_dsa_set_attend_variant")
