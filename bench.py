@@ -793,7 +793,7 @@ def main():
     ap.add_argument("--spec-batch", type=int, default=SPEC["B"], help="batch elements of the speculative-tree line (default: "
                     "the configuration's 4; with fewer elements than ranks the caches are split by position)")
     ap.add_argument("--rounds", type=int, default=30, help="shuffled rounds per configuration of the per-op lines")
-    ap.add_argument("--attend-variant", default=None, choices=["mma", "tcgen05", "tcgen05_tma", "tcgen05_pair", "tcgen05_pair_n128"],
+    ap.add_argument("--attend-variant", default=None, choices=["mma", "tcgen05", "tcgen05_tma", "tcgen05_pair"],
                     help="dsa stage 3 implementation (default: the library's, tcgen05_pair); for A/B runs")
     ap.add_argument("--side-only", default=None, help="time only one configuration (prefix_small, spec_chain, "
                     "spec_tree, dsa_small, prefix_sweep, decode, decode_small, spec_tree_paged) on one GPU and print "

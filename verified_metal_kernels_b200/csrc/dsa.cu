@@ -618,10 +618,7 @@ static int attend_impl(const void* q, const void* kv, const int32_t* idx, const 
     t.B = B; t.L = L; t.ncta = 0; t.sc = p.sc; t.status = status; t.bf16 = bf16;
     t.page_table = pg.pages > 0 ? pg.table : nullptr;
     t.page_size = pg.page_size; t.table_stride = pg.table_stride; t.pages = pg.pages;
-    if (g_attend_variant >= 3) {
-      t.gather_tma = g_attend_variant == 4 ? 1 : 0;
-      return mla_pair_launch(t, static_cast<float*>(ws), stream);
-    }
+    if (g_attend_variant == 3) return mla_pair_launch(t, static_cast<float*>(ws), stream);
     return mla_tc_launch(t, static_cast<float*>(ws), stream);
   }
   static int configured_dev = -1;
@@ -649,7 +646,7 @@ using namespace vmk;
 // half), rows gathered by cp.async from four warps, 2 = the same with the rows gathered by TMA tile::gather4,
 // 3 = tcgen05, a cluster of two CTAs per request that share the score product (default)).
 extern "C" VMK_API int vmk_dsa_set_attend_variant(int v) {
-  if (v < 0 || v > 4) return VMK_E_BADARG;
+  if (v < 0 || v > 3) return VMK_E_BADARG;
   g_attend_variant = v;
   return VMK_OK;
 }

@@ -6,27 +6,36 @@
 // 8 instructions of P.V: 44 x 96 = 4.25 k cycles per 64 keys, 36 of the 44 spent on a product the other half
 // computes as well.  Here the two CTAs of a cluster take one request together:
 //   * CTA r computes the partial scores over HALF of the 576 contraction elements (r = 0: elements [0,288),
-//     r = 1: [288,576); 18 instructions instead of 36) and adds its peer's partial, which the peer's softmax
-//     threads store straight into this CTA's shared memory (distributed shared memory; the sum has the same
-//     bits on both sides because the addition commutes), so both CTAs hold the same S, P, m and l;
-//   * CTA r owns value columns [256 r, 256 r + 256): its P.V is four instructions of N = 256 (138 cycles each)
-//     into a 256-column scratch of tensor memory, added to register accumulators by the softmax threads;
+//     r = 1: [288,576); 18 instructions instead of 36).  Four exchange warps take them out of tensor memory into a
+//     staging buffer and send them on to the peer with one asynchronous shared-memory-to-shared-memory copy per warp
+//     (8 KiB each, completing on a barrier in the peer's shared memory).  Every softmax thread adds the two halves
+//     in the same order, so both CTAs hold the same S, P, m and l;
+//   * CTA r owns value columns [256 r, 256 r + 256): its P.V is four instructions of N = 256 (138 cycles each) that
+//     ACCUMULATE O in tensor memory.  The softmax threads keep a reference maximum that follows the true one lazily
+//     (raised only when a block exceeds it by more than 2^8, so that P stays far inside the 16-bit range); only then
+//     is O read, rescaled and written back, which after a request's first block is rare.  The result is the same
+//     quotient: numerator and denominator carry the same factor;
 //   * CTA r therefore gathers only column blocks [4 r, 4 r + 5) of every selected row (its value columns, which
 //     are also its share of the contraction; block 4 goes to both): 40 KiB per 64 keys instead of 72.
-// Floor: 18 x 96.5 + 4 x 138 = 2.3 k cycles per 64 keys.
+// Floor of the tensor pipe: 18 x 96.5 + 4 x 138 = 2.3 k cycles per 64 keys.  What sets the period in practice is the
+// chain of the softmax threads (3.5-3.8 k cycles per block): the copy of a block's 32 KiB of partial scores takes
+// about 2 k cycles to cross, which is why it is issued by warps of its own, a block ahead of the softmax.
 // The B requests x 32 block slots form one list, cut into equal contiguous ranges, one per cluster; a request
 // cut by a range boundary leaves (m, l, o) partials, at most two per cluster, merged by mla_pair_combine_kernel.
-// Shared memory: a ring of four 40 KiB slots (per request two entries of staged queries, then the key blocks:
-// five [64 rows][128 B] blocks with the 128-byte swizzle) and the 32 KiB exchange buffer the peer writes.
-// One CTA = 512 threads in four warp groups (setmaxnreg: 208 registers for the softmax threads, 48 for the rest):
+// Shared memory: a ring of three 40 KiB slots (per request two entries of staged queries, then the key blocks:
+// five [64 rows][128 B] blocks with the 128-byte swizzle), two 32 KiB staging buffers and the 32 KiB buffer the
+// peer's copies land in.  One CTA = 576 threads:
 //   warps 0-3   softmax group A, warps 4-7 group B: one thread per head and group.  A takes keys [0,32) of each
-//               block and value columns [0,128) of the CTA's half, B keys [32,64) and columns [128,256)
-//   warps 8-11  gather by cp.async: warp w fetches rows [16 w, 16 w + 16) of every key block
+//               block and value columns [0,128) of the CTA's half (when O is rescaled or written out), B keys
+//               [32,64) and columns [128,256); the two threads of a head exchange block maxima through shared memory
+//   warps 8-11  gather by cp.async: warp w fetches rows [16 w, 16 w + 16) of every key block; positions are
+//               loaded a block ahead, and the rows of the block three ahead are asked into L2
 //   warp 12     issues S = Q.K^T (A = the queries, kept in tensor memory)
 //   warp 13     owns tensor memory and issues P.V (A = P from tensor memory)
+//   warps 14-17 exchange (above)
 // Every mbarrier wait is bounded; a wait that runs out sets the status word and the CTA winds down through the
-// common exit, where both CTAs meet at a cluster barrier (nobody leaves while its peer may still write to its
-// shared memory) and tensor memory is freed.  No load of this kernel uses cluster multicast.
+// common exit, where both CTAs meet at a cluster barrier (nobody leaves while its peer may still copy into its
+// shared memory) and tensor memory is freed.  Nothing here is a multicast: every copy has one destination.
 #include "dsa_mla_tc.cuh"
 #include "tcgen05.cuh"
 
@@ -40,9 +49,11 @@ constexpr int kBlkBytes = kBK * 128;                  // one [64 rows][128 B] sw
 constexpr int kSlotBlocks = 5;                        // column blocks a CTA holds per key block
 constexpr int kSlot = kSlotBlocks * kBlkBytes;        // 40 KiB
 constexpr int kStages = 3;
-constexpr int kThreads = 448;
+constexpr int kThreads = 576;
 constexpr int kGatherWarps = 4, kWarpGather0 = 8;     // warps 8..11
 constexpr int kWarpQK = 12, kWarpPV = 13;
+constexpr int kWarpExch0 = 14;                        // warps 14..17: partial scores out of tensor memory, to the peer
+constexpr int kPrefetch = 3;                          // key blocks the L2 prefetch runs ahead of the gather
 constexpr float kLazy = 8.f;                          // how far (log2) a block maximum may exceed the reference maximum
 constexpr int kQEntries = 2;                          // ring entries that stage a request's queries
 constexpr int kKSteps = 18;                           // K = 16 steps of the contraction per CTA
@@ -51,9 +62,9 @@ constexpr int kColS = 160;                            // 64 columns: partial sco
 constexpr int kColT = 224;                            // 256 columns: O, the output accumulator of the CTA's value half
 constexpr int kColP = 480;                            // 32 columns: P as packed pairs
 constexpr int kCols = 512;
-constexpr int kXBytes = 128 * kBK * 4;                // partial scores of a block: [softmax warp][float4 i of 8][lane]
-constexpr int kBars = 2 * kStages + 13;
-constexpr int kSmem = kStages * kSlot + 2 * kXBytes + kBars * 8 + 16 + 8 * 128 * 4 + 1024;
+constexpr int kXBytes = 128 * kBK * 4;                // partial scores of a block: [lane quarter][float4 i of 16][lane]
+constexpr int kBars = 2 * kStages + 17;
+constexpr int kSmem = kStages * kSlot + 3 * kXBytes + kBars * 8 + 16 + 8 * 128 * 4 + 1024;
 
 constexpr int kUnitSlots = kTopK / kBK;               // 32 block slots per request
 constexpr int kMinSlotsPerCluster = 2;
@@ -125,6 +136,10 @@ __device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_addr, const void*
                "r"(smem_u32(src)), "r"(bytes), "r"(bar_addr)
                : "memory");
 }
+// Asks for `bytes` (a multiple of 16) of global memory to be brought into L2.
+__device__ __forceinline__ void l2_prefetch(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -145,20 +160,22 @@ __global__ void __launch_bounds__(kThreads, 1) mla_pair_kernel(const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;                                   // [stages][5 blocks][64 rows][128 B]
-  float4* xsend = reinterpret_cast<float4*>(sK + kStages * kSlot);          // our partial scores, staged for the copy
-  float4* xbuf = xsend + kXBytes / 16;                                      // the peer's, written by its copy
+  float4* xsend = reinterpret_cast<float4*>(sK + kStages * kSlot);          // [2] our partial scores, staged for the copy
+  float4* xbuf = xsend + 2 * (kXBytes / 16);                                // the peer's, written by its copy
   uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(xbuf) + kXBytes);   // entry landed
   uint64_t* empty = full + kStages;                     // entry consumed                       (MMA commit)
   uint64_t* q_full = empty + kStages;                   // Q stored to tensor memory            (8 warps)
   uint64_t* s_full = q_full + 1;                        // partial scores ready                 (MMA commit)
-  uint64_t* s_free = s_full + 1;                        // partial scores consumed              (8 warps)
+  uint64_t* s_free = s_full + 1;                        // partial scores out of tensor memory  (4 warps)
   uint64_t* p_full = s_free + 1;                        // P in tensor memory, O rescaled       (8 warps)
   uint64_t* pv_done = p_full + 1;                       // P.V added to O                       (MMA commit)
   uint64_t* o_free = pv_done + 1;                       // a request's O has been written out   (8 warps)
   uint64_t* x_full = o_free + 1;                        // the peer's partial scores are here   (1 arrival + 32 KiB)
   uint64_t* x_free = x_full + 1;                        // the peer has read what we sent       (8 peer warps)
   uint64_t* xch = x_free + 1;                           // [4] pair of warps that share 32 heads exchanged values
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xch + 4);
+  uint64_t* xs_full = xch + 4;                          // [2] our partial scores are staged    (4 warps)
+  uint64_t* xs_free = xs_full + 2;                      // [2] ... and have been read           (8 warps)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xs_free + 2);
   float* smax = reinterpret_cast<float*>(tmem_slot + 4);    // [2 parities][2 groups][128 heads] block maxima
   float* ssum = smax + 4 * 128;                             // [2 parities][2 groups][128 heads] row sums
 
@@ -176,7 +193,11 @@ __global__ void __launch_bounds__(kThreads, 1) mla_pair_kernel(const __grid_cons
     }
     mbar_init(q_full, 8);
     mbar_init(s_full, 1);
-    mbar_init(s_free, 8);
+    mbar_init(s_free, 4);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&xs_full[i], 4);
+      mbar_init(&xs_free[i], 8);
+    }
     mbar_init(p_full, 8);
     mbar_init(pv_done, 1);
     mbar_init(o_free, 8);
@@ -194,6 +215,8 @@ __global__ void __launch_bounds__(kThreads, 1) mla_pair_kernel(const __grid_cons
   // Launched as a programmatic dependent: everything above overlaps the tail of the kernel before (the top-k
   // selection, in the fused call); the candidate lists and counts are read only below this line.
   pdl_wait();
+  int nblk_total = 0;                                   // key blocks of this CTA's whole range
+  for (int u = u_first; u <= u_last; ++u) nblk_total += unit_work(p, u, slot0, slot1).nblk;
 
   bool timed_out = false;
   if (warp < 8) {
@@ -205,12 +228,13 @@ __global__ void __launch_bounds__(kThreads, 1) mla_pair_kernel(const __grid_cons
     const int quarter = warp & 3;
     const int head = quarter * 32 + lane;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    const uint32_t tS = lane_base + kColS + grp * 32, tO = lane_base + kColT + grp * 128, tPw = lane_base + kColP + grp * 16;
-    const uint32_t peer = (uint32_t)(rank ^ 1);
-    float4* snd = xsend + (warp * 8) * 32 + lane;       // this warp's 4 KiB: [float4 i][lane]
-    const float4* rcv = xbuf + (warp * 8) * 32 + lane;
-    const uint32_t peer_x = peer_addr(xbuf + (warp * 8) * 32, peer);
-    const uint32_t peer_x_full = peer_addr(x_full, peer), peer_x_free = peer_addr(x_free, peer);
+    const uint32_t tO = lane_base + kColT + grp * 128, tPw = lane_base + kColP + grp * 16;
+    // this thread's 32 partial scores of a block: float4 [16 quarter + 8 grp + i][lane], i < 8, in a staging buffer
+    // (ours) and in xbuf (the peer's)
+    const int xoff = (quarter * 16 + grp * 8) * 32 + lane;
+    const float4* rcv = xbuf + xoff;
+    const uint32_t peer_x_free = peer_addr(x_free, (uint32_t)(rank ^ 1));
+    if (tid == 0 && nblk_total > 0) mbar_expect_tx(x_full, kXBytes);      // the first block's 32 KiB from the peer
     int base = 0, rbase = 0;                            // blocks / ring entries of the requests before this one
     uint32_t nx = 0;                                    // exchanges through xch so far
     for (int u = u_first; u <= u_last && !timed_out; ++u) {
@@ -249,73 +273,62 @@ __global__ void __launch_bounds__(kThreads, 1) mla_pair_kernel(const __grid_cons
       // far inside the range of a 16-bit float) is it raised and O rescaled, which is rare after a request's first
       // block.  The result is the same sum; only the common factor of numerator and denominator differs.
       float m = -INFINITY, l = 0.f;
-      // Our half of the contraction for block g: tensor memory -> registers (sn) -> staging buffer -> one
-      // asynchronous 4 KiB copy per warp into the peer's shared memory, completing on the peer's barrier.  The copy
-      // of 32 KiB takes about 2 k cycles, so a block's partial scores are sent BEFORE the softmax of the block
-      // before, whose arithmetic then covers the transfer.
-      uint32_t sn[32];
-#define PAIR_SEND(G)                                                                                              \
-      {                                                                                                             \
-        const int gs = (G);                                                                                         \
-        bool oks = mbar_wait(s_full, (uint32_t)(gs & 1));                                                           \
-        if (!__all_sync(0xffffffffu, oks)) { timed_out = true; break; }                                             \
-        if (quarter == 0) PAIR_E(2 + grp, gs, 0);                                                                   \
-        if (tid == 0) mbar_expect_tx(x_full, kXBytes);       /* this block's 32 KiB from the peer */                \
-        tc_fence_after();                                                                                           \
-        tmem_ld32(tS, sn);                                                                                          \
-        tmem_ld_wait();                                                                                             \
-        tc_fence_before();                                                                                          \
-        __syncwarp();                                                                                               \
-        if (lane == 0) mbar_arrive(s_free);                  /* the partial scores live in registers from here on */ \
-        if (quarter == 0) PAIR_E(2 + grp, gs, 1);                                                                   \
-        if (gs >= 1) {                                       /* the peer has read what we sent for the block before */ \
-          oks = mbar_wait_peer_relaxed(x_free, (uint32_t)((gs - 1) & 1));                                           \
-          if (!__all_sync(0xffffffffu, oks)) { timed_out = true; break; }                                           \
-        }                                                                                                           \
-        if (quarter == 0) PAIR_E(2 + grp, gs, 7);                                                                   \
-        _Pragma("unroll")                                                                                           \
-        for (int i = 0; i < 8; ++i)                                                                                 \
-          snd[i * 32] = make_float4(__uint_as_float(sn[4 * i]), __uint_as_float(sn[4 * i + 1]),                     \
-                                    __uint_as_float(sn[4 * i + 2]), __uint_as_float(sn[4 * i + 3]));                \
-        fence_proxy_async();                                 /* the copy reads what these threads just wrote */     \
-        __syncwarp();                                                                                               \
-        if (lane == 0) bulk_copy_to_peer(peer_x, xsend + (warp * 8) * 32, kXBytes / 8, peer_x_full);               \
-        if (quarter == 0) PAIR_E(2 + grp, gs, 2);                                                                   \
-      }
       for (int j = 0; j < w.nblk; ++j) {
         const int g = base + j;
-        if (j == 0) PAIR_SEND(g);
-        // ---- the peer's half
-        bool ok = mbar_wait(x_full, (uint32_t)(g & 1));      // the bytes were written into OUR shared memory: as for a TMA load
+        // ---- the two halves of the contraction: ours from the staging buffer, the peer's from its copy
+        bool ok = mbar_wait(&xs_full[g & 1], (uint32_t)((g >> 1) & 1));
+        if (quarter == 0) PAIR_E(2 + grp, g, 0);
+        if (ok) ok = mbar_wait(x_full, (uint32_t)(g & 1));   // the bytes were written into OUR shared memory: as for a TMA load
         if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
+        if (tid == 0 && g + 1 < nblk_total) mbar_expect_tx(x_full, kXBytes);     // the next block's
         if (quarter == 0) PAIR_E(2 + grp, g, 3);
+        const float4* own = xsend + (g & 1) * (kXBytes / 16) + xoff;
         const int kb = w.k0 + j * kBK + grp * 32;
         const bool tail = kb + 32 > w.k1;
         float bm = -INFINITY;
         uint32_t s[32];
+        {
+          // both halves into registers first, so that the two buffers go back at once: the peer's next copy waits
+          // for that, and it takes about 2 k cycles to cross
+          float4 v[8], o[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float4 v = rcv[i * 32];
-          float t0 = (__uint_as_float(sn[4 * i]) + v.x) * p.sc, t1 = (__uint_as_float(sn[4 * i + 1]) + v.y) * p.sc;
-          float t2 = (__uint_as_float(sn[4 * i + 2]) + v.z) * p.sc, t3 = (__uint_as_float(sn[4 * i + 3]) + v.w) * p.sc;
-          if (tail) {
-            if (kb + 4 * i >= w.k1) t0 = -INFINITY;
-            if (kb + 4 * i + 1 >= w.k1) t1 = -INFINITY;
-            if (kb + 4 * i + 2 >= w.k1) t2 = -INFINITY;
-            if (kb + 4 * i + 3 >= w.k1) t3 = -INFINITY;
+          for (int i = 0; i < 8; ++i) {
+            v[i] = rcv[i * 32];
+            o[i] = own[i * 32];
           }
-          s[4 * i] = __float_as_uint(t0); s[4 * i + 1] = __float_as_uint(t1);
-          s[4 * i + 2] = __float_as_uint(t2); s[4 * i + 3] = __float_as_uint(t3);
-          bm = fmaxf(bm, fmaxf(fmaxf(t0, t1), fmaxf(t2, t3)));
+          // The arrivals must not be issued before the loads have returned: their address is made to depend on one
+          // word of every load (and'ed to zero where the compiler cannot see it).
+          uint32_t dep = 0u;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) dep |= __float_as_uint(v[i].x) | __float_as_uint(o[i].x);
+          asm volatile("and.b32 %0, %0, 0;" : "+r"(dep));
+          __syncwarp();
+          if (lane == 0) {
+            arrive_peer_relaxed(peer_x_free + dep);          // the peer's copy for the next block may come
+            mbar_arrive(&xs_free[(g & 1) + dep]);            // ... and our staging buffer may be refilled
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            // (rank 0's half first on both sides: the two CTAs then hold the same bits)
+            float t0 = (rank == 0 ? o[i].x + v[i].x : v[i].x + o[i].x) * p.sc;
+            float t1 = (rank == 0 ? o[i].y + v[i].y : v[i].y + o[i].y) * p.sc;
+            float t2 = (rank == 0 ? o[i].z + v[i].z : v[i].z + o[i].z) * p.sc;
+            float t3 = (rank == 0 ? o[i].w + v[i].w : v[i].w + o[i].w) * p.sc;
+            if (tail) {
+              if (kb + 4 * i >= w.k1) t0 = -INFINITY;
+              if (kb + 4 * i + 1 >= w.k1) t1 = -INFINITY;
+              if (kb + 4 * i + 2 >= w.k1) t2 = -INFINITY;
+              if (kb + 4 * i + 3 >= w.k1) t3 = -INFINITY;
+            }
+            s[4 * i] = __float_as_uint(t0); s[4 * i + 1] = __float_as_uint(t1);
+            s[4 * i + 2] = __float_as_uint(t2); s[4 * i + 3] = __float_as_uint(t3);
+            bm = fmaxf(bm, fmaxf(fmaxf(t0, t1), fmaxf(t2, t3)));
+          }
         }
         if (quarter == 0) PAIR_E(2 + grp, g, 8);
         smax[((g & 1) * 2 + grp) * 128 + head] = bm;
         __syncwarp();
-        if (lane == 0) {
-          arrive_peer_relaxed(peer_x_free);                  // the peer's copy for the next block may come
-          mbar_arrive(&xch[quarter]);
-        }
-        if (j + 1 < w.nblk) PAIR_SEND(g + 1);                // the next block's half goes out before this block's softmax
+        if (lane == 0) mbar_arrive(&xch[quarter]);
         ok = mbar_wait(&xch[quarter], nx & 1);
         ++nx;
         if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
@@ -368,7 +381,6 @@ __global__ void __launch_bounds__(kThreads, 1) mla_pair_kernel(const __grid_cons
         }
         if (quarter == 0) PAIR_E(2 + grp, g, 6);
       }
-#undef PAIR_SEND
       if (timed_out) break;
       // row sums of the two key halves
       ssum[((nx & 1) * 2 + grp) * 128 + head] = l;
@@ -444,6 +456,14 @@ __global__ void __launch_bounds__(kThreads, 1) mla_pair_kernel(const __grid_cons
       const UnitWork w = unit_work(p, u, slot0, slot1);
       if (w.nblk == 0) continue;
       const int32_t* idxb = p.idx + (size_t)u * kTopK;
+      // position in the request's cache -> row of the tensor (request base or page base); -1 = a row of zeros
+      auto row_of = [&](int ridx) -> long long {
+        if (ridx < 0) return -1;
+        if (p.page_table == nullptr) return (long long)u * p.L + ridx;
+        const int pi = ridx / p.page_size;
+        const int pg = p.page_table[(size_t)u * p.table_stride + pi];
+        return (pg >= 0 && pg < p.pages) ? (long long)pg * p.page_size + (ridx - pi * p.page_size) : -1;   // outside the pool: zeros
+      };
       // ---- the request's queries: two entries of 64 rows, five TMA boxes of 64 x 64 each
       for (int e = 0; e < kQEntries && !timed_out; ++e) {
         const int r = rbase + e, s = r % kStages;
@@ -461,28 +481,37 @@ __global__ void __launch_bounds__(kThreads, 1) mla_pair_kernel(const __grid_cons
           mbar_arrive(&full[s]);
         }
       }
-      // ---- its key blocks
+      // ---- its key blocks.  Lanes 0-15 (and their mirrors 16-31) each look up one row of this warp's sixteen: its
+      // position in the cache (-1 = a row of zeros), then its row in the tensor.  The positions are loaded one block
+      // ahead of their use, so that their latency is off the path; the rows of the block kPrefetch ahead are asked
+      // into L2 (lanes 0-15: one row of 640 bytes each): a row comes from HBM in about 2 k cycles, more than the
+      // ring's three slots cover at the rate the blocks are consumed.
+      auto load_idx = [&](int blk) -> int {
+        const int krow = w.k0 + blk * kBK + pw * 16 + (lane & 15);
+        return (blk < w.nblk && krow < w.k1) ? idxb[krow] : -1;
+      };
+      auto prefetch_row = [&](int pidx) {
+        if (lane < 16 && pidx >= 0 && pidx < p.L) {
+          const long long pc = row_of(pidx);
+          if (pc >= 0) l2_prefetch(reinterpret_cast<const uint8_t*>(p.kv + (size_t)pc * kDK) + cb0 * 128, kSlotBlocks * 128);
+        }
+      };
+      int cur = load_idx(0);
+      for (int ja = 1; ja < kPrefetch; ++ja) prefetch_row(load_idx(ja));
+      int pf = load_idx(kPrefetch);
       for (int j = 0; j < w.nblk && !timed_out; ++j) {
         const int r = rbase + kQEntries + j, s = r % kStages;
         uint8_t* st = sK + s * kSlot;
-        // lanes 0-15 (and their mirrors 16-31) each look up one row of this warp's sixteen: its position in the
-        // cache, then its row in the tensor (request base or page base); -1 = a row of zeros
-        const int krow = w.k0 + j * kBK + pw * 16 + (lane & 15);
-        int ridx = krow < w.k1 ? idxb[krow] : -1;
+        const int nxt = load_idx(j + 1), pf_nxt = load_idx(j + 1 + kPrefetch);   // used in the next iteration
+        int ridx = cur;
         if (ridx >= p.L) {
           report(p.status, kStatusBadIndex);
           ridx = 0;
         }
-        long long coord = -1;
-        if (ridx >= 0) {
-          if (p.page_table == nullptr) {
-            coord = (long long)u * p.L + ridx;
-          } else {
-            const int pi = ridx / p.page_size;
-            const int pg = p.page_table[(size_t)u * p.table_stride + pi];
-            coord = (pg >= 0 && pg < p.pages) ? (long long)pg * p.page_size + (ridx - pi * p.page_size) : -1;   // outside the pool: zeros
-          }
-        }
+        const long long coord = row_of(ridx);
+        prefetch_row(pf);
+        cur = nxt;
+        pf = pf_nxt;
         if (pw == 0) PAIR_E(1, gb + j, 0);
         if (r >= kStages) {
           const bool ok = mbar_wait(&empty[s], (uint32_t)(((r / kStages) - 1) & 1));
@@ -513,6 +542,53 @@ __global__ void __launch_bounds__(kThreads, 1) mla_pair_kernel(const __grid_cons
     // no copy outlives the CTA, on the give-up path either
     cp_async_commit();
     cp_async_wait<0>();
+  } else if (warp >= kWarpExch0) {
+    // ------------------------------------------------------------------------------ exchange warps
+    // Warp w takes the 32 heads of tensor-memory lane quarter w % 4: the block's 64 partial scores of each head go
+    // to registers (the score columns are then free for the next Q.K^T), to the staging buffer, where this CTA's
+    // softmax threads find them, and from there by one asynchronous 8 KiB copy into the peer's shared memory,
+    // completing on the peer's barrier.  The 32 KiB of a block take about 2 k cycles to cross; done here, a block
+    // ahead of the softmax, the transfer is off its path.
+    const int quarter = warp & 3;
+    const uint32_t tS = tmem_base + ((uint32_t)(quarter * 32) << 16) + kColS;
+    const uint32_t peer = (uint32_t)(rank ^ 1);
+    const uint32_t peer_x = peer_addr(xbuf + (quarter * 16) * 32, peer);
+    const uint32_t peer_x_full = peer_addr(x_full, peer);
+    for (int g = 0; g < nblk_total; ++g) {
+      bool ok = mbar_wait(s_full, (uint32_t)(g & 1));
+      if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
+      if (quarter == 0) PAIR_E(3, g, 0);
+      tc_fence_after();
+      uint32_t s0[32], s1[32];
+      tmem_ld32(tS, s0);
+      tmem_ld32(tS + 32, s1);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_free);
+      if (quarter == 0) PAIR_E(3, g, 1);
+      // the staging buffer of two blocks back has been read by our softmax threads; the peer has read the block
+      // before (so its buffer is free, and our copy out of this staging buffer, older still, is complete)
+      if (g >= 2) ok = mbar_wait(&xs_free[g & 1], (uint32_t)(((g >> 1) - 1) & 1));
+      if (ok && g >= 1) ok = mbar_wait_peer_relaxed(x_free, (uint32_t)((g - 1) & 1));
+      if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
+      if (quarter == 0) PAIR_E(3, g, 2);
+      float4* snd = xsend + (g & 1) * (kXBytes / 16) + (quarter * 16) * 32 + lane;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        snd[i * 32] = make_float4(__uint_as_float(s0[4 * i]), __uint_as_float(s0[4 * i + 1]), __uint_as_float(s0[4 * i + 2]),
+                                  __uint_as_float(s0[4 * i + 3]));
+        snd[(8 + i) * 32] = make_float4(__uint_as_float(s1[4 * i]), __uint_as_float(s1[4 * i + 1]),
+                                        __uint_as_float(s1[4 * i + 2]), __uint_as_float(s1[4 * i + 3]));
+      }
+      fence_proxy_async();                                   // the copy reads what these threads just wrote
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&xs_full[g & 1]);
+        bulk_copy_to_peer(peer_x, snd - lane, kXBytes / 4, peer_x_full);
+      }
+      if (quarter == 0) PAIR_E(3, g, 3);
+    }
   } else if (warp == kWarpQK) {
     // ------------------------------------------------------------------------------ Q.K^T issuer
     if (lane == 0) {

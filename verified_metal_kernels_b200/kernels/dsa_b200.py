@@ -298,7 +298,7 @@ def set_indexer_variant(name):
     _lib.check(rc, "vmk_dsa_set_indexer_variant")
 
 
-ATTEND_VARIANTS = {"mma": 0, "tcgen05": 1, "tcgen05_tma": 2, "tcgen05_pair": 3, "tcgen05_pair_n128": 4}
+ATTEND_VARIANTS = {"mma": 0, "tcgen05": 1, "tcgen05_tma": 2, "tcgen05_pair": 3}
 DEFAULT_ATTEND_VARIANT = "tcgen05_pair"
 
 
