@@ -322,6 +322,10 @@ VMK_API int vmk_attn_set_tc(int on);
 VMK_API int vmk_prefix_set_side_by_side(int on);
 VMK_API int vmk_dsa_set_indexer_variant(int variant);
 VMK_API int vmk_dsa_set_attend_variant(int variant);
+/*   vmk_dsa_set_select_cluster(c): CTAs per request of the top-k selection on rows of 32768 positions and more
+ *   (1, 2, 4 or 8: that many SMs read a row together and exchange histograms through distributed shared memory);
+ *   0, the default, takes the largest size whose CTAs fit in one wave.  The selection is the same set. */
+VMK_API int vmk_dsa_set_select_cluster(int csize);
 
 #ifdef __cplusplus
 }

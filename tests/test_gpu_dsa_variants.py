@@ -88,3 +88,32 @@ def test_attend_variants_agree(B, dist):
     assert judge.nerr(outs["tcgen05_pair"], outs["tcgen05"])[0] <= 2e-3
     # the two gathers fill the same shared-memory tiles, so everything after them sees the same bits
     assert np.array_equal(outs["tcgen05"], outs["tcgen05_tma"], equal_nan=True)
+
+
+def test_select_cluster_sizes_agree():
+    """The top-k selection splits a long row over 1, 2, 4 or 8 CTAs (the batch size decides): the selected positions
+    and counts are the same, with and without the indexer's fused histogram."""
+    B, L = 3, 40000
+    inp = op.make_inputs(dict(B=B, L=L), seed=5, dist="ragged")
+    d = _verify.device_inputs("dsa", inp)
+    scores, hist = dsa_b200.indexer_hist(d["iq"], d["ik"], d["w"], d.get("lens"))
+    outs = {}
+    try:
+        for cs in (0, 1, 2, 4, 8):
+            dsa_b200.set_select_cluster(cs)
+            i1, c1 = dsa_b200.select(scores, d.get("lens"), hist)
+            i2, c2 = dsa_b200.select(scores, d.get("lens"))
+            outs[cs] = (i1.cpu().numpy(), c1.cpu().numpy())
+            assert np.array_equal(outs[cs][1], c2.cpu().numpy())
+            for b in range(B):
+                n = int(outs[cs][1][b])
+                assert np.array_equal(outs[cs][0][b, :n], i2.cpu().numpy()[b, :n])
+    finally:
+        dsa_b200.set_select_cluster(0)
+    _verify.assert_clean_status()
+    s64 = ref64.dsa_scores64(inp["iq"], inp["ik"], inp["w"])
+    for cs, (idx, cnt) in outs.items():
+        for b in range(B):
+            assert judge.select_check(idx[b], cnt[b], s64[b], int(inp["lens"][b]))["ok"], cs
+            n = int(cnt[b])
+            assert np.array_equal(idx[b, :n], outs[0][0][b, :n]), cs

@@ -53,6 +53,7 @@ SIGNATURES = {
     "vmk_prefix_set_side_by_side": (_i, [_i]),
     "vmk_dsa_set_indexer_variant": (_i, [_i]),
     "vmk_dsa_set_attend_variant": (_i, [_i]),
+    "vmk_dsa_set_select_cluster": (_i, [_i]),
 }
 # exported by debug builds only (-DVMK_MLA_TIMING, -DVMK_TC_TIMING, -DVMK_SEL_TIMING, -DVMK_ATTN_TIMING): device-side event traces
 DEBUG_EXPORTS = ("vmk_debug_mla_trace", "vmk_debug_pair_trace", "vmk_debug_tc_trace", "vmk_debug_sel_timing", "vmk_debug_attn_marks")

@@ -515,7 +515,8 @@ extern "C" VMK_API int vmk_debug_sel_timing(long long* out, int reset) {
 }
 #endif
 
-constexpr int kSelCluster = 8;         // CTAs per request for long rows
+constexpr int kSelCluster = 8;         // most CTAs per request for long rows
+static int g_select_cluster = 0;       // test hook: 0 = chosen by the batch, else 1, 2, 4 or 8
 
 template <int EPL>
 static int launch_select(const float* scores, const uint32_t* hist, const int32_t* lens, int32_t* idx, int32_t* cnt,
@@ -530,25 +531,58 @@ static int launch_select(const float* scores, const uint32_t* hist, const int32_
     if (e != cudaSuccess) return check_launch(e);
     configured_dev = dev;
   }
-  // Long rows of a small batch are split over a cluster of 8 CTAs (8 SMs read a row together).  With many
-  // requests every SM is busy anyway and one CTA per request does the same work with fewer barriers.
-  if (L >= 32768 && B * kSelCluster <= 2 * sm_count()) {
+  // Long rows of a small batch are split over a cluster of 8, 4 or 2 CTAs (that many SMs read a row together): the
+  // largest size at which all B clusters are resident together.  That is fewer than SMs / size: a cluster lives inside
+  // one GPC (16 requests x 8 CTAs are 128 CTAs, but they took two waves: 0.036 ms against 0.020 ms with 4 CTAs each;
+  // 32 x 8: 0.055 against 0.021; 37 x 4: 0.043 against 0.028 with 2 each).  With many requests every SM is busy
+  // anyway and one CTA per request does the same work with fewer barriers.
+  static int resident[4] = {0, 0, 0, 0};       // clusters of 1 << i CTAs that can be resident together (i = 1..3)
+  static int resident_dev = -1;
+  if (resident_dev != dev) {
+    for (int i = 1; i <= 3; ++i) {
+      cudaLaunchConfig_t q;
+      memset(&q, 0, sizeof(q));
+      q.gridDim = dim3((unsigned)(sm_count() / (1 << i)) * (1 << i));
+      q.blockDim = dim3(kSelThreads);
+      q.dynamicSmemBytes = kSelSmem;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = 1 << i;
+      qa[0].val.clusterDim.y = 1;
+      qa[0].val.clusterDim.z = 1;
+      q.attrs = qa;
+      q.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, select_kernel<EPL, true>, &q) != cudaSuccess) n = 0;
+      cudaGetLastError();
+      resident[i] = n;
+    }
+    resident_dev = dev;
+  }
+  int csize = 1;
+  if (g_select_cluster > 0) {
+    csize = g_select_cluster;
+  } else {
+    for (int i = 3; i >= 1 && csize == 1; --i)
+      if (B <= resident[i]) csize = 1 << i;
+  }
+  if (L >= 32768 && csize > 1) {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3((unsigned)B * kSelCluster);
+    cfg.gridDim = dim3((unsigned)B * csize);
     cfg.blockDim = dim3(kSelThreads);
     cfg.dynamicSmemBytes = kSelSmem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = kSelCluster;
+    attr[0].val.clusterDim.x = csize;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    return check_launch(cudaLaunchKernelEx(&cfg, select_kernel<EPL, true>, scores, hist, lens, idx, cnt, L, kSelCluster));
+    return check_launch(cudaLaunchKernelEx(&cfg, select_kernel<EPL, true>, scores, hist, lens, idx, cnt, L, csize));
   }
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -573,6 +607,13 @@ int select_launch(const float* scores, const uint32_t* hist, const int32_t* lens
 }
 
 }  // namespace vmk
+
+// Test hook: CTAs per request of the top-k selection on long rows (0 = chosen by the batch size, the default).
+extern "C" VMK_API int vmk_dsa_set_select_cluster(int csize) {
+  if (csize != 0 && csize != 1 && csize != 2 && csize != 4 && csize != 8) return VMK_E_BADARG;
+  vmk::g_select_cluster = csize;
+  return VMK_OK;
+}
 
 extern "C" int vmk_dsa_select(const float* scores, const int32_t* lens, int32_t* idx, int32_t* cnt, int B, int L,
                               void* stream) {

@@ -302,6 +302,12 @@ ATTEND_VARIANTS = {"mma": 0, "tcgen05": 1, "tcgen05_tma": 2, "tcgen05_pair": 3}
 DEFAULT_ATTEND_VARIANT = "tcgen05_pair"
 
 
+def set_select_cluster(csize):
+    """CTAs per request of the top-k selection on long rows: 1, 2, 4 or 8; 0 (the default) = the largest size whose
+    CTAs fit in one wave.  The selected set does not depend on it."""
+    _lib.check(_lib.lib().vmk_dsa_set_select_cluster(int(csize)), "vmk_dsa_set_select_cluster")
+
+
 def set_attend_variant(name):
     """Chooses the stage-3 implementation: "mma" (warp-level mma.sync), "tcgen05" (tensor memory, one CTA per
     request and value half, rows gathered by cp.async from four warps), "tcgen05_tma" (the same with the rows
