@@ -88,6 +88,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
   // EVEN so that a slot always comes back to the same thread: a thread that ran ahead and asked for a slot that still
   // holds the other thread's earlier tile would see the parity of the phase before and take the old tile for its own.
   constexpr int kSt = FP8 ? 2 * kStages : kStages;
+  static_assert(!FP8 || (kSt % 2 == 0 && kAccs % 2 == 0), "two issuing threads: slots and accumulators must not change hands");
   constexpr int kIqLoad = FP8 ? kIqBytes / 2 : kIqBytes;
   constexpr int kIssuers = FP8 ? 2 : 1;
   constexpr int kSets = FP8 ? 2 : 1;
