@@ -32,7 +32,8 @@
 //               loaded a block ahead, and the rows of the block three ahead are asked into L2
 //   warp 12     issues S = Q.K^T (A = the queries, kept in tensor memory)
 //   warp 13     owns tensor memory and issues P.V (A = P from tensor memory)
-//   warps 14-17 exchange (above)
+//   warps 14-17 exchange (above); they also copy a request's queries from the ring into tensor memory, so that the
+//               next request's first scores are on their way while the softmax threads still write the last one out
 // Every mbarrier wait is bounded; a wait that runs out sets the status word and the CTA winds down through the
 // common exit, where both CTAs meet at a cluster barrier (nobody leaves while its peer may still copy into its
 // shared memory) and tensor memory is freed.  Nothing here is a multicast: every copy has one destination.
@@ -164,7 +165,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_pair_kernel(const __grid_cons
   float4* xbuf = xsend + 2 * (kXBytes / 16);                                // the peer's, written by its copy
   uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(xbuf) + kXBytes);   // entry landed
   uint64_t* empty = full + kStages;                     // entry consumed                       (MMA commit)
-  uint64_t* q_full = empty + kStages;                   // Q stored to tensor memory            (8 warps)
+  uint64_t* q_full = empty + kStages;                   // Q stored to tensor memory            (4 warps)
   uint64_t* s_full = q_full + 1;                        // partial scores ready                 (MMA commit)
   uint64_t* s_free = s_full + 1;                        // partial scores out of tensor memory  (4 warps)
   uint64_t* p_full = s_free + 1;                        // P in tensor memory, O rescaled       (8 warps)
@@ -191,7 +192,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_pair_kernel(const __grid_cons
       mbar_init(&full[s], kGatherWarps * 32);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(q_full, 8);
+    mbar_init(q_full, 4);
     mbar_init(s_full, 1);
     mbar_init(s_free, 4);
     for (int i = 0; i < 2; ++i) {
@@ -235,39 +236,10 @@ __global__ void __launch_bounds__(kThreads, 1) mla_pair_kernel(const __grid_cons
     const float4* rcv = xbuf + xoff;
     const uint32_t peer_x_free = peer_addr(x_free, (uint32_t)(rank ^ 1));
     if (tid == 0 && nblk_total > 0) mbar_expect_tx(x_full, kXBytes);      // the first block's 32 KiB from the peer
-    int base = 0, rbase = 0;                            // blocks / ring entries of the requests before this one
+    int base = 0;                                       // blocks of the requests before this one
     uint32_t nx = 0;                                    // exchanges through xch so far
     for (int u = u_first; u <= u_last && !timed_out; ++u) {
       const UnitWork w = unit_work(p, u, slot0, slot1);
-      if (w.nblk > 0) {
-        // This head's share of the queries: from the ring entry that holds its row (rows 0-63 in the request's
-        // first entry, 64-127 in its second) to tensor memory, two 16-bit values per column.  The CTA's 288
-        // elements are 36 chunks of 16 bytes, starting 4 rank chunks into the five blocks; group A copies the
-        // first 20 (80 columns), group B the other 16.  Every Q.K^T of the previous request has completed: this
-        // thread has seen its last scores.
-        const int rq = rbase + (head >> 6), sq = rq % kStages;
-        const bool okq = mbar_wait(&full[sq], (uint32_t)((rq / kStages) & 1));
-        if (!__all_sync(0xffffffffu, okq)) { timed_out = true; break; }
-        const uint8_t* qs = sK + sq * kSlot;
-        const int qrow = head & 63;
-        const int k0 = grp == 0 ? 0 : 20, nst = grp == 0 ? 5 : 4;
-#pragma unroll 1
-        for (int c = 0; c < nst; ++c) {
-          uint32_t rr[16];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int ch = rank * 4 + k0 + c * 4 + i;
-            const uint4 v = *reinterpret_cast<const uint4*>(qs + (ch >> 3) * kBlkBytes + swz128(qrow, ch & 7));
-            rr[4 * i] = v.x; rr[4 * i + 1] = v.y; rr[4 * i + 2] = v.z; rr[4 * i + 3] = v.w;
-          }
-          tmem_st16(lane_base + kColQ + (k0 + c * 4) * 4, rr);
-        }
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(q_full);
-      }
-
       // m is the REFERENCE maximum: P = exp2(s - m) and O, l are sums relative to it.  It follows the true
       // maximum lazily: only when a block's maximum exceeds it by more than kLazy (P then stays below 2^kLazy,
       // far inside the range of a 16-bit float) is it raised and O rescaled, which is rare after a request's first
@@ -442,7 +414,6 @@ __global__ void __launch_bounds__(kThreads, 1) mla_pair_kernel(const __grid_cons
         __syncwarp();
         if (lane == 0) mbar_arrive(o_free);
         base += w.nblk;
-        rbase += kQEntries + w.nblk;
       }
     }
   } else if (warp < kWarpGather0 + kGatherWarps) {
@@ -554,40 +525,75 @@ __global__ void __launch_bounds__(kThreads, 1) mla_pair_kernel(const __grid_cons
     const uint32_t peer = (uint32_t)(rank ^ 1);
     const uint32_t peer_x = peer_addr(xbuf + (quarter * 16) * 32, peer);
     const uint32_t peer_x_full = peer_addr(x_full, peer);
-    for (int g = 0; g < nblk_total; ++g) {
-      bool ok = mbar_wait(s_full, (uint32_t)(g & 1));
-      if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
-      if (quarter == 0) PAIR_E(3, g, 0);
-      tc_fence_after();
-      uint32_t s0[32], s1[32];
-      tmem_ld32(tS, s0);
-      tmem_ld32(tS + 32, s1);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_free);
-      if (quarter == 0) PAIR_E(3, g, 1);
-      // the staging buffer of two blocks back has been read by our softmax threads; the peer has read the block
-      // before (so its buffer is free, and our copy out of this staging buffer, older still, is complete)
-      if (g >= 2) ok = mbar_wait(&xs_free[g & 1], (uint32_t)(((g >> 1) - 1) & 1));
-      if (ok && g >= 1) ok = mbar_wait_peer_relaxed(x_free, (uint32_t)((g - 1) & 1));
-      if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
-      if (quarter == 0) PAIR_E(3, g, 2);
-      float4* snd = xsend + (g & 1) * (kXBytes / 16) + (quarter * 16) * 32 + lane;
+    const int head = quarter * 32 + lane;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    int g = 0, rbase = 0;                               // blocks / ring entries of the requests before this one
+    for (int u = u_first; u <= u_last && !timed_out; ++u) {
+      const UnitWork w = unit_work(p, u, slot0, slot1);
+      if (w.nblk == 0) continue;
+      {
+        // This head's share of the request's queries: from the ring entry that holds its row (rows 0-63 in the
+        // request's first entry, 64-127 in its second) to tensor memory, two 16-bit values per column.  The CTA's
+        // 288 elements are 36 chunks of 16 bytes, starting 4 rank chunks into the five blocks.  Every Q.K^T of the
+        // request before has completed: this warp has taken its last scores out of tensor memory.  Done here, the
+        // next request's first scores are on their way while the softmax threads still write the last one out.
+        const int rq = rbase + (head >> 6), sq = rq % kStages;
+        const bool okq = mbar_wait(&full[sq], (uint32_t)((rq / kStages) & 1));
+        if (!__all_sync(0xffffffffu, okq)) { timed_out = true; break; }
+        const uint8_t* qs = sK + sq * kSlot;
+        const int qrow = head & 63;
+#pragma unroll 1
+        for (int c = 0; c < 9; ++c) {
+          uint32_t rr[16];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        snd[i * 32] = make_float4(__uint_as_float(s0[4 * i]), __uint_as_float(s0[4 * i + 1]), __uint_as_float(s0[4 * i + 2]),
-                                  __uint_as_float(s0[4 * i + 3]));
-        snd[(8 + i) * 32] = make_float4(__uint_as_float(s1[4 * i]), __uint_as_float(s1[4 * i + 1]),
-                                        __uint_as_float(s1[4 * i + 2]), __uint_as_float(s1[4 * i + 3]));
+          for (int i = 0; i < 4; ++i) {
+            const int ch = rank * 4 + c * 4 + i;
+            const uint4 v = *reinterpret_cast<const uint4*>(qs + (ch >> 3) * kBlkBytes + swz128(qrow, ch & 7));
+            rr[4 * i] = v.x; rr[4 * i + 1] = v.y; rr[4 * i + 2] = v.z; rr[4 * i + 3] = v.w;
+          }
+          tmem_st16(lane_base + kColQ + c * 16, rr);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(q_full);
       }
-      fence_proxy_async();                                   // the copy reads what these threads just wrote
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&xs_full[g & 1]);
-        bulk_copy_to_peer(peer_x, snd - lane, kXBytes / 4, peer_x_full);
+      for (int j = 0; j < w.nblk; ++j, ++g) {
+        bool ok = mbar_wait(s_full, (uint32_t)(g & 1));
+        if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
+        if (quarter == 0) PAIR_E(3, g, 0);
+        tc_fence_after();
+        uint32_t s0[32], s1[32];
+        tmem_ld32(tS, s0);
+        tmem_ld32(tS + 32, s1);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free);
+        if (quarter == 0) PAIR_E(3, g, 1);
+        // the staging buffer of two blocks back has been read by our softmax threads; the peer has read the block
+        // before (so its buffer is free, and our copy out of this staging buffer, older still, is complete)
+        if (g >= 2) ok = mbar_wait(&xs_free[g & 1], (uint32_t)(((g >> 1) - 1) & 1));
+        if (ok && g >= 1) ok = mbar_wait_peer_relaxed(x_free, (uint32_t)((g - 1) & 1));
+        if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
+        if (quarter == 0) PAIR_E(3, g, 2);
+        float4* snd = xsend + (g & 1) * (kXBytes / 16) + (quarter * 16) * 32 + lane;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          snd[i * 32] = make_float4(__uint_as_float(s0[4 * i]), __uint_as_float(s0[4 * i + 1]), __uint_as_float(s0[4 * i + 2]),
+                                    __uint_as_float(s0[4 * i + 3]));
+          snd[(8 + i) * 32] = make_float4(__uint_as_float(s1[4 * i]), __uint_as_float(s1[4 * i + 1]),
+                                          __uint_as_float(s1[4 * i + 2]), __uint_as_float(s1[4 * i + 3]));
+        }
+        fence_proxy_async();                                   // the copy reads what these threads just wrote
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&xs_full[g & 1]);
+          bulk_copy_to_peer(peer_x, snd - lane, kXBytes / 4, peer_x_full);
+        }
+        if (quarter == 0) PAIR_E(3, g, 3);
       }
-      if (quarter == 0) PAIR_E(3, g, 3);
+      rbase += kQEntries + w.nblk;
     }
   } else if (warp == kWarpQK) {
     // ------------------------------------------------------------------------------ Q.K^T issuer
@@ -602,7 +608,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_pair_kernel(const __grid_cons
       for (int u = u_first; u <= u_last && !timed_out; ++u) {
         const UnitWork w = unit_work(p, u, slot0, slot1);
         if (w.nblk == 0) continue;
-        // the softmax threads have copied the request's queries out of their two entries: hand the slots back
+        // the exchange warps have copied the request's queries out of their two entries: hand the slots back
         if (!mbar_wait(q_full, (uint32_t)(units & 1))) { timed_out = true; break; }
         for (int e = 0; e < kQEntries; ++e) umma_commit(&empty[(rbase + e) % kStages]);
         for (int j = 0; j < w.nblk; ++j) {
