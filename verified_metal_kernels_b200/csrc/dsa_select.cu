@@ -6,8 +6,10 @@
 //            its epilogue, or built here in one pass when absent;
 //   fast path (the boundary bin holds at most 8192 entries and the entries equal to T all fit in the
 //            result): ONE pass over the scores stages the boundary bin's (key, position) pairs in shared
-//            memory and counts, per warp span, the entries above the bin; levels 2 and 3 then run on the
-//            staged pairs only; ONE more pass writes the positions in ascending order;
+//            memory and, per warp span, counts the entries above the bin and keeps their positions while they
+//            fit; levels 2 and 3 then run on the staged pairs only; a warp whose selected entries were all kept
+//            (the usual case) ranks them by counting and writes them out, any other warp makes ONE more pass over
+//            its span that writes the positions in ascending order;
 //   general path (huge boundary bin, or more ties at T than fit): levels 2 and 3 over the scores, then an
 //            ordered compaction that takes the ties at T from the lowest positions.
 // The result is deterministic: the same scores always give the same ascending index list.  Passes read
@@ -24,7 +26,10 @@ constexpr int kTopK = VMK_DSA_TOPK;
 constexpr int kSelThreads = 1024;
 constexpr int kCandCap = 8192;              // staged pairs in total
 constexpr int kCandWarp = kCandCap / 32;    // each warp stages into a region of its own (no atomics)
-constexpr int kSelSmem = kCandCap * 8;      // (key, position) pairs
+constexpr int kAboveWarp = 160;             // per warp: positions of the entries above the boundary bin (staged too,
+                                            // so that a warp whose selected entries fit here needs no second pass)
+constexpr int kRankMax = 96;                // ... and are few enough to be ranked by counting
+constexpr int kSelSmem = kCandCap * 8 + 32 * kAboveWarp * 4;      // (key, position) pairs, then the positions above
 
 #ifdef VMK_SEL_TIMING
 // Debug build only: cycles per phase of CTA 0, thread 0.
@@ -298,6 +303,7 @@ __global__ void __launch_bounds__(kSelThreads, 1) select_kernel(const float* __r
   extern __shared__ uint32_t cand[];          // [kCandCap] keys, then [kCandCap] positions
   uint32_t* ckey = cand;
   uint32_t* cidx = cand + kCandCap;
+  uint32_t* cpos = cand + 2 * kCandCap;       // [32 warps][kAboveWarp]
 
   const int b = CLUSTER ? blockIdx.x / csize : blockIdx.x;
   const int crank = CLUSTER ? blockIdx.x % csize : 0;
@@ -329,7 +335,8 @@ __global__ void __launch_bounds__(kSelThreads, 1) select_kernel(const float* __r
   const int part = CLUSTER ? (((n + csize - 1) / csize + 127) & ~127) : n;
   const int pbeg = min(n, crank * part), pend = min(n, pbeg + part);
   const int span = ((pend - pbeg + 31) / 32 + 3) & ~3;
-  const int beg = min(pend, pbeg + warp * span), end = min(pend, beg + span);
+  const int beg = min(pend, pbeg + warp * span);
+  int end = min(pend, beg + span);
 
 #ifdef VMK_SEL_TIMING
   long long _t0 = clock64();
@@ -355,6 +362,7 @@ __global__ void __launch_bounds__(kSelThreads, 1) select_kernel(const float* __r
   // cluster-uniform; the lowest bin (NaN lives there) and the empty top bins take the general path
   bool fast = c1 <= (uint32_t)kCandCap && b1 >= 1u && b1 <= 2043u;
   uint32_t T = 0;
+  uint32_t bstaged = 0;                         // entries above the boundary bin in this warp's span (warp-uniform)
   if (fast) {
     // ---- one pass: every warp stages the boundary-bin entries of its span, in position order, into its
     //      own region, and counts what lies above the bin.  Membership in the bin is an interval test on
@@ -363,6 +371,7 @@ __global__ void __launch_bounds__(kSelThreads, 1) select_kernel(const float* __r
     uint32_t above = 0, staged = 0;             // staged is warp-uniform
     uint32_t* wkey = ckey + warp * kCandWarp;
     uint32_t* widx = cidx + warp * kCandWarp;
+    uint32_t* wpos = cpos + warp * kAboveWarp;  // positions of the entries above the bin, kept while they fit
     {
       constexpr int U = 8;
       const int per_step = 32 * EPL;
@@ -371,14 +380,32 @@ __global__ void __launch_bounds__(kSelThreads, 1) select_kernel(const float* __r
         float x[U][EPL];
 #pragma unroll
         for (int u = 0; u < U; ++u) load_vals<EPL>(s, beg + ((t + u) * 32 + lane) * EPL, end, x[u]);
-        uint32_t cf = 0;
+        uint32_t cf = 0, af = 0;
 #pragma unroll
         for (int u = 0; u < U; ++u) {
 #pragma unroll
           for (int e = 0; e < EPL; ++e) {
-            above += x[u][e] >= hi ? 1u : 0u;
+            af |= x[u][e] >= hi ? (1u << (u * EPL + e)) : 0u;
             cf |= (x[u][e] >= lo && x[u][e] < hi) ? (1u << (u * EPL + e)) : 0u;
           }
+        }
+        above += __popc(af);
+        if (bstaged <= (uint32_t)kAboveWarp && __any_sync(0xffffffffu, af != 0u)) {
+          const uint32_t c = __popc(af);
+          uint32_t incl = c;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t y = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += y;
+          }
+          uint32_t slot = bstaged + incl - c;
+          while (af != 0u) {                      // about one element in sixty
+            const int bit = __ffs(af) - 1;
+            af &= af - 1u;
+            if (slot < (uint32_t)kAboveWarp) wpos[slot] = (uint32_t)(beg + ((t + bit / EPL) * 32 + lane) * EPL + bit % EPL);
+            ++slot;
+          }
+          bstaged += __shfl_sync(0xffffffffu, incl, 31);
         }
         if (__any_sync(0xffffffffu, cf != 0u)) {
           const uint32_t c = __popc(cf);
@@ -469,15 +496,47 @@ __global__ void __launch_bounds__(kSelThreads, 1) select_kernel(const float* __r
   SEL_T(3);
   // ---- ordered emission: positions with score >= the threshold, ascending -------------------------------
   for (int w = 0; w < warp; ++w) pos += sh.w_a[w];
+  {
+    // A warp whose selected entries were all staged (those above the bin in the first pass, those of the bin with
+    // key >= T now) and are few ranks them by counting and writes them out: no second pass over its span.
+    uint32_t n = bstaged;
+    bool staged_all = bstaged <= (uint32_t)kAboveWarp;
+    if (staged_all) {
+      uint32_t* wpos = cpos + warp * kAboveWarp;
+      const uint32_t* wkey = ckey + warp * kCandWarp;
+      const uint32_t* widx = cidx + warp * kCandWarp;
+      const uint32_t nA = sh.w_n[warp];
+      for (uint32_t j0 = 0; j0 < nA; j0 += 32) {
+        const uint32_t j = j0 + lane;
+        const bool f = j < nA && wkey[j] >= T;
+        const uint32_t mask = __ballot_sync(0xffffffffu, f);
+        const uint32_t at = n + __popc(mask & ((1u << lane) - 1u));
+        if (f && at < (uint32_t)kAboveWarp) wpos[at] = widx[j];
+        n += __popc(mask);
+      }
+      staged_all = n <= (uint32_t)kRankMax;
+      if (staged_all) {
+        __syncwarp();
+        for (uint32_t i = lane; i < n; i += 32) {
+          const uint32_t pi = wpos[i];
+          uint32_t r = 0;
+          for (uint32_t j = 0; j < n; ++j) r += wpos[j] < pi ? 1u : 0u;
+          if (pos + r < (uint32_t)kTopK) out[pos + r] = (int32_t)pi;
+        }
+      }
+    }
+    if (staged_all) end = beg;                  // nothing left for the second pass
+  }
   const int per_step = 32 * EPL;
   const int steps = (end - beg + per_step - 1) / per_step;
   const float Tf = key_to_float(T);             // score >= Tf  <=>  key >= T (NaN: false)
-  for (int t = 0; t < steps; t += 4) {
-    float x[4][EPL];
+  constexpr int UE = 8;                           // loads in flight per lane
+  for (int t = 0; t < steps; t += UE) {
+    float x[UE][EPL];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) load_vals<EPL>(s, beg + ((t + u) * 32 + lane) * EPL, end, x[u]);
+    for (int u = 0; u < UE; ++u) load_vals<EPL>(s, beg + ((t + u) * 32 + lane) * EPL, end, x[u]);
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < UE; ++u) {
       const int i0 = beg + ((t + u) * 32 + lane) * EPL;
       uint32_t flags = 0;
 #pragma unroll
@@ -515,7 +574,6 @@ extern "C" VMK_API int vmk_debug_sel_timing(long long* out, int reset) {
 }
 #endif
 
-constexpr int kSelCluster = 8;         // most CTAs per request for long rows
 static int g_select_cluster = 0;       // test hook: 0 = chosen by the batch, else 1, 2, 4 or 8
 
 template <int EPL>
