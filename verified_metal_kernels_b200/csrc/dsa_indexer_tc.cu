@@ -288,6 +288,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
     auto ebar = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(kSets * 128) : "memory"); };
     if (set < kSets) {
       int j = 0;
+      uint64_t score_policy;
+      asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(score_policy));
       while (next_run(p, run, g0, g1)) {
         const int b = run.req, n = run.n;
         // the request's head weights (times its query scales with fp8 keys): everybody is past the closing
@@ -323,7 +325,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) indexer_tc_kernel(const __grid_
           for (int h = 0; h < 32; ++h) s += sW[32 + h] * relu_nan(__uint_as_float(r1[h]));
           if (pos < n) {
             if (FP8) s *= kscale;
-            dst[pos] = s;
+            // the scores are read again at once by the selection: last to leave L2 among what this kernel streams
+            asm volatile("st.global.L2::cache_hint.f32 [%0], %1, %2;" ::"l"(dst + pos), "f"(s), "l"(score_policy) : "memory");
             // first level of the top-k radix select, fused here so that the select pass starts one level down
             if (p.hist != nullptr) atomicAdd(&sHist[score_key(s) >> kSelShift], 1u);
           }
