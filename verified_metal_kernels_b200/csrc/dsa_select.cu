@@ -29,6 +29,7 @@ constexpr int kCandWarp = kCandCap / 32;    // each warp stages into a region of
 constexpr int kAboveWarp = 160;             // per warp: positions of the entries above the boundary bin (staged too,
                                             // so that a warp whose selected entries fit here needs no second pass)
 constexpr int kRankMax = 96;                // ... and are few enough to be ranked by counting
+constexpr int kRankSpan = 1024;             // shortest warp span for which that is done
 constexpr int kSelSmem = kCandCap * 8 + 32 * kAboveWarp * 4;      // (key, position) pairs, then the positions above
 
 #ifdef VMK_SEL_TIMING
@@ -362,7 +363,10 @@ __global__ void __launch_bounds__(kSelThreads, 1) select_kernel(const float* __r
   // cluster-uniform; the lowest bin (NaN lives there) and the empty top bins take the general path
   bool fast = c1 <= (uint32_t)kCandCap && b1 >= 1u && b1 <= 2043u;
   uint32_t T = 0;
-  uint32_t bstaged = 0;                         // entries above the boundary bin in this warp's span (warp-uniform)
+  // entries above the boundary bin in this warp's span (warp-uniform).  Their positions are kept only for a span
+  // long enough that ranking the kept entries beats a second pass over it (measured: 4096 positions per warp
+  // 41 -> 35.5 us, 1024: 19.7 -> 18.6; a span of 256 lost 2-4 us): a short span starts "full".
+  uint32_t bstaged = (end - beg) >= kRankSpan ? 0u : (uint32_t)kAboveWarp + 1u;
   if (fast) {
     // ---- one pass: every warp stages the boundary-bin entries of its span, in position order, into its
     //      own region, and counts what lies above the bin.  Membership in the bin is an interval test on
