@@ -141,7 +141,7 @@ class ClockSampler:
         for r in rows:
             bits |= r[2]
         sm = [r[1] for r in rows]
-        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=self.max_mhz,
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_mhz_min=min(sm) if sm else None, sm_max_mhz=self.max_mhz,
                     reasons=[n for b, n in self.REASONS.items() if bits & b], samples=len(sm), window=window,
                     sampler_error=self.err)
 
@@ -151,6 +151,9 @@ def dsa_inputs(B, L, device, seed):
     """Synthetic dsa inputs on the device with the generator's distributions (chunked to bound memory)."""
     from verified_metal_kernels_b200 import abbench
     return abbench.device_inputs("dsa", dict(B=B, L=L), seed, device)
+
+
+RANK_MS = []          # per call of timed_steps under torch.distributed: ms per step of every rank
 
 
 def timed_steps(fn, steps, warmup, dist, torch, sampler=None):
@@ -178,9 +181,12 @@ def timed_steps(fn, steps, warmup, dist, torch, sampler=None):
     total_ms = ev[0].elapsed_time(ev[-1])
     per = [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
     if dist is not None:
+        # every rank's own time for the K steps: the step is their maximum, the spread says where a loss comes from
         t = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
+        every = torch.empty(dist.get_world_size(), device="cuda", dtype=torch.float64)
+        dist.all_gather_into_tensor(every, t)
+        RANK_MS.append([round(float(x) / steps, 5) for x in every.tolist()])
+        total_ms = float(every.max().item())
     return total_ms / 1e3, per, clocks
 
 
@@ -846,15 +852,26 @@ def main():
 
     sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
     results = {}
+    clocks_by_rank = {}
     if world == 1:
         results["weak"] = timed(inp_full, B, sampler) + (B, B)
     else:
         order = ["strong", "weak"] if scaling == "strong" else ["weak", "strong"]
+        rank_ms = {}
         for i, kind in enumerate(order):
+            # every rank samples its own GPU's clock in both runs: when the step (the maximum over the ranks) is
+            # slower than one GPU's, the per-rank times and clocks say which GPUs and why
+            smp = sampler if (i == 0 and rank == 0) else ClockSampler(torch.cuda.current_device())
             if kind == "strong":
-                results[kind] = timed(inp_strong, n_strong, sampler if i == 0 else None) + (B, n_strong)
+                results[kind] = timed(inp_strong, n_strong, smp) + (B, n_strong)
             else:
-                results[kind] = timed(inp_full, B, sampler if i == 0 else None) + (B * world, B)
+                results[kind] = timed(inp_full, B, smp) + (B * world, B)
+            rank_ms[kind] = RANK_MS[-1]
+            mine = results[kind][2] or {}
+            every = [None] * world
+            dist.all_gather_object(every, dict(sm_mhz=mine.get("sm_mhz"), sm_mhz_min=mine.get("sm_mhz_min"),
+                                               reasons=mine.get("reasons")))
+            clocks_by_rank[kind] = every
     status = _lib.read_status(dev)
     ok = ok and abbench.checksum({k: v for k, v in inp_strong.items() if v is not None}) == before
     ok = all_ranks_ok(ok, dist, torch)
@@ -881,6 +898,9 @@ def main():
         if kind != head or world > 1:
             line[kind] = dict(value=bt * a.steps / s_, unit=UNIT, ms_per_step=s_ * 1e3 / a.steps, global_batch=bt,
                               per_rank_batch=bl, scaling=kind)
+            if world > 1:
+                line[kind]["ms_per_step_by_rank"] = rank_ms[kind]
+                line[kind]["clocks_by_rank"] = clocks_by_rank[kind]
 
     side_ops = None
     if world > 1 and not a.no_side:
