@@ -147,8 +147,8 @@ __device__ __forceinline__ void cluster_sync_all() {
 
 #ifdef VMK_MLA_TIMING
 // Debug build only.  Time stamps of blocks 8..15 of CTA 0: [role][block - 8][event]; roles 0 = issuers,
-// 1 = gather warp 0, 2 = softmax group A warp 0, 3 = softmax group B warp 0.
-__device__ long long g_pair_trace[4 * 8 * 16];
+// 1 = gather warp 0, 2 = softmax group A warp 0, 3 = softmax group B warp 0, 4 = the exchange warp of lane quarter 0.
+__device__ long long g_pair_trace[5 * 8 * 16];
 #define PAIR_E(role, j, ev) do { if (blockIdx.x == 0 && (j) >= 8 && (j) < 16 && lane == 0) \
     g_pair_trace[((role) * 8 + (j) - 8) * 16 + (ev)] = clock64(); } while (0)
 #else
@@ -561,7 +561,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_pair_kernel(const __grid_cons
       for (int j = 0; j < w.nblk; ++j, ++g) {
         bool ok = mbar_wait(s_full, (uint32_t)(g & 1));
         if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
-        if (quarter == 0) PAIR_E(3, g, 0);
+        if (quarter == 0) PAIR_E(4, g, 0);
         tc_fence_after();
         uint32_t s0[32], s1[32];
         tmem_ld32(tS, s0);
@@ -570,13 +570,13 @@ __global__ void __launch_bounds__(kThreads, 1) mla_pair_kernel(const __grid_cons
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(s_free);
-        if (quarter == 0) PAIR_E(3, g, 1);
+        if (quarter == 0) PAIR_E(4, g, 1);
         // the staging buffer of two blocks back has been read by our softmax threads; the peer has read the block
         // before (so its buffer is free, and our copy out of this staging buffer, older still, is complete)
         if (g >= 2) ok = mbar_wait(&xs_free[g & 1], (uint32_t)(((g >> 1) - 1) & 1));
         if (ok && g >= 1) ok = mbar_wait_peer_relaxed(x_free, (uint32_t)((g - 1) & 1));
         if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
-        if (quarter == 0) PAIR_E(3, g, 2);
+        if (quarter == 0) PAIR_E(4, g, 2);
         float4* snd = xsend + (g & 1) * (kXBytes / 16) + (quarter * 16) * 32 + lane;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -591,7 +591,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_pair_kernel(const __grid_cons
           mbar_arrive(&xs_full[g & 1]);
           bulk_copy_to_peer(peer_x, snd - lane, kXBytes / 4, peer_x_full);
         }
-        if (quarter == 0) PAIR_E(3, g, 3);
+        if (quarter == 0) PAIR_E(4, g, 3);
       }
       rbase += kQEntries + w.nblk;
     }
@@ -683,7 +683,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_pair_kernel(const __grid_cons
 #ifdef VMK_MLA_TIMING
 extern "C" VMK_API int vmk_debug_pair_trace(long long* out) {
   cudaDeviceSynchronize();
-  return (int)cudaMemcpyFromSymbol(out, g_pair_trace, sizeof(long long) * 512);
+  return (int)cudaMemcpyFromSymbol(out, g_pair_trace, sizeof(long long) * 640);
 }
 #endif
 
