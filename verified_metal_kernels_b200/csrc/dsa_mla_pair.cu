@@ -328,6 +328,7 @@ __global__ void __launch_bounds__(kThreads, 1) mla_pair_kernel(const __grid_cons
           if (!__all_sync(0xffffffffu, ok)) { timed_out = true; break; }
           tc_fence_after();
         }
+        if (quarter == 0) PAIR_E(2 + grp, g, 9);
         // O of this warp's heads, this group's 128 columns, is rescaled when some head's reference moved (warp-uniform)
         if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll 1
@@ -345,8 +346,10 @@ __global__ void __launch_bounds__(kThreads, 1) mla_pair_kernel(const __grid_cons
           uint32_t pk[16];
 #pragma unroll
           for (int e = 0; e < 16; ++e) pk[e] = pack2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1]), p.bf16);
+          if (quarter == 0) PAIR_E(2 + grp, g, 10);
           tmem_st16(tPw, pk);
           tmem_st_wait();
+          if (quarter == 0) PAIR_E(2 + grp, g, 11);
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(p_full);
