@@ -593,8 +593,8 @@ static int launch_select(const float* scores, const uint32_t* hist, const int32_
     if (e != cudaSuccess) return check_launch(e);
     configured_dev = dev;
   }
-  // Long rows of a small batch are split over a cluster of 8, 4 or 2 CTAs (that many SMs read a row together): the
-  // largest size at which all B clusters are resident together.  That is fewer than SMs / size: a cluster lives inside
+  // Long rows of a small batch are split over a cluster of 8, 4 or 2 CTAs (that many SMs read a row together), at
+  // most the size at which all B clusters are resident together.  That is fewer than SMs / size: a cluster lives inside
   // one GPC (16 requests x 8 CTAs are 128 CTAs, but they took two waves: 0.036 ms against 0.020 ms with 4 CTAs each;
   // 32 x 8: 0.055 against 0.021; 37 x 4: 0.043 against 0.028 with 2 each).  With many requests every SM is busy
   // anyway and one CTA per request does the same work with fewer barriers.
@@ -625,8 +625,15 @@ static int launch_select(const float* scores, const uint32_t* hist, const int32_
   if (g_select_cluster > 0) {
     csize = g_select_cluster;
   } else {
-    for (int i = 3; i >= 1 && csize == 1; --i)
-      if (B <= resident[i]) csize = 1 << i;
+    // about 32768 positions per CTA (L = 131072, 1-8 requests: 27.7-31.7 us with one CTA, 15.0-16.9 with four,
+    // 17.9-20.1 with eight, whose extra barriers cost more than the shorter spans save), then as many CTAs per
+    // request as are resident together
+    while (csize < 8 && L / csize > 49152) csize <<= 1;
+    int i = csize == 8 ? 3 : csize == 4 ? 2 : 1;
+    while (csize > 1 && B > resident[i]) {
+      csize >>= 1;
+      --i;
+    }
   }
   if (L >= 32768 && csize > 1) {
     cudaLaunchConfig_t cfg;
