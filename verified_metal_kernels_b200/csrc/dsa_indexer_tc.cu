@@ -379,10 +379,11 @@ int indexer_tc_launch(const CUtensorMap& tmIK, const CUtensorMap& tmIQ, const fl
     if (e != cudaSuccess) return check_launch(e);
     configured_dev = dev;
   }
-  // one CTA per SM; fewer when the tiles would not give each of them eight
+  // one CTA per SM; fewer when the tiles would not give each of them two (a small call is all latency: spreading
+  // it thin costs a CTA's set-up once, in parallel, and shortens every CTA's run)
   const long long tiles = (long long)B * cdiv(L, kTile);
   int ncta = sm_count();
-  if (tiles < (long long)ncta * 8) ncta = (int)((tiles + 7) / 8);
+  if (tiles < (long long)ncta * 2) ncta = (int)((tiles + 1) / 2);
   if (ncta < 1) ncta = 1;
   if (fp8) indexer_tc_kernel<true><<<ncta, kTcThreads, kTcSmem, stream>>>(p);
   else indexer_tc_kernel<false><<<ncta, kTcThreads, kTcSmem, stream>>>(p);
