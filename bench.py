@@ -777,6 +777,22 @@ def e2e_leg(fn, inp, Bl, L, world, steps, dist, torch):
         finally:
             dsa_b200.HOST_CACHE_IN_PLACE = True
         e2e["copy_everything"] = dict(value=e_rows * e_steps / fsec, unit=UNIT, h2d_bytes_per_step=all_bytes)
+        # the same call with the index queries and keys as e4m3 bytes + scales (a different input format, reported
+        # beside): the index keys are most of what crosses the link, and this halves them
+        iq8, iqs, ik8, iks = fp8_index({k: inp[k][:Be] for k in ("iq", "ik")}, torch)
+        h8 = []
+        for t in (iq8, iqs, ik8, iks):
+            h = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+            h.copy_(t)
+            h8.append(h)
+        del iq8, iqs, ik8, iks
+        torch.cuda.synchronize()
+        run_8 = ((lambda: dsa_b200.kernel_fp8_index(host["q"], host["kv"], h8[0], h8[1], h8[2], h8[3], host["w"]))
+                 if Bl > 0 else (lambda: None))
+        gsec, _, _ = timed_steps(run_8, e_steps, 1, dist, torch)
+        small = sum(host[k].numel() * host[k].element_size() for k in ("q", "w")) + sum(h.numel() * h.element_size() for h in h8)
+        e2e["fp8_index"] = dict(value=e_rows * e_steps / gsec, unit=UNIT,
+                                h2d_bytes_per_step=small + Be * min(L, 2048) * 576 * 2)
     return e2e
 
 

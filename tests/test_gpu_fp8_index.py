@@ -45,3 +45,21 @@ def test_fp8_index_keys(shape, dist):
     sel = [idx[b, :cnt[b]].cpu().numpy().astype(np.int64) for b in range(B)]
     truth = ref64.dsa_ref64(inp["q"], inp["kv"], inp["iq"], inp["ik"], inp["w"], lens, sel=sel)
     assert judge.judge_l2(out.float().cpu().numpy(), truth, half=True)["ok"]
+
+
+def test_fp8_index_host_tensors_and_host_cache():
+    """kernel_fp8_index with host tensors: everything copied in, or the page-locked latent cache read in place
+    (only the selected rows cross the link): the same bits as the device-resident call, returned on the host."""
+    inp = op.make_inputs(dict(B=2, L=6000), seed=82, dist="ragged")
+    d = _verify.device_inputs("dsa", inp)
+    iq8, iqs = dsa_b200.quantize_e4m3(d["iq"])
+    ik8, iks = dsa_b200.quantize_e4m3(d["ik"])
+    ref = dsa_b200.kernel_fp8_index(d["q"], d["kv"], iq8, iqs, ik8, iks, d["w"], d["lens"])
+    torch.cuda.synchronize()
+    host = [t.cpu() for t in (d["q"], d["kv"], iq8, iqs, ik8, iks, d["w"], d["lens"])]
+    out_copy = dsa_b200.kernel_fp8_index(*host)
+    assert not out_copy.is_cuda and torch.equal(out_copy, ref.cpu())
+    host[1] = host[1].pin_memory()
+    out_in_place = dsa_b200.kernel_fp8_index(*host)
+    assert not out_in_place.is_cuda and torch.equal(out_in_place, ref.cpu())
+    _verify.assert_clean_status()

@@ -247,10 +247,20 @@ def kernel_projected(q, kv, x, wq, ww, ik, w_scale=1.0, lens=None, return_select
 
 def kernel_fp8_index(q, kv, iq8, iq_scale, ik8, ik_scale, w, lens=None, return_selection=False):
     """The op with the index queries and keys in fp8 (q and kv stay fp16 or bf16): stage 1 on fp8, then the
-    usual select and sparse attention."""
+    usual select and sparse attention.  Host tensors are copied in and the result comes back on the host; a
+    page-locked host `kv` is read in place (only the selected rows cross the link), as in kernel()."""
+    if (HOST_CACHE_IN_PLACE and isinstance(kv, torch.Tensor) and not kv.is_cuda and kv.is_pinned() and kv.dim() == 3
+            and kv.shape[1] > TOPK and kv.dtype in (torch.float16, torch.bfloat16) and kv.is_contiguous()):
+        (q, iq8, iq_scale, ik8, ik_scale, w, lens), _ = stage_in([q, iq8, iq_scale, ik8, ik_scale, w, lens])
+        scores, hist = indexer_hist_fp8(iq8, iq_scale, ik8, ik_scale, w, lens)
+        idx, cnt = select(scores, lens, hist)
+        kv_sel, idx_sel = gather(kv, idx, cnt)
+        out = _lib.finish(attend(q, kv_sel, idx_sel, cnt), True, True, q.device, "dsa, fp8 index keys (host-resident cache)")
+        return (out, idx, cnt) if return_selection else out
+    (q, kv, iq8, iq_scale, ik8, ik_scale, w, lens), host = stage_in([q, kv, iq8, iq_scale, ik8, ik_scale, w, lens])
     scores, hist = indexer_hist_fp8(iq8, iq_scale, ik8, ik_scale, w, lens)
     idx, cnt = select(scores, lens, hist)
-    out = attend(q, kv, idx, cnt)
+    out = _lib.finish(attend(q, kv, idx, cnt), host, False, q.device, "dsa, fp8 index keys")
     return (out, idx, cnt) if return_selection else out
 
 
