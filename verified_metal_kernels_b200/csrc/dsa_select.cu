@@ -625,10 +625,11 @@ static int launch_select(const float* scores, const uint32_t* hist, const int32_
   if (g_select_cluster > 0) {
     csize = g_select_cluster;
   } else {
-    // about 32768 positions per CTA (L = 131072, 1-8 requests: 27.7-31.7 us with one CTA, 15.0-16.9 with four,
-    // 17.9-20.1 with eight, whose extra barriers cost more than the shorter spans save), then as many CTAs per
-    // request as are resident together
-    while (csize < 8 && L / csize > 49152) csize <<= 1;
+    // measured with 1-8 requests (us, CTAs per request 1 / 2 / 4 / 8): L = 32768: 16.0-16.9 / 15.4-15.9 / 15.5-16.0 /
+    // 17.3-17.8; L = 65536: 19.8-22.2 / 15.2-17.2 / 16.1-17.5 / 17.6-19.0; L = 131072: 27.7-31.7 / 19.4-22.0 /
+    // 15.0-16.9 / 17.9-20.1 (eight CTAs: the extra barriers cost more than the shorter spans save until the rows are
+    // much longer); then no more CTAs per request than are resident together
+    csize = L >= 524288 ? 8 : L >= 98304 ? 4 : 2;
     int i = csize == 8 ? 3 : csize == 4 ? 2 : 1;
     while (csize > 1 && B > resident[i]) {
       csize >>= 1;
