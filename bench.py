@@ -918,6 +918,15 @@ def main():
                 line[kind]["ms_per_step_by_rank"] = rank_ms[kind]
                 line[kind]["clocks_by_rank"] = clocks_by_rank[kind]
 
+    if world > 1:
+        # the stages one by one on every rank's own 128 requests: when some GPUs are slower than others on the whole
+        # step (ms_per_step_by_rank), this says in which stage
+        mine = stage_times(inp_full, min(a.steps, 10), torch)
+        every = [None] * world
+        dist.all_gather_object(every, {k: round(v, 5) for k, v in mine.items()})
+        if "weak" in line:
+            line["weak"]["stages_ms_by_rank"] = every
+
     side_ops = None
     if world > 1 and not a.no_side:
         # side configurations on all ranks (collectives inside): the big dsa inputs go first

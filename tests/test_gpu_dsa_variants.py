@@ -117,3 +117,30 @@ def test_select_cluster_sizes_agree():
             assert judge.select_check(idx[b], cnt[b], s64[b], int(inp["lens"][b]))["ok"], cs
             n = int(cnt[b])
             assert np.array_equal(idx[b, :n], outs[0][0][b, :n]), cs
+
+
+def test_select_crowded_boundary_bin_and_ties_stay_exact():
+    """Scores whose boundary bin is crowded and unevenly spread (one warp's span holds far more than its share),
+    and scores with many entries equal to the threshold: the selection is still the exact top-2048 with ties to the
+    lowest positions, whichever path the kernel takes."""
+    L = 131072
+    g = torch.Generator(device="cuda").manual_seed(5)
+    crowded = torch.randn(L, device="cuda", generator=g) * 0.1
+    # 2.0 .. 2.49 share the top 11 key bits: 6000 such values, a third of them inside one warp's span of 4096
+    crowded[torch.randperm(L, device="cuda", generator=g)[:4000]] = 2.0 + 0.49 * torch.rand(4000, device="cuda", generator=g)
+    crowded[8192:8192 + 2000] = 2.0 + 0.49 * torch.rand(2000, device="cuda", generator=g)
+    crowded[torch.randperm(L, device="cuda", generator=g)[:1500]] = 3.0 + torch.rand(1500, device="cuda", generator=g)
+    tied = torch.randn(L, device="cuda", generator=g) * 0.1
+    tied[torch.randperm(L, device="cuda", generator=g)[:2000]] = 5.0 + torch.rand(2000, device="cuda", generator=g)
+    tied[torch.randperm(L, device="cuda", generator=g)[:150]] = 4.25            # 150 equal values around the threshold
+    scores = torch.stack([crowded, tied]).contiguous()
+    order = torch.sort(scores, dim=1, descending=True, stable=True).indices[:, :2048]
+    want = torch.sort(order, dim=1).values.to(torch.int32)
+    try:
+        for cs in (0, 1, 4):
+            dsa_b200.set_select_cluster(cs)
+            idx, cnt = dsa_b200.select(scores)
+            assert bool((cnt == 2048).all()) and torch.equal(idx, want), cs
+    finally:
+        dsa_b200.set_select_cluster(0)
+    _verify.assert_clean_status()

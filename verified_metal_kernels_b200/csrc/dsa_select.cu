@@ -4,14 +4,15 @@
 // last) and the 2048-th largest key T is found by a radix select over 11 + 11 + 10 bits:
 //   level 1  a 2048-bin histogram of the top 11 bits -- taken from the indexer, which accumulates it in
 //            its epilogue, or built here in one pass when absent;
-//   fast path (the boundary bin holds at most 8192 entries and the entries equal to T all fit in the
-//            result): ONE pass over the scores stages the boundary bin's (key, position) pairs in shared
-//            memory and, per warp span, counts the entries above the bin and keeps their positions while they
+//   fast path (the boundary bin holds at most 8192 entries; entries equal to T that do not all fit in the
+//            result are told apart by position): ONE pass over the scores stages the boundary bin's (key,
+//            position) pairs in shared memory and, per warp span, counts the entries above the bin and keeps their positions while they
 //            fit; levels 2 and 3 then run on the staged pairs only; a warp whose selected entries were all kept
 //            (the usual case) ranks them by counting and writes them out, any other warp makes ONE more pass over
 //            its span that writes the positions in ascending order;
-//   general path (huge boundary bin, or more ties at T than fit): levels 2 and 3 over the scores, then an
-//            ordered compaction that takes the ties at T from the lowest positions.
+//   general path (a boundary bin of more than 8192 entries, more than twice a warp's share of it inside one warp's
+//            span, or more than 256 entries equal to T): levels 2 and 3 over the scores, then an ordered compaction
+//            that takes the ties at T from the lowest positions.
 // The result is deterministic: the same scores always give the same ascending index list.  Passes read
 // the scores as float4 when the row length allows (four independent 16-byte loads in flight per lane).
 #include <cooperative_groups.h>
@@ -24,12 +25,17 @@ namespace vmk {
 
 constexpr int kTopK = VMK_DSA_TOPK;
 constexpr int kSelThreads = 1024;
-constexpr int kCandCap = 8192;              // staged pairs in total
-constexpr int kCandWarp = kCandCap / 32;    // each warp stages into a region of its own (no atomics)
+constexpr int kCandBin = 8192;              // largest boundary bin the fast path takes
+constexpr int kCandCap = 2 * kCandBin;      // room for staged pairs: each warp stages into a region of its own (no
+constexpr int kCandWarp = kCandCap / 32;    // atomics) that holds twice its share of the largest bin.  With regions of
+                                            // exactly the share, a bin of 7738 entries (242 per warp on average) had a
+                                            // warp with 283 and sent its request down the general path: 0.137 ms for
+                                            // the kernel instead of 0.035, on about one batch of 128 in four
 constexpr int kAboveWarp = 160;             // per warp: positions of the entries above the boundary bin (staged too,
                                             // so that a warp whose selected entries fit here needs no second pass)
 constexpr int kRankMax = 96;                // ... and are few enough to be ranked by counting
 constexpr int kRankSpan = 1024;             // shortest warp span for which that is done
+constexpr int kTieCap = 256;                // most entries equal to the threshold key the fast path sorts out itself
 constexpr int kSelSmem = kCandCap * 8 + 32 * kAboveWarp * 4;      // (key, position) pairs, then the positions above
 
 #ifdef VMK_SEL_TIMING
@@ -48,6 +54,9 @@ struct SelShared {
   uint32_t w_n[32];          // staged pairs per warp
   uint32_t overflow;
   uint32_t total;            // entries this CTA contributes to the result
+  uint32_t tie_n;            // rank 0 only: entries with key == T gathered so far (peers add theirs remotely)
+  uint32_t tie_cut;          // entries with key == T belong to the result up to this position
+  uint32_t tie_pos[kTieCap]; // rank 0: their positions, in no order; every rank: a local copy
   uint32_t sum[kSelBins];    // histogram summed over the cluster (level 1, or a local copy of acc*)
   uint32_t acc2[kSelBins];   // rank 0 only: level-2 histogram, peers add their staged entries remotely
   uint32_t acc3[kSelBins];   // rank 0 only: level-3 histogram
@@ -314,6 +323,8 @@ __global__ void __launch_bounds__(kSelThreads, 1) select_kernel(const float* __r
   if (tid == 0) {
     sh.overflow = 0u;
     sh.total = 0u;
+    sh.tie_n = 0u;
+    sh.tie_cut = 0xffffffffu;
   }
   for (int i = tid; i < kSelBins; i += kSelThreads) sh.acc2[i] = sh.acc3[i] = 0u;
   __syncthreads();
@@ -361,7 +372,7 @@ __global__ void __launch_bounds__(kSelThreads, 1) select_kernel(const float* __r
   SEL_T(1);
 
   // cluster-uniform; the lowest bin (NaN lives there) and the empty top bins take the general path
-  bool fast = c1 <= (uint32_t)kCandCap && b1 >= 1u && b1 <= 2043u;
+  bool fast = c1 <= (uint32_t)kCandBin && b1 >= 1u && b1 <= 2043u;
   uint32_t T = 0;
   // entries above the boundary bin in this warp's span (warp-uniform).  Their positions are kept only for a span
   // long enough that ranking the kept entries beats a second pass over it (measured: 4096 positions per warp
@@ -464,13 +475,51 @@ __global__ void __launch_bounds__(kSelThreads, 1) select_kernel(const float* __r
       tie_total = sh.res[2];
       __syncthreads();
     }
-    fast = !overflow && tie_total == need;      // every entry equal to T belongs to the result
+    // Entries equal to T: all of them belong to the result (the usual case), or only the `need` of them at the lowest
+    // positions.  With scores summed from 16-bit products a tie at the threshold is not rare (about one request in a
+    // thousand at L = 131072), and the general path costs a request 0.13 ms instead of 0.035: the tied entries are
+    // staged ones, so they are gathered (positions only, on rank 0 of a cluster) and the cut position is the need-th
+    // smallest of them.
+    bool ties_ok = tie_total == need;
+    if (!overflow && !ties_ok && tie_total <= (uint32_t)kTieCap) {
+      uint32_t* n0 = &sh.tie_n;
+      uint32_t* pos0 = sh.tie_pos;
+      if (CLUSTER) {
+        cg::cluster_group cluster = cg::this_cluster();
+        n0 = cluster.map_shared_rank(&sh.tie_n, 0);
+        pos0 = cluster.map_shared_rank(sh.tie_pos, 0);
+      }
+      for (int j = tid; j < kCandCap; j += kSelThreads) {
+        if ((uint32_t)(j % kCandWarp) < sh.w_n[j / kCandWarp] && ckey[j] == T) {
+          const uint32_t slot = atomicAdd(n0, 1u);
+          if (slot < (uint32_t)kTieCap) pos0[slot] = cidx[j];
+        }
+      }
+      if (CLUSTER) cg::this_cluster().sync(); else __syncthreads();
+      uint32_t mine = 0xffffffffu;
+      if ((uint32_t)tid < tie_total) mine = pos0[tid];      // (rank 0's list; every rank takes its own copy)
+      __syncthreads();
+      if ((uint32_t)tid < tie_total) sh.tie_pos[tid] = mine;
+      __syncthreads();
+      if ((uint32_t)tid < tie_total) {
+        uint32_t r = 0;
+        for (uint32_t j = 0; j < tie_total; ++j) r += sh.tie_pos[j] < mine ? 1u : 0u;
+        if (r + 1u == need) sh.tie_cut = mine;              // positions are distinct: exactly one thread
+      }
+      __syncthreads();
+      ties_ok = true;
+    }
+    fast = !overflow && ties_ok;
   }
+  const uint32_t tie_cut = sh.tie_cut;          // 0xffffffff when every entry equal to T is taken
+  // a staged or scanned entry belongs to the result
+  auto taken = [&](uint32_t key, uint32_t position) { return key > T || (key == T && position <= tie_cut); };
   uint32_t pos = 0;
   if (fast) {
     // selected entries of this warp's span = those above the boundary bin + its staged ones with key >= T
     uint32_t c = 0;
-    for (uint32_t j = lane; j < sh.w_n[warp]; j += 32) c += ckey[warp * kCandWarp + j] >= T ? 1u : 0u;
+    for (uint32_t j = lane; j < sh.w_n[warp]; j += 32)
+      c += taken(ckey[warp * kCandWarp + j], cidx[warp * kCandWarp + j]) ? 1u : 0u;
     c = (uint32_t)__reduce_add_sync(0xffffffffu, c);
     if (lane == 0) {
       sh.w_a[warp] += c;
@@ -512,7 +561,7 @@ __global__ void __launch_bounds__(kSelThreads, 1) select_kernel(const float* __r
       const uint32_t nA = sh.w_n[warp];
       for (uint32_t j0 = 0; j0 < nA; j0 += 32) {
         const uint32_t j = j0 + lane;
-        const bool f = j < nA && wkey[j] >= T;
+        const bool f = j < nA && taken(wkey[j], widx[j]);
         const uint32_t mask = __ballot_sync(0xffffffffu, f);
         const uint32_t at = n + __popc(mask & ((1u << lane) - 1u));
         if (f && at < (uint32_t)kAboveWarp) wpos[at] = widx[j];
@@ -544,7 +593,8 @@ __global__ void __launch_bounds__(kSelThreads, 1) select_kernel(const float* __r
       const int i0 = beg + ((t + u) * 32 + lane) * EPL;
       uint32_t flags = 0;
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) flags |= x[u][e] >= Tf ? (1u << e) : 0u;
+      for (int e = 0; e < EPL; ++e)
+        flags |= (x[u][e] > Tf || (x[u][e] == Tf && (uint32_t)(i0 + e) <= tie_cut)) ? (1u << e) : 0u;
       if (!__any_sync(0xffffffffu, flags != 0u)) continue;
       const uint32_t c = __popc(flags);
       uint32_t incl = c;
