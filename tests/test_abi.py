@@ -113,3 +113,14 @@ def test_build_is_keyed_by_content_not_by_file_times(monkeypatch):
     assert not build.needs_build()
     monkeypatch.setenv("VMK_EXTRA_NVCC_FLAGS", "-DVMK_SOME_FLAG")
     assert build.needs_build()                                 # other flags are
+
+
+def test_variant_switches_refuse_unknown_values(lib):
+    """The process-wide switches are host-side state: unknown values are refused and change nothing."""
+    assert lib.vmk_dsa_set_attend_variant(7) == -1 and lib.vmk_dsa_set_attend_variant(-1) == -1
+    assert lib.vmk_dsa_set_select_cluster(3) == -1 and lib.vmk_dsa_set_select_cluster(16) == -1
+    for v in (0, 1, 2, 3):
+        assert lib.vmk_dsa_set_attend_variant(v) == 0
+    for c in (1, 2, 4, 8, 0):
+        assert lib.vmk_dsa_set_select_cluster(c) == 0
+    assert lib.vmk_dsa_set_attend_variant(3) == 0          # back to the defaults
